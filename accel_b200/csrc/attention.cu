@@ -1,0 +1,368 @@
+// Decode attention over a KV cache: contiguous (internal/kernels/attention.go:97,422), paged
+// (paged.go:47,362), batched (batched.go:53) and ragged (ragged.go:61, raggedf16.go:43).
+//
+// All of them are one computation per (query row, KV head): softmax(q.K^T * scale) V over the
+// positions the row may see, with K/V rows reached through a page table,
+//
+//   physical(j) = pages[j / Block] * Block + j % Block,   row = (physical * KVHeads + kvHead) * HeadDim
+//
+// The reference walks the cache in blocks of 128 with a running softmax and launches one workgroup
+// per QUERY head, so grouped-query heads re-read their shared K/V.  Here a CTA owns one
+// (row, KV head, context partition): its warps stream K and V rows once with 128-bit loads, keep
+// every query head of the group in registers, and carry their own running (max, sum, output); the
+// warps are merged through shared memory and the partitions by a second kernel (split-K).  The
+// recurrence is the reference's (alpha = exp(m - m')), applied across warps and partitions instead
+// of across blocks, so the result differs from the reference's only by summation order.
+//
+// Edge semantics kept from the reference: a length beyond the page table's reach is clamped to the
+// reach; positions past the length are never read; a zero length gives 0/0 = NaN; ragged padding
+// tokens and tokens with no position write zeros.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace ab {
+
+static constexpr int kWarps = 4;
+static constexpr int kAttnThreads = kWarps * 32;
+static constexpr int kPartition = 256;      // positions per context partition
+static constexpr int kPosUnroll = 4;
+static constexpr float kLog2e = 1.4426950408889634f;
+static constexpr float kNegBig = -3.0e38f;
+
+enum Mode { kContiguous = 0, kPaged = 1, kBatched = 2, kRagged = 3 };
+
+struct AttnParams {
+    const float *q;
+    const void *k, *v;
+    const uint32_t *pages, *lengths, *offsets;
+    float *out;
+    float *part_o;      // [rows][qH][parts][D]
+    float2 *part_ml;    // [rows][qH][parts]
+    uint32_t rows;      // sequences (batched), tokens (ragged), 1 otherwise
+    uint32_t batch, q_heads, kv_heads, head_dim, block, max_pages, parts;
+    uint32_t capacity;  // positions the page table (or the contiguous cache) can address
+    float scale_log2;   // Scale * log2(e)
+    int mode;
+};
+
+// What one query row may see.
+struct RowView { const uint32_t *pages; uint32_t len; bool zero; };
+
+__device__ __forceinline__ RowView row_view(const AttnParams &p, uint32_t row)
+{
+    RowView rv{p.pages, 0, false};
+    if (p.mode == kRagged) {
+        uint32_t seq = 0;
+        for (uint32_t r = 0; r < p.batch; r++) seq += (p.offsets[r + 1] <= row) ? 1u : 0u;
+        if (seq >= p.batch) { rv.zero = true; return rv; }
+        uint32_t i = row - p.offsets[seq], n = p.offsets[seq + 1] - p.offsets[seq];
+        uint32_t kv_len = p.lengths[seq];
+        if (kv_len + i < n) { rv.zero = true; return rv; }
+        uint32_t limit = kv_len + i - n;
+        uint32_t vis = min(min(limit + 1, kv_len), p.capacity);
+        rv.len = vis;
+        rv.pages = p.pages + (size_t)seq * p.max_pages;
+    } else if (p.mode == kBatched) {
+        rv.len = min(p.lengths[row], p.capacity);
+        rv.pages = p.pages + (size_t)row * p.max_pages;
+    } else {
+        rv.len = min(p.lengths[0], p.capacity);
+    }
+    return rv;
+}
+
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float *p)
+    {
+        float4 v;
+        asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+        return v;
+    }
+};
+template <> struct Vec4<__half> {
+    static __device__ __forceinline__ float4 load(const __half *p)
+    {
+        uint2 raw;
+        asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
+                     : "=r"(raw.x), "=r"(raw.y) : "l"(p));
+        float2 a = __half22float2(*reinterpret_cast<__half2 *>(&raw.x));
+        float2 b = __half22float2(*reinterpret_cast<__half2 *>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+
+// grid = (parts, kv_heads, rows).  G = query heads per KV head.
+template <typename T, int G>
+__global__ void __launch_bounds__(kAttnThreads)
+attn_partition_kernel(const AttnParams p)
+{
+    // With G > 1 blockIdx.y is a KV head and the CTA serves its G query heads; with G == 1 it is
+    // a query head, which also covers group widths that have no instantiation.
+    const uint32_t part = blockIdx.x, row = blockIdx.z;
+    const uint32_t hq0 = blockIdx.y * G;
+    const uint32_t kvh = G == 1 ? blockIdx.y / (p.q_heads / p.kv_heads) : blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t D = p.head_dim;
+    const bool lane_on = (uint32_t)lane * 4 < D;
+
+    const RowView rv = row_view(p, row);
+    const uint32_t begin = part * kPartition;
+    if (rv.zero) {
+        if (part == 0) {
+            for (uint32_t i = threadIdx.x; i < G * D; i += kAttnThreads)
+                p.out[((size_t)row * p.q_heads + hq0) * D + i] = 0.f;
+        }
+        return;
+    }
+    if (begin >= rv.len && !(part == 0)) return;     // partition 0 always reports (len 0 -> NaN)
+    const uint32_t end = min(rv.len, begin + kPartition);
+
+    const T *kc = reinterpret_cast<const T *>(p.k);
+    const T *vc = reinterpret_cast<const T *>(p.v);
+    const size_t row_stride = (size_t)p.kv_heads * D;
+    const size_t head_off = (size_t)kvh * D + (size_t)lane * 4;
+
+    float4 qv[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        qv[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (lane_on)
+            qv[g] = *reinterpret_cast<const float4 *>(
+                p.q + ((size_t)row * p.q_heads + hq0 + g) * D + lane * 4);
+        qv[g].x *= p.scale_log2; qv[g].y *= p.scale_log2;
+        qv[g].z *= p.scale_log2; qv[g].w *= p.scale_log2;
+    }
+
+    float m[G], l[G];
+    float4 o[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) { m[g] = kNegBig; l[g] = 0.f; o[g] = make_float4(0.f, 0.f, 0.f, 0.f); }
+
+    for (uint32_t j0 = begin + warp; j0 < end; j0 += kWarps * kPosUnroll) {
+        float4 kv[kPosUnroll], vv[kPosUnroll];
+        bool ok[kPosUnroll];
+#pragma unroll
+        for (int u = 0; u < kPosUnroll; u++) {
+            uint32_t j = j0 + u * kWarps;
+            ok[u] = j < end;
+            kv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            vv[u] = kv[u];
+            if (ok[u] && lane_on) {
+                size_t phys = p.mode == kContiguous
+                                  ? (size_t)j
+                                  : (size_t)__ldg(rv.pages + j / p.block) * p.block + j % p.block;
+                const size_t off = phys * row_stride + head_off;
+                kv[u] = Vec4<T>::load(kc + off);
+                vv[u] = Vec4<T>::load(vc + off);
+            }
+        }
+        float s[kPosUnroll][G];
+#pragma unroll
+        for (int u = 0; u < kPosUnroll; u++)
+#pragma unroll
+            for (int g = 0; g < G; g++)
+                s[u][g] = qv[g].x * kv[u].x + qv[g].y * kv[u].y + qv[g].z * kv[u].z + qv[g].w * kv[u].w;
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1)
+#pragma unroll
+            for (int u = 0; u < kPosUnroll; u++)
+#pragma unroll
+                for (int g = 0; g < G; g++) s[u][g] += __shfl_xor_sync(0xffffffffu, s[u][g], sh);
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float mx = m[g];
+#pragma unroll
+            for (int u = 0; u < kPosUnroll; u++) mx = ok[u] ? fmaxf(mx, s[u][g]) : mx;
+            const float alpha = exp2f(m[g] - mx);
+            m[g] = mx;
+            float sum = 0.f;
+            float4 acc = make_float4(o[g].x * alpha, o[g].y * alpha, o[g].z * alpha, o[g].w * alpha);
+#pragma unroll
+            for (int u = 0; u < kPosUnroll; u++) {
+                const float e = ok[u] ? exp2f(s[u][g] - mx) : 0.f;
+                sum += e;
+                acc.x = fmaf(e, vv[u].x, acc.x); acc.y = fmaf(e, vv[u].y, acc.y);
+                acc.z = fmaf(e, vv[u].z, acc.z); acc.w = fmaf(e, vv[u].w, acc.w);
+            }
+            l[g] = l[g] * alpha + sum;
+            o[g] = acc;
+        }
+    }
+
+    // merge the warps
+    __shared__ float sm_m[kWarps][G], sm_l[kWarps][G];
+    __shared__ float4 sm_o[kWarps][G][32];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+        sm_o[warp][g][lane] = o[g];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float mx = sm_m[0][g];
+#pragma unroll
+            for (int w = 1; w < kWarps; w++) mx = fmaxf(mx, sm_m[w][g]);
+            float lt = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < kWarps; w++) {
+                const float f = exp2f(sm_m[w][g] - mx);
+                lt = fmaf(sm_l[w][g], f, lt);
+                const float4 ow = sm_o[w][g][lane];
+                acc.x = fmaf(ow.x, f, acc.x); acc.y = fmaf(ow.y, f, acc.y);
+                acc.z = fmaf(ow.z, f, acc.z); acc.w = fmaf(ow.w, f, acc.w);
+            }
+            const size_t qrow = (size_t)row * p.q_heads + hq0 + g;
+            if (p.parts == 1) {
+                if (lane_on) {
+                    float4 r4 = make_float4(acc.x / lt, acc.y / lt, acc.z / lt, acc.w / lt);
+                    *reinterpret_cast<float4 *>(p.out + qrow * D + lane * 4) = r4;
+                }
+            } else {
+                if (lane_on)
+                    *reinterpret_cast<float4 *>(p.part_o + (qrow * p.parts + part) * D + lane * 4) = acc;
+                if (lane == 0) p.part_ml[qrow * p.parts + part] = make_float2(mx, lt);
+            }
+        }
+    }
+}
+
+// grid = (q_heads, rows); one thread per output element.
+__global__ void attn_combine_kernel(const AttnParams p)
+{
+    const uint32_t h = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
+    const RowView rv = row_view(p, row);
+    if (rv.zero || d >= p.head_dim) return;
+    uint32_t nparts = (rv.len + kPartition - 1) / kPartition;
+    if (nparts == 0) nparts = 1;
+    const size_t qrow = (size_t)row * p.q_heads + h;
+    float mx = kNegBig;
+    for (uint32_t s = 0; s < nparts; s++) mx = fmaxf(mx, p.part_ml[qrow * p.parts + s].x);
+    float lt = 0.f, acc = 0.f;
+    for (uint32_t s = 0; s < nparts; s++) {
+        const float2 ml = p.part_ml[qrow * p.parts + s];
+        const float f = exp2f(ml.x - mx);
+        lt = fmaf(ml.y, f, lt);
+        acc = fmaf(p.part_o[(qrow * p.parts + s) * p.head_dim + d], f, acc);
+    }
+    p.out[qrow * p.head_dim + d] = acc / lt;
+}
+
+template <typename T>
+static int run_attention(Launch &l, AttnParams &p, const char *name)
+{
+    if (p.kv_heads == 0 || p.q_heads % p.kv_heads != 0)
+        return fail(AB_ERR_INVALID, "%s: %u query heads over %u key/value heads", name, p.q_heads,
+                    p.kv_heads);
+    if (p.head_dim == 0 || p.head_dim % 8 != 0 || p.head_dim > 128)
+        return fail(AB_ERR_INVALID, "%s: head dimension %u; it is a multiple of eight and at most "
+                    "128", name, p.head_dim);
+    if (p.mode != kContiguous && p.block == 0)
+        return fail(AB_ERR_INVALID, "%s: a page table addresses blocks, and Block is 0", name);
+    p.parts = (p.capacity + kPartition - 1) / kPartition;
+    if (p.parts == 0) p.parts = 1;
+    const size_t o_bytes = align_up((size_t)p.rows * p.q_heads * p.parts * p.head_dim * 4, 256);
+    const size_t ml_bytes = (size_t)p.rows * p.q_heads * p.parts * sizeof(float2);
+    const size_t need = p.parts > 1 ? o_bytes + ml_bytes : 0;
+    if (l.query_ws) { l.ws_need = need; return AB_OK; }
+    if (need > l.ws_bytes || (need && !l.ws))
+        return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, need,
+                    l.ws_bytes);
+    p.part_o = reinterpret_cast<float *>(l.ws);
+    p.part_ml = reinterpret_cast<float2 *>(reinterpret_cast<char *>(l.ws) + o_bytes);
+    if (p.rows == 0) return AB_OK;
+
+    const uint32_t group = p.q_heads / p.kv_heads;
+    // a group width with no instantiation runs one query head per CTA (K/V re-read per head)
+    const int G = (group == 2 || group == 4 || group == 8) ? (int)group : 1;
+    dim3 grid(p.parts, G == 1 ? p.q_heads : p.kv_heads, p.rows);
+    switch (G) {
+    case 1: attn_partition_kernel<T, 1><<<grid, kAttnThreads, 0, l.stream>>>(p); break;
+    case 2: attn_partition_kernel<T, 2><<<grid, kAttnThreads, 0, l.stream>>>(p); break;
+    case 4: attn_partition_kernel<T, 4><<<grid, kAttnThreads, 0, l.stream>>>(p); break;
+    default: attn_partition_kernel<T, 8><<<grid, kAttnThreads, 0, l.stream>>>(p); break;
+    }
+    if (p.parts > 1) {
+        dim3 cgrid(p.q_heads, p.rows);
+        attn_combine_kernel<<<cgrid, 128, 0, l.stream>>>(p);
+    }
+    note_selection("%s: split-K decode, %u partition(s) of %d positions, %u query head(s) sharing "
+                   "each K/V read, %u row(s)", name, p.parts, kPartition, group, p.rows);
+    return check_cuda(cudaGetLastError(), name);
+}
+
+// ---- front ends: read the uniform block and the lengths block the way each reference kernel does
+static int contiguous(Launch &l, bool f16, const char *name)
+{   // q, k, v, lengths, out; AttnDims{QHeads,KVHeads,HeadDim,Scale}
+    AttnParams p{};
+    p.mode = kContiguous;
+    p.q_heads = u32_at(l.u, 0); p.kv_heads = u32_at(l.u, 4); p.head_dim = u32_at(l.u, 8);
+    p.scale_log2 = f32_at(l.u, 12) * kLog2e;
+    p.rows = 1; p.batch = 1; p.block = 1;
+    if (!l.query_ws) {
+        p.q = ptr<const float>(l, 0); p.k = l.b[1]; p.v = l.b[2];
+        p.lengths = ptr<const uint32_t>(l, 3); p.out = ptr<float>(l, 4);
+    }
+    uint64_t per = (uint64_t)p.kv_heads * p.head_dim;
+    p.capacity = per ? (uint32_t)(l.len[1] / per) : 0;     // len(k) / (kvHeads*headDim)
+    return f16 ? run_attention<__half>(l, p, name) : run_attention<float>(l, p, name);
+}
+
+static int paged(Launch &l, bool f16, const char *name)
+{   // q, k, v, pages, lengths, out; PagedDims{QHeads,KVHeads,HeadDim,Block,Scale}
+    AttnParams p{};
+    p.mode = kPaged;
+    p.q_heads = u32_at(l.u, 0); p.kv_heads = u32_at(l.u, 4); p.head_dim = u32_at(l.u, 8);
+    p.block = u32_at(l.u, 12);
+    p.scale_log2 = f32_at(l.u, 16) * kLog2e;
+    p.rows = 1; p.batch = 1;
+    if (!l.query_ws) {
+        p.q = ptr<const float>(l, 0); p.k = l.b[1]; p.v = l.b[2];
+        p.pages = ptr<const uint32_t>(l, 3); p.lengths = ptr<const uint32_t>(l, 4);
+        p.out = ptr<float>(l, 5);
+    }
+    p.max_pages = l.len[3];
+    p.capacity = l.len[3] * p.block;                        // len(pages) * Block
+    return f16 ? run_attention<__half>(l, p, name) : run_attention<float>(l, p, name);
+}
+
+static int batched(Launch &l, bool f16, bool ragged, const char *name)
+{   // q, k, v, pages, lengths, [offsets,] out; BatchedDims / RaggedDims
+    AttnParams p{};
+    p.mode = ragged ? kRagged : kBatched;
+    p.batch = u32_at(l.u, 0); p.q_heads = u32_at(l.u, 4); p.kv_heads = u32_at(l.u, 8);
+    p.head_dim = u32_at(l.u, 12); p.block = u32_at(l.u, 16); p.max_pages = u32_at(l.u, 20);
+    p.scale_log2 = f32_at(l.u, 24) * kLog2e;
+    const int out_i = ragged ? 6 : 5;
+    uint64_t per = (uint64_t)p.q_heads * p.head_dim;
+    p.rows = ragged ? (per ? (uint32_t)(l.len[0] / per) : 0) : p.batch;   // tokens = len(q)/(qH*D)
+    p.capacity = p.max_pages * p.block;
+    if (l.len[3] < (uint64_t)p.batch * p.max_pages || l.len[4] < p.batch ||
+        (ragged && l.len[5] < p.batch + 1) || l.len[out_i] < (uint64_t)p.rows * per)
+        return fail(AB_ERR_INVALID, "%s: Batch=%u MaxPages=%u rows=%u and the lengths block says "
+                    "pages[%u] lengths[%u] out[%u]", name, p.batch, p.max_pages, p.rows, l.len[3],
+                    l.len[4], l.len[out_i]);
+    if (!l.query_ws) {
+        p.q = ptr<const float>(l, 0); p.k = l.b[1]; p.v = l.b[2];
+        p.pages = ptr<const uint32_t>(l, 3); p.lengths = ptr<const uint32_t>(l, 4);
+        p.offsets = ragged ? ptr<const uint32_t>(l, 5) : nullptr;
+        p.out = ptr<float>(l, out_i);
+    }
+    return f16 ? run_attention<__half>(l, p, name) : run_attention<float>(l, p, name);
+}
+
+int launch_attention_decode(Launch &l) { return contiguous(l, false, "AttentionDecode"); }
+int launch_attention_decode_f16(Launch &l) { return contiguous(l, true, "AttentionDecodeF16"); }
+int launch_attention_decode_paged(Launch &l) { return paged(l, false, "AttentionDecodePaged"); }
+int launch_attention_decode_paged_f16(Launch &l) { return paged(l, true, "AttentionDecodePagedF16"); }
+int launch_attention_decode_batched(Launch &l) { return batched(l, false, false, "AttentionDecodeBatched"); }
+int launch_attention_decode_batched_f16(Launch &l) { return batched(l, true, false, "AttentionDecodeBatchedF16"); }
+int launch_attention_ragged(Launch &l) { return batched(l, false, true, "AttentionRagged"); }
+int launch_attention_ragged_f16(Launch &l) { return batched(l, true, true, "AttentionRaggedF16"); }
+
+}  // namespace ab

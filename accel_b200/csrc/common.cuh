@@ -1,0 +1,122 @@
+// Shared declarations of the sm_100a kernels and their launchers.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "../../include/accel_b200.h"
+
+namespace ab {
+
+// One dispatch: the reference's argument convention (binding pointers, a lengths block with one
+// element count per binding, the std140 uniform block) plus scratch memory.
+struct Launch {
+    cudaStream_t stream;
+    void *const *b;
+    const uint32_t *len;
+    int nb;
+    const uint8_t *u;
+    size_t ubytes;
+    void *ws;
+    size_t ws_bytes;
+    bool query_ws;      // true: only compute *ws_need, launch nothing, b may be NULL
+    size_t ws_need;
+};
+
+typedef int (*launch_fn)(Launch &);
+
+struct KernelEntry {
+    const char *name;
+    int n_bindings;
+    size_t uniform_bytes;   // 0 = the kernel takes no uniform block
+    launch_fn fn;
+};
+
+int fail(int code, const char *fmt, ...);          // records the thread's last error
+void note_selection(const char *fmt, ...);         // records which variant a launch selected
+int check_cuda(cudaError_t e, const char *what);   // maps a CUDA error to an ab_status
+int sm_count();                                    // SMs of the current device (cached)
+
+inline uint32_t u32_at(const uint8_t *u, size_t off) { uint32_t v; memcpy(&v, u + off, 4); return v; }
+inline float f32_at(const uint8_t *u, size_t off) { float v; memcpy(&v, u + off, 4); return v; }
+
+template <typename T> inline T *ptr(const Launch &l, int i) { return reinterpret_cast<T *>(l.b[i]); }
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// launchers, one per reference kernel name (defined beside their kernels)
+int launch_quant_matvec_int4(Launch &);
+int launch_quant_matmul_int4(Launch &);
+int launch_attention_decode(Launch &);
+int launch_attention_decode_f16(Launch &);
+int launch_attention_decode_paged(Launch &);
+int launch_attention_decode_paged_f16(Launch &);
+int launch_attention_decode_batched(Launch &);
+int launch_attention_decode_batched_f16(Launch &);
+int launch_attention_ragged(Launch &);
+int launch_attention_ragged_f16(Launch &);
+int launch_grouped_matvec(Launch &);
+int launch_grouped_matmul(Launch &);
+int launch_grouped_matmul_int4(Launch &);
+int launch_segment_offsets(Launch &);
+int launch_scatter_rows(Launch &);
+int launch_scatter_rows_f16(Launch &);
+int launch_gather_rows(Launch &);
+int launch_gather_rows_f16(Launch &);
+int launch_rmsnorm(Launch &);
+int launch_rope(Launch &);
+int launch_swiglu(Launch &);
+int launch_elem_add(Launch &);
+int launch_sample_argmax(Launch &);
+int launch_cast_f32_to_f16(Launch &);
+int launch_cast_f16_to_f32(Launch &);
+int launch_int4_quantize(Launch &);
+
+// f32 -> f16 with the reference's rule: round to nearest even, except that every magnitude below
+// 2^-24 becomes a signed zero (internal/kernel/narrow.go:82-83); IEEE rounds (2^-25, 2^-24) up.
+__host__ __device__ inline uint16_t f32_to_f16_ref(float x)
+{
+    uint32_t b;
+#ifdef __CUDA_ARCH__
+    b = __float_as_uint(x);
+#else
+    memcpy(&b, &x, 4);
+#endif
+    uint16_t sign = (uint16_t)((b >> 16) & 0x8000u);
+    int32_t exp = (int32_t)((b >> 23) & 0xffu) - 127;
+    uint32_t mant = b & 0x7fffffu;
+    if ((b & 0x7fffffffu) > 0x7f800000u) return 0x7e00;
+    if (exp >= 16) return (uint16_t)(sign | 0x7c00u);
+    if (exp < -24) return sign;
+    uint32_t shift, base;
+    if (exp < -14) { mant |= 0x800000u; shift = 13u + (uint32_t)(-exp - 14); base = 0; }
+    else { shift = 13u; base = (uint32_t)(exp + 15) << 10; }
+    uint32_t q = mant >> shift, rem = mant & ((1u << shift) - 1u), half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (q & 1u))) q++;
+    return (uint16_t)(sign | (uint16_t)(base + q));
+}
+
+__host__ __device__ inline float f16_bits_to_f32(uint16_t h)
+{
+#ifdef __CUDA_ARCH__
+    return __half2float(__ushort_as_half(h));
+#else
+    uint32_t sign = ((uint32_t)h & 0x8000u) << 16, exp = ((uint32_t)h >> 10) & 0x1fu,
+             mant = (uint32_t)h & 0x3ffu, out;
+    if (exp == 0) {
+        if (mant == 0) out = sign;
+        else {
+            uint32_t shift = 0;
+            while ((mant & 0x400u) == 0) { mant <<= 1; shift++; }
+            out = sign | ((127 - 15 + 1 - shift) << 23) | ((mant & 0x3ffu) << 13);
+        }
+    } else if (exp == 0x1f) out = sign | 0x7f800000u | (mant << 13);
+    else out = sign | ((exp + 127 - 15) << 23) | (mant << 13);
+    float f;
+    memcpy(&f, &out, 4);
+    return f;
+#endif
+}
+
+}  // namespace ab

@@ -1,0 +1,265 @@
+// int4 group-quantized linear: the row kernel (QuantMatVecInt4, internal/kernels/int4.go:60) and the
+// batched form (QuantMatMulInt4, internal/kernels/int4tiled.go:66) for small batches.
+//
+//   out[m][n] = sum_k a[m][k] * w(k,n),   w = s == 0 ? z : (code - z) * s
+//
+// with code = nibble (k*N+n) of bq (eight per u32, low first) and one f16 scale s and zero z per 128
+// consecutive flat weights.  When N is a multiple of 128 a group is 128 adjacent columns of one row
+// k, so the kernel streams each row segment once with 128-bit loads and evaluates
+//
+//   out[m][n] = sum_k (a[m][k]*s) * code  -  sum_k (a[m][k]*s) * z        (s != 0)
+//
+// in f32: the per-weight work is one integer-to-float conversion and one FMA, and the zero-point
+// term costs one FMA per row and group.  A group with s == 0 contributes a[m][k]*z through the
+// second sum.  The summation order differs from the reference's, the values do not.
+#include "common.cuh"
+
+namespace ab {
+
+static constexpr uint32_t kGroup = 128;     // quant.Int4Group
+static constexpr int kTileCols = 256;       // columns per CTA: 8 lanes x 32 nibbles
+static constexpr int kThreads = 256;        // 8 warps, each warp-load covers 4 rows x 256 columns
+static constexpr int kRowsPerStep = 32;     // 8 warps x 4 rows
+static constexpr int kUnroll = 4;
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4 *p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// The nibble at bit position P of w as a float.  OR-ing the masked nibble into the mantissa of
+// 2^(23-P) gives exactly 2^(23-P) + code, and the subtraction is exact, so this is code itself:
+// one logic op and one add, no integer-to-float conversion instruction.  P <= 16 keeps the nibble
+// inside the mantissa; the three high nibbles come from w >> 12.
+template <int P> __device__ __forceinline__ float nib(uint32_t w)
+{
+    constexpr uint32_t magic = (150u - P) << 23;
+    return __uint_as_float((w & (0xFu << P)) | magic) - __uint_as_float(magic);
+}
+
+template <int MR>
+__device__ __forceinline__ void fma_word(uint32_t w, const float (&c)[MR], float (&acc)[MR][32],
+                                         int j)
+{
+    uint32_t w2 = w >> 12;
+    float x[8] = {nib<0>(w), nib<4>(w), nib<8>(w), nib<12>(w),
+                  nib<16>(w), nib<8>(w2), nib<12>(w2), nib<16>(w2)};
+#pragma unroll
+    for (int m = 0; m < MR; m++)
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[m][j * 8 + i] = fmaf(c[m], x[i], acc[m][j * 8 + i]);
+}
+
+// grid = (column tiles, K splits).  dst is `out` when gridDim.y == 1, else the partials
+// [split][M][N] that int4_reduce_kernel sums.
+template <int MR>
+__global__ void __launch_bounds__(kThreads)
+int4_gemv_kernel(const float *__restrict__ a, const uint4 *__restrict__ bq,
+                 const __half *__restrict__ bs, const __half *__restrict__ bz,
+                 float *__restrict__ dst, uint32_t M, uint32_t N, uint32_t K, uint32_t kc,
+                 uint32_t m0, uint32_t mrows)
+{
+    __shared__ float red[8][kTileCols];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 3, c8 = lane & 7;
+    const uint32_t col0 = blockIdx.x * kTileCols + c8 * 32;
+    const bool active = col0 < N;
+    const uint32_t gpr = N / kGroup;                 // groups per row
+    const uint32_t g = col0 / kGroup;
+    const uint32_t kbeg = blockIdx.y * kc;
+    const uint32_t kend = min(K, kbeg + kc);
+
+    float acc[MR][32];
+    float zc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+        zc[m] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; j++) acc[m][j] = 0.f;
+    }
+
+    if (active) {
+        for (uint32_t kk = kbeg + warp * 4 + r; kk < kend; kk += kRowsPerStep * kUnroll) {
+            uint4 cw[kUnroll];
+            float s[kUnroll], z[kUnroll], av[kUnroll][MR];
+#pragma unroll
+            for (int u = 0; u < kUnroll; u++) {
+                uint32_t k = kk + u * kRowsPerStep;
+                bool ok = k < kend;
+                uint32_t ks = ok ? k : kbeg;
+                cw[u] = ldg_stream(bq + ((size_t)ks * N + col0) / 32);
+                s[u] = ok ? __half2float(__ldg(bs + (size_t)ks * gpr + g)) : 0.f;
+                z[u] = ok ? __half2float(__ldg(bz + (size_t)ks * gpr + g)) : 0.f;
+#pragma unroll
+                for (int m = 0; m < MR; m++)
+                    av[u][m] = (ok && (uint32_t)m < mrows) ? __ldg(a + (size_t)(m0 + m) * K + ks) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; u++) {
+                float c[MR];
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    c[m] = av[u][m] * s[u];
+                    // s == 0: the group is the constant z, so the row adds a*z; written as a
+                    // subtraction of -a*z because zc is subtracted below
+                    zc[m] += (s[u] == 0.f) ? -av[u][m] * z[u] : c[m] * z[u];
+                }
+                fma_word<MR>(cw[u].x, c, acc, 0);
+                fma_word<MR>(cw[u].y, c, acc, 1);
+                fma_word<MR>(cw[u].z, c, acc, 2);
+                fma_word<MR>(cw[u].w, c, acc, 3);
+            }
+        }
+    }
+
+    // fold the four row-lanes of the warp, then the eight warps through shared memory
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            float v = acc[m][j] - zc[m];
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            acc[m][j] = v;
+        }
+    }
+    const uint32_t col = blockIdx.x * kTileCols + threadIdx.x;
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+        __syncthreads();
+        if (r == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4 *>(&red[warp][c8 * 32 + j]) =
+                    make_float4(acc[m][j], acc[m][j + 1], acc[m][j + 2], acc[m][j + 3]);
+        }
+        __syncthreads();
+        if ((uint32_t)m < mrows && col < N) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) v += red[w][threadIdx.x];
+            dst[((size_t)blockIdx.y * M + m0 + m) * N + col] = v;
+        }
+    }
+}
+
+__global__ void int4_reduce_kernel(const float *__restrict__ part, float *__restrict__ out,
+                                   uint32_t splits, size_t mn)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= mn) return;
+    float v = 0.f;
+    for (uint32_t s = 0; s < splits; s++) v += part[(size_t)s * mn + i];
+    out[i] = v;
+}
+
+// Any shape: one thread per output, flat weight index, groups that straddle rows and a partial
+// last word included (quant/int4.go:67-80).  Slow; it exists so that no shape is refused.
+__global__ void int4_generic_kernel(const float *__restrict__ a, const uint32_t *__restrict__ bq,
+                                    const __half *__restrict__ bs, const __half *__restrict__ bz,
+                                    float *__restrict__ out, uint32_t M, uint32_t N, uint32_t K)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)M * N) return;
+    uint32_t m = (uint32_t)(i / N), n = (uint32_t)(i % N);
+    float acc = 0.f;
+    for (uint32_t k = 0; k < K; k++) {
+        size_t w = (size_t)k * N + n;
+        uint32_t code = (bq[w / 8] >> (4 * (w % 8))) & 0xFu;
+        float s = __half2float(bs[w / kGroup]), z = __half2float(bz[w / kGroup]);
+        float wv = s == 0.f ? z : ((float)code - z) * s;
+        acc = fmaf(a[(size_t)m * K + k], wv, acc);
+    }
+    out[i] = acc;
+}
+
+struct Int4Plan { bool fast; uint32_t tiles, splits, kc; size_t ws; };
+
+static Int4Plan plan_int4(uint32_t M, uint32_t N, uint32_t K)
+{
+    Int4Plan p{};
+    p.fast = (N % kGroup == 0) && N > 0 && K > 0;
+    if (!p.fast) return p;
+    p.tiles = (N + kTileCols - 1) / kTileCols;
+    uint32_t target = 3u * (uint32_t)sm_count();
+    uint32_t splits = (target + p.tiles - 1) / p.tiles;
+    uint32_t max_splits = (K + kRowsPerStep - 1) / kRowsPerStep;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    p.kc = ((K + splits - 1) / splits + kRowsPerStep - 1) / kRowsPerStep * kRowsPerStep;
+    p.splits = (K + p.kc - 1) / p.kc;
+    p.ws = p.splits > 1 ? (size_t)p.splits * M * N * sizeof(float) : 0;
+    return p;
+}
+
+template <int MR>
+static void run_gemv(const Launch &l, const Int4Plan &p, float *dst, uint32_t M, uint32_t N,
+                     uint32_t K, uint32_t m0, uint32_t mrows)
+{
+    dim3 grid(p.tiles, p.splits);
+    int4_gemv_kernel<MR><<<grid, kThreads, 0, l.stream>>>(
+        ptr<const float>(l, 0), ptr<const uint4>(l, 1), ptr<const __half>(l, 2),
+        ptr<const __half>(l, 3), dst, M, N, K, p.kc, m0, mrows);
+}
+
+static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint32_t K)
+{
+    if (N == 0 || K == 0 || M == 0) return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u", name, M, N, K);
+    Int4Plan p = plan_int4(M, N, K);
+    if (l.query_ws) { l.ws_need = p.ws; return AB_OK; }
+
+    uint64_t weights = (uint64_t)K * N;
+    if (l.len[0] < (uint64_t)M * K || l.len[1] < (weights + 7) / 8 ||
+        l.len[2] < (weights + kGroup - 1) / kGroup || l.len[3] < (weights + kGroup - 1) / kGroup ||
+        l.len[4] < (uint64_t)M * N)
+        return fail(AB_ERR_INVALID,
+                    "%s: M=%u N=%u K=%u needs a[%llu] bq[%llu] bs/bz[%llu] out[%llu]; the lengths "
+                    "block says %u %u %u %u %u",
+                    name, M, N, K, (unsigned long long)M * K, (unsigned long long)(weights + 7) / 8,
+                    (unsigned long long)(weights + kGroup - 1) / kGroup, (unsigned long long)M * N,
+                    l.len[0], l.len[1], l.len[2], l.len[3], l.len[4]);
+    float *out = ptr<float>(l, 4);
+    if (!p.fast) {
+        size_t mn = (size_t)M * N;
+        int4_generic_kernel<<<(unsigned)((mn + 127) / 128), 128, 0, l.stream>>>(
+            ptr<const float>(l, 0), ptr<const uint32_t>(l, 1), ptr<const __half>(l, 2),
+            ptr<const __half>(l, 3), out, M, N, K);
+        note_selection("%s: generic kernel, N=%u is not a multiple of %u", name, N, kGroup);
+        return check_cuda(cudaGetLastError(), name);
+    }
+    if (p.ws > l.ws_bytes || (p.ws && !l.ws))
+        return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, p.ws,
+                    l.ws_bytes);
+    float *dst = p.splits > 1 ? reinterpret_cast<float *>(l.ws) : out;
+    for (uint32_t m0 = 0; m0 < M;) {
+        uint32_t left = M - m0;
+        if (left >= 4) { run_gemv<4>(l, p, dst, M, N, K, m0, 4); m0 += 4; }
+        else if (left >= 2) { run_gemv<2>(l, p, dst, M, N, K, m0, 2); m0 += 2; }
+        else { run_gemv<1>(l, p, dst, M, N, K, m0, 1); m0 += 1; }
+    }
+    if (p.splits > 1) {
+        size_t mn = (size_t)M * N;
+        int4_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, l.stream>>>(dst, out, p.splits, mn);
+    }
+    note_selection("%s: streaming row kernel, %u column tiles x %u K splits of %u rows, %u row(s) "
+                   "of activations per pass", name, p.tiles, p.splits, p.kc, M >= 4 ? 4 : M);
+    return check_cuda(cudaGetLastError(), name);
+}
+
+int launch_quant_matvec_int4(Launch &l)
+{   // GEMMDims{M,N,K}; the reference's matvec leaves M zero (tensor/int4.go:131-133)
+    uint32_t N = u32_at(l.u, 4), K = u32_at(l.u, 8);
+    return launch_int4(l, "QuantMatVecInt4", 1, N, K);
+}
+
+int launch_quant_matmul_int4(Launch &l)
+{
+    uint32_t M = u32_at(l.u, 0), N = u32_at(l.u, 4), K = u32_at(l.u, 8);
+    return launch_int4(l, "QuantMatMulInt4", M, N, K);
+}
+
+}  // namespace ab

@@ -1,0 +1,236 @@
+/*
+ * accel_b200.h -- C ABI of libaccelb200.so, a Blackwell (sm_100a) backend for the quantized decode
+ * path of golang-design/accel.
+ *
+ * The entry points are what accel's cgo-free FFI would bind to put a CUDA backend behind
+ * `internal/driver` (the seam between accel's device layer and a backend): integer and pointer
+ * arguments only, at most 15 of them, no float passed by value, no callback, no exception or abort
+ * across the boundary.  Every function returns 0 or a negative ab_status unless stated otherwise;
+ * ab_last_error() gives the thread's last message.
+ *
+ * Reference citations (file:line) are paths inside the accel module.
+ */
+#ifndef ACCEL_B200_H
+#define ACCEL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AB_API __attribute__((visibility("default")))
+
+typedef enum ab_status {
+    AB_OK = 0,
+    AB_ERR_INVALID = -1,      /* an argument the call can check is wrong; nothing was launched   */
+    AB_ERR_UNSUPPORTED = -2,  /* no sm_100a kernel under that name: a pipeline-creation error,   */
+                              /* never a silent CPU run (pipeline.go:115-119)                    */
+    AB_ERR_OOM = -3,          /* allocation failed; the device is NOT lost                       */
+    AB_ERR_DEVICE_LOST = -4,  /* sticky: driver.ErrDeviceLost (internal/driver/plan.go:385-391)  */
+    AB_ERR_BUSY = -5,         /* a submission of this executable is still in flight              */
+    AB_ERR_CUDA = -6,         /* a CUDA call failed for a reason that is not loss                */
+    AB_ERR_NO_DEVICE = -7     /* no CUDA device or driver                                        */
+} ab_status;
+
+AB_API const char *ab_error_string(int code);
+AB_API const char *ab_last_error(void);              /* thread-local, valid until the next call */
+
+/* ------------------------------------------------------------------------------------------ */
+/* Adapter and device: driver.Adapter / driver.Device (internal/driver/driver.go:149-190)      */
+/* ------------------------------------------------------------------------------------------ */
+typedef struct ab_device ab_device;
+typedef struct ab_block ab_block;
+typedef struct ab_exec ab_exec;
+typedef struct ab_fence ab_fence;
+
+typedef struct ab_info {               /* driver.Info */
+    char name[128];
+    uint8_t token[16];                 /* Adapter.Token(): the device UUID */
+    uint64_t total_memory;
+    uint32_t sm_count;
+    uint32_t cc_major, cc_minor;
+    uint32_t max_shared_per_block;
+    uint32_t storage_offset_alignment; /* 256, as cuMemAlloc aligns (specs/060-cuda-bringup.md:318) */
+    uint32_t subgroup_size;            /* 32 */
+} ab_info;
+
+typedef struct ab_open_opts {
+    uint32_t struct_size;              /* sizeof(ab_open_opts): the struct may grow */
+    int32_t lose_at_submission;        /* >0: report loss at that submission, counted from 1, without
+                                          touching the GPU; mirrors CPUOptions.LoseAtSubmission
+                                          (accel.go:306-314).  0 = never */
+    int32_t use_graphs;                /* 1: replay each executable as a CUDA graph */
+} ab_open_opts;
+
+AB_API int ab_init(void);
+AB_API int ab_device_count(int *count);
+AB_API int ab_device_info(int ordinal, ab_info *out);
+AB_API int ab_open(int ordinal, const ab_open_opts *opts, ab_device **out);   /* Adapter.Open  */
+AB_API int ab_close(ab_device *dev);   /* refuses (AB_ERR_BUSY) while blocks or executables live */
+AB_API int ab_lost(ab_device *dev);    /* Device.Lost(): AB_OK or AB_ERR_DEVICE_LOST              */
+
+/* driver.Block (internal/driver/driver.go:219-238).  kind: */
+enum { AB_MEMORY_DEVICE = 0, AB_MEMORY_HOST_VISIBLE = 1 };
+AB_API int ab_alloc(ab_device *dev, int kind, size_t bytes, const char *label, ab_block **out);
+AB_API void *ab_block_bytes(ab_block *b);         /* Block.Bytes(): NULL for AB_MEMORY_DEVICE    */
+AB_API void *ab_block_device_ptr(ab_block *b);    /* the device address (no accel analogue)      */
+AB_API size_t ab_block_size(ab_block *b);
+AB_API int ab_block_write(ab_block *b, size_t off, const void *src, size_t n);  /* synchronous   */
+AB_API int ab_block_read(ab_block *b, size_t off, void *dst, size_t n);         /* synchronous   */
+AB_API int ab_block_free(ab_block *b);
+
+/* driver.KernelSupport.SupportsKernel (internal/driver/plan.go:424-428): AB_OK when this library
+ * holds an sm_100a kernel for the reference kernel of that name.  digest may be NULL. */
+AB_API int ab_supports_kernel(ab_device *dev, const char *name, const char *digest);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Plans: driver.Plan / PlanNode / Dispatch / Operand (internal/driver/plan.go:31-201)          */
+/* ------------------------------------------------------------------------------------------ */
+enum { AB_OP_COPY = 0, AB_OP_HOST_WRITE = 1, AB_OP_DISPATCH = 2 };
+
+typedef struct ab_operand {
+    ab_block *block;     /* a fixed block, or NULL when `slot` names a rebindable slot */
+    uint32_t slot;       /* 1-based, as accel numbers slots; 0 = none */
+    uint32_t _pad;
+    uint64_t offset;     /* bytes; a multiple of 256 for a dispatch binding */
+    uint64_t size;       /* bytes; a whole number of elements */
+} ab_operand;
+
+typedef struct ab_node {
+    int32_t op;
+    int32_t barrier_before;        /* accepted and ignored: one in-order stream orders every node */
+    /* AB_OP_DISPATCH */
+    const char *kernel;            /* the reference kernel's name, e.g. "QuantMatVecInt4" */
+    const char *digest;            /* optional */
+    uint32_t count[3];             /* the reference's workgroup count; ignored (the backend derives
+                                      its own launch geometry from uniforms and binding lengths) */
+    int32_t n_bindings;
+    const ab_operand *bindings;    /* positional, the reference kernel's binding order */
+    const void *uniform;           /* std140 bytes of uniform block 0, or NULL */
+    uint64_t uniform_bytes;
+    /* AB_OP_COPY: bindings[0] = source, bindings[1] = destination (n_bindings = 2).
+     * AB_OP_HOST_WRITE: bindings[0] = destination, payload below; the payload is copied into
+     * staging the executable owns at compile time and again on ab_exec_set_payload. */
+    const void *payload;
+    uint64_t payload_bytes;
+} ab_node;
+
+typedef struct ab_plan {
+    const ab_node *nodes;          /* a valid topological order */
+    int32_t n_nodes;
+    int32_t n_slots;
+    int32_t collect_timings;       /* Plan.CollectTimings: time each submission with an event pair */
+    int32_t _pad;
+} ab_plan;
+
+typedef struct ab_slot_binding { uint32_t slot; uint32_t _pad; ab_block *block; uint64_t offset; } ab_slot_binding;
+
+/* GraphCompiler.Compile / Executable (internal/driver/plan.go:360-400) */
+AB_API int ab_compile(ab_device *dev, const ab_plan *plan, ab_exec **out);
+AB_API int ab_exec_rebind(ab_exec *e, const ab_slot_binding *b, int n);            /* all or nothing */
+AB_API int ab_exec_set_uniform(ab_exec *e, int node, int index, const void *std140, size_t n);
+AB_API int ab_exec_set_payload(ab_exec *e, int node, const void *bytes, size_t n);
+AB_API int ab_exec_submit(ab_exec *e, ab_fence **out);     /* begins the work, does not wait */
+AB_API int ab_exec_close(ab_exec *e);
+AB_API int ab_fence_wait(ab_fence *f);                     /* AB_ERR_DEVICE_LOST on loss */
+AB_API int ab_fence_done(ab_fence *f);                     /* 1 done, 0 running, <0 error */
+AB_API uint64_t ab_fence_elapsed_ns(ab_fence *f);          /* driver.Timer.Elapsed; 0 if untimed */
+AB_API void ab_fence_free(ab_fence *f);
+
+/* ------------------------------------------------------------------------------------------ */
+/* One dispatch on caller-owned device memory and a caller-owned stream.                        */
+/* The argument convention is the one accel's GPU targets keep (specs/061-ptx-target.md:152-159,*/
+/* internal/mslabi/mslabi.go): binding k is a device pointer with its offset applied, the        */
+/* lengths block holds one u32 element count per binding, the uniform block arrives as std140   */
+/* bytes.  `stream` is a CUstream / cudaStream_t of the current device (NULL = legacy default). */
+/* Kernels that need scratch memory take it from `workspace`; ab_workspace_bytes says how much. */
+/* ------------------------------------------------------------------------------------------ */
+AB_API int ab_kernel_count(void);
+AB_API const char *ab_kernel_name(int index);
+AB_API int ab_workspace_bytes(const char *kernel, const uint32_t *lengths, int n_bindings,
+                              const void *uniform, size_t uniform_bytes, size_t *bytes);
+AB_API int ab_launch(const char *kernel, void *stream, void *const *bindings,
+                     const uint32_t *lengths, int n_bindings, const void *uniform,
+                     size_t uniform_bytes, void *workspace, size_t workspace_bytes);
+/* Which variant the last ab_launch of this thread selected, and why: Plan.Selections()
+ * (tensor/compile.go:36-41). */
+AB_API const char *ab_last_selection(void);
+
+/*
+ * Kernel names and their bindings (order is ABI) and uniform blocks (std140, little-endian):
+ *
+ *  QuantMatVecInt4   a f32[K], bq u32, bs f16, bz f16, out f32[N]          GEMMDims{M,N,K}@0,4,8 (16 B)
+ *                    internal/kernels/int4.go:60
+ *  QuantMatMulInt4   a f32[M*K], bq, bs, bz, out f32[M*N]                  GEMMDims
+ *                    internal/kernels/int4tiled.go:66
+ *  AttentionDecode, AttentionDecodeF16     q, k, v, lengths u32[1], out    AttnDims{QHeads,KVHeads,HeadDim,Scale f32}@0,4,8,12 (16 B)
+ *                    internal/kernels/attention.go:97,422
+ *  AttentionDecodePaged, AttentionDecodePagedF16   q, k, v, pages u32[P], lengths u32[1], out
+ *                    PagedDims{QHeads,KVHeads,HeadDim,Block,Scale f32}@0,4,8,12,16 (32 B)   internal/kernels/paged.go:47,362
+ *  AttentionDecodeBatched   q f32[B*qH*D], k f32, v f32, pages u32[B*MaxPages], lengths u32[B], out
+ *                    BatchedDims{Batch,QHeads,KVHeads,HeadDim,Block,MaxPages,Scale f32}@0..24 (32 B)   internal/kernels/batched.go:53
+ *  AttentionDecodeBatchedF16   the same over an f16 cache (no reference kernel of this name; the
+ *                    reference reaches an f16 cache for a batch through AttentionRaggedF16)
+ *  AttentionRagged, AttentionRaggedF16   q, k, v, pages, lengths u32[B], offsets u32[B+1], out
+ *                    RaggedDims = BatchedDims layout                          internal/kernels/ragged.go:61, raggedf16.go:43
+ *  GroupedMatVec     x f32[T*K], w f32[E*K*N], offsets u32[E+1], out f32[T*N]   GroupedDims{Experts,K,N}@0,4,8 (16 B)
+ *                    internal/kernels/grouped.go:49
+ *  GroupedMatMul     same bindings                                          GroupedTiledDims{Experts,Tokens,K,N}@0,4,8,12 (16 B)
+ *                    internal/kernels/groupedtiled.go:77
+ *  GroupedMatMulInt4 x f32[T*K], bq u32[E*ceil(KN/8)], bs f16[E*ceil(KN/128)], bz f16, offsets u32[E+1], out
+ *                    GroupedTiledDims.  No reference kernel: each expert's [K,N] matrix quantized
+ *                    on its own with quant.Int4Quantize, result = GroupedMatMul over the dequantized
+ *                    weights.
+ *  SegmentOffsets    counts u32[R], offsets u32[R+1]                        SegmentDims{Rows}@0 (16 B)   internal/kernels/segment.go:40
+ *  ScatterRows, ScatterRowsF16   rows, ids u32, state                        RowParams{Rows,Width,Capacity}@0,4,8 (16 B)
+ *                    internal/kernels/elementwise.go:182,221
+ *  GatherRows, GatherRowsF16     table, ids u32, out f32                     RowParams   internal/kernels/elementwise.go:118,133
+ *  RMSNorm           x, w, out                                              RowDims{Rows,Width,Eps f32}@0,4,8 (16 B)   internal/kernels/norm.go:46
+ *  RoPE              positions u32[rows], inout f32                          RoPEParams{Rows,Width,RotaryDim,Base f32}@0,4,8,12 (16 B)
+ *                    internal/kernels/elementwise.go:267
+ *  SwiGLU, ElemAdd   a, b, out                                               none   internal/kernels/elementwise.go:85,22
+ *  SampleArgmax      logits f32[rows*vocab], out u32[rows]                   SampleDims{Vocab,Rows}@0,4 (16 B)   internal/kernels/sample.go:50
+ *  CastF32ToF16, CastF16ToF32    in, out                                     none   internal/kernels/cast.go:30,38
+ *  Int4Quantize      w f32[n], packed u32, scales f16, zeros f16            none.  quant.Int4Quantize
+ *                    (quant/int4.go:71) run on the device, bit-identical to the host routine.
+ */
+
+/* ------------------------------------------------------------------------------------------ */
+/* Host-side pieces of the path                                                                 */
+/* ------------------------------------------------------------------------------------------ */
+/* quant.Int4Quantize / Int4Nibble / Int4Dequantize (quant/int4.go:71-175).  packed holds
+ * ceil(n/8) words, scales and zeros ceil(n/128) f16 bit patterns each. */
+AB_API int ab_int4_quantize(const float *w, size_t n, uint32_t *packed, uint16_t *scales,
+                            uint16_t *zeros);
+AB_API uint32_t ab_int4_nibble(const uint32_t *packed, size_t i);
+AB_API int ab_int4_dequantize(const uint32_t *packed, const uint16_t *scales,
+                              const uint16_t *zeros, size_t n, float *out);
+/* accel.ToFloat16 / Float16.F32 (internal/kernel/narrow.go:67-140) */
+AB_API uint16_t ab_f32_to_f16(const float *x);     /* by pointer: no float crosses by value */
+AB_API void ab_f16_to_f32(uint16_t h, float *out);
+
+/* tensor.BlockPool (tensor/blockpool.go:46-133).  Thread-safe. */
+typedef struct ab_blockpool ab_blockpool;
+AB_API int ab_blockpool_new(int blocks, int positions_per_block, ab_blockpool **out);
+AB_API void ab_blockpool_close(ab_blockpool *p);
+AB_API int ab_blockpool_block_size(ab_blockpool *p);
+AB_API int ab_blockpool_available(ab_blockpool *p);
+/* Grow: `pages` holds n_pages entries and has room for ceil(n/block); returns the new count
+ * (>= n_pages) or a negative status; the pool never evicts (AB_ERR_OOM). */
+AB_API int ab_blockpool_grow(ab_blockpool *p, uint32_t *pages, int n_pages, int n_positions);
+/* Free: returns AB_OK, or AB_ERR_INVALID when any page was already free (the others are freed). */
+AB_API int ab_blockpool_free(ab_blockpool *p, const uint32_t *pages, int n_pages);
+AB_API int ab_blockpool_positions(ab_blockpool *p, int n_pages);
+
+/* Group-aligned column split of an int4 [K,N] matrix for tensor-parallel sharding: shard r of
+ * `parts` owns columns [begin, end), both multiples of 128, so each shard's codes, scales and
+ * zeros are bit-identical to the same columns of the unsharded matrix. */
+AB_API int ab_int4_column_split(uint32_t n_cols, int parts, int rank, uint32_t *begin,
+                                uint32_t *end);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ACCEL_B200_H */

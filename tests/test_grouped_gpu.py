@@ -1,0 +1,111 @@
+"""Parity of the grouped (per-expert) products with the oracle, through the C ABI, on a B200.
+Tolerance: 1e-3 relative, f32 accumulate; the int4 form is checked against the composition
+dequantize-per-expert -> grouped product, which is its definition (no reference kernel exists)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as orc
+from accel_b200 import tensor as T
+from util import GEMM_TOL, assert_close, normal
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(a):
+    if a.dtype == np.uint32:
+        return torch.from_numpy(a.view(np.int32)).to(DEV)
+    return torch.from_numpy(a).to(DEV)
+
+
+def fixture(E, K, N, counts):
+    # internal/kernels/grouped_test.go:17-41
+    off = orc.segment_offsets(np.array(counts, np.uint32))
+    tokens = int(off[-1])
+    x = np.sin(np.arange(tokens * K) * 0.23).astype(np.float32).reshape(tokens, K)
+    base = np.cos(np.arange(K * N) * 0.17).astype(np.float32)
+    w = np.stack([base * np.float32(e + 1) for e in range(E)]).reshape(E, K, N)
+    return x, w, off, tokens
+
+
+@pytest.mark.parametrize("E,K,N,counts", [(3, 64, 5, [2, 1, 3]), (4, 64, 3, [2, 0, 2, 0]),
+                                          (2, 64, 2, [1, 1]), (3, 64, 256, [130, 0, 7]),
+                                          (5, 48, 132, [9, 300, 0, 1, 128])])
+def test_reference_fixtures(E, K, N, counts):
+    x, w, off, tokens = fixture(E, K, N, counts)
+    c = dev(np.array(counts, np.uint32))
+    assert np.array_equal(T.segment_offsets(c).cpu().numpy().view(np.uint32), off)
+    want = orc.grouped_matmul(x, w, off, tokens, E, K, N)
+    mm = T.grouped_matmul(dev(x), dev(w), c).cpu().numpy()
+    mv = T.grouped_matvec(dev(x), dev(w), c).cpu().numpy()
+    assert_close(mm, want, GEMM_TOL, "GroupedMatMul")
+    assert_close(mv, orc.grouped_matvec(x, w, off, tokens, E, K, N), GEMM_TOL, "GroupedMatVec")
+
+
+def test_padding_rows_and_clamp():
+    # grouped.go:72-77 (zeros), groupedtiled.go:87-91,96-133 (untouched; clamp to Tokens)
+    E, K, N = 2, 64, 8
+    x, w, off, tokens = fixture(E, K, N, [2, 1])
+    xpad = np.concatenate([x, np.ones((2, K), np.float32)])
+    c = dev(np.array([2, 1], np.uint32))
+    mv = T.grouped_matvec(dev(xpad), dev(w), c).cpu().numpy()
+    assert np.all(mv[tokens:] == 0)
+    out = torch.full((tokens + 2, N), 7.0, device=DEV)
+    T.grouped_matmul(dev(xpad), dev(w), c, out=out)
+    assert torch.all(out[tokens:] == 7.0) and not torch.any(out[:tokens] == 7.0)
+    big = dev(np.array([2, 9], np.uint32))            # claims eleven rows; three exist
+    out = torch.full((tokens, N), 7.0, device=DEV)
+    T.grouped_matmul(dev(x), dev(w), big, out=out)
+    want = orc.grouped_matmul(x, w, np.array([0, 2, 11], np.uint32), tokens, E, K, N)
+    assert_close(out.cpu().numpy(), want, GEMM_TOL, "clamped")
+
+
+def test_moe_shape_reduced_against_the_oracle():
+    # eight experts, seeded multinomial counts, d=4096 contracting into a 1024-column slice of the
+    # expert FFN: the full 14336 columns are the same kernel over more column tiles
+    E, K, N, rows = 8, 4096, 1024, 512
+    rng = np.random.default_rng(5)
+    counts = rng.multinomial(rows, np.ones(E) / E).astype(np.uint32)
+    x = normal(6, (rows, K))
+    w = normal(7, (E, K, N), 0.02)
+    off = orc.segment_offsets(counts)
+    want = orc.grouped_matmul(x, w, off, rows, E, K, N)
+    got = T.grouped_matmul(dev(x), dev(w), dev(counts)).cpu().numpy()
+    assert_close(got, want, GEMM_TOL, "MoE slice")
+
+
+def test_int4_grouped_is_the_composition():
+    E, K, N, rows = 4, 256, 384, 200
+    rng = np.random.default_rng(8)
+    counts = np.array([70, 0, 129, 1], np.uint32)
+    x = normal(9, (rows, K))
+    w = normal(10, (E, K, N), 0.02)
+    planes = [orc.int4_quantize(w[e]) for e in range(E)]
+    back = np.stack([orc.int4_dequantize(*planes[e], K * N).reshape(K, N) for e in range(E)])
+    q = T.Int4(dev(np.concatenate([p[0] for p in planes])),
+               torch.from_numpy(np.concatenate([p[1] for p in planes]).view(np.float16)).to(DEV),
+               torch.from_numpy(np.concatenate([p[2] for p in planes]).view(np.float16)).to(DEV),
+               E * K * N)
+    off = orc.segment_offsets(counts)
+    want = orc.grouped_matmul(x, back, off, rows, E, K, N)
+    got = T.grouped_matmul_int4(dev(x), q, E, dev(counts)).cpu().numpy()
+    assert_close(got, want, GEMM_TOL, "int4 grouped")
+
+
+def test_refusals():
+    x = torch.zeros(4, 8, device=DEV)
+    w = torch.zeros(2, 8, 3, device=DEV)
+    c = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(T.Refused, match="counts is nil"):
+        T.grouped_matmul(x, w, None)
+    with pytest.raises(T.Refused, match="reads f32"):
+        T.grouped_matmul(x.half(), w, c)
+    with pytest.raises(T.Refused, match=r"\[tokens, K\]"):
+        T.grouped_matmul(x[0], w, c)
+    with pytest.raises(T.Refused, match="one matrix per expert"):
+        T.grouped_matmul(x, w[0], c)
+    with pytest.raises(T.Refused, match="same width"):
+        T.grouped_matmul(torch.zeros(4, 9, device=DEV), w, c)
+    with pytest.raises(T.Refused, match="one token count per expert"):
+        T.grouped_matvec(x, w, torch.zeros(3, dtype=torch.int32, device=DEV))
