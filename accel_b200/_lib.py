@@ -104,6 +104,7 @@ SYMBOLS = [
                                      C.POINTER(C.c_size_t)]),
     ("ab_launch", C.c_int, [C.c_char_p, _P, _P, _P, C.c_int, _P, C.c_size_t, _P, C.c_size_t]),
     ("ab_last_selection", C.c_char_p, []),
+    ("ab_launch_count", C.c_uint64, []),
     ("ab_int4_quantize", C.c_int, [_P, C.c_size_t, _P, _P, _P]),
     ("ab_int4_nibble", C.c_uint32, [_P, C.c_size_t]),
     ("ab_int4_dequantize", C.c_int, [_P, _P, _P, C.c_size_t, _P]),

@@ -63,6 +63,9 @@ int check_cuda(cudaError_t e, const char *what)
     return fail(AB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 int sm_count()
 {
     static std::mutex mu;
@@ -108,6 +111,7 @@ static const KernelEntry kKernels[] = {
     {"CastF32ToF16", 2, 0, launch_cast_f32_to_f16},
     {"CastF16ToF32", 2, 0, launch_cast_f16_to_f32},
     {"Int4Quantize", 4, 0, launch_int4_quantize},
+    {"DecodeStepInputs", 7, 32, launch_decode_step_inputs},
 };
 static constexpr int kKernelCount = (int)(sizeof(kKernels) / sizeof(kKernels[0]));
 
@@ -320,6 +324,7 @@ const char *ab_error_string(int code)
 
 const char *ab_last_error(void) { return g_err; }
 const char *ab_last_selection(void) { return g_sel; }
+uint64_t ab_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int ab_kernel_count(void) { return kKernelCount; }
 const char *ab_kernel_name(int i) { return (i >= 0 && i < kKernelCount) ? kKernels[i].name : nullptr; }

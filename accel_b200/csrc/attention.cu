@@ -282,14 +282,14 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
     const int G = (group == 2 || group == 4 || group == 8) ? (int)group : 1;
     dim3 grid(p.parts, G == 1 ? p.q_heads : p.kv_heads, p.rows);
     switch (G) {
-    case 1: attn_partition_kernel<T, 1><<<grid, kAttnThreads, 0, l.stream>>>(p); break;
-    case 2: attn_partition_kernel<T, 2><<<grid, kAttnThreads, 0, l.stream>>>(p); break;
-    case 4: attn_partition_kernel<T, 4><<<grid, kAttnThreads, 0, l.stream>>>(p); break;
-    default: attn_partition_kernel<T, 8><<<grid, kAttnThreads, 0, l.stream>>>(p); break;
+    case 1: attn_partition_kernel<T, 1><<<grid, kAttnThreads, 0, l.stream>>>(p); count_launch(); break;
+    case 2: attn_partition_kernel<T, 2><<<grid, kAttnThreads, 0, l.stream>>>(p); count_launch(); break;
+    case 4: attn_partition_kernel<T, 4><<<grid, kAttnThreads, 0, l.stream>>>(p); count_launch(); break;
+    default: attn_partition_kernel<T, 8><<<grid, kAttnThreads, 0, l.stream>>>(p); count_launch(); break;
     }
     if (p.parts > 1) {
         dim3 cgrid(p.q_heads, p.rows);
-        attn_combine_kernel<<<cgrid, 128, 0, l.stream>>>(p);
+        attn_combine_kernel<<<cgrid, 128, 0, l.stream>>>(p); count_launch();
     }
     note_selection("%s: split-K decode, %u partition(s) of %d positions, %u query head(s) sharing "
                    "each K/V read, %u row(s)", name, p.parts, kPartition, group, p.rows);

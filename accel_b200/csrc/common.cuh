@@ -37,6 +37,7 @@ int fail(int code, const char *fmt, ...);          // records the thread's last 
 void note_selection(const char *fmt, ...);         // records which variant a launch selected
 int check_cuda(cudaError_t e, const char *what);   // maps a CUDA error to an ab_status
 int sm_count();                                    // SMs of the current device (cached)
+void count_launch();                               // one more kernel launch issued by this library
 
 inline uint32_t u32_at(const uint8_t *u, size_t off) { uint32_t v; memcpy(&v, u + off, 4); return v; }
 inline float f32_at(const uint8_t *u, size_t off) { float v; memcpy(&v, u + off, 4); return v; }
@@ -44,6 +45,12 @@ inline float f32_at(const uint8_t *u, size_t off) { float v; memcpy(&v, u + off,
 template <typename T> inline T *ptr(const Launch &l, int i) { return reinterpret_cast<T *>(l.b[i]); }
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// the tensor-core int4 kernel for small batches (int4_mma.cu), driven by the int4 launcher
+struct Int4MmaPlan { bool ok; uint32_t groups, splits, kc; size_t ws; };
+Int4MmaPlan plan_int4_mma(uint32_t M, uint32_t N, uint32_t K);
+int run_int4_mma(const Launch &l, const Int4MmaPlan &p, float *part, float *out, uint32_t M, uint32_t N,
+                 uint32_t K);
 
 // launchers, one per reference kernel name (defined beside their kernels)
 int launch_quant_matvec_int4(Launch &);
@@ -72,6 +79,7 @@ int launch_sample_argmax(Launch &);
 int launch_cast_f32_to_f16(Launch &);
 int launch_cast_f16_to_f32(Launch &);
 int launch_int4_quantize(Launch &);
+int launch_decode_step_inputs(Launch &);
 
 // f32 -> f16 with the reference's rule: round to nearest even, except that every magnitude below
 // 2^-24 becomes a signed zero (internal/kernel/narrow.go:82-83); IEEE rounds (2^-25, 2^-24) up.

@@ -180,16 +180,16 @@ static int run_grouped(Launch &l, GroupedParams &p, bool int4, bool zero_tail, u
     bool fast = p.K % BK == 0 && (int4 ? p.N % kGroup == 0 : p.N % 4 == 0);
     if (fast) {
         dim3 grid((p.N + BN - 1) / BN, (p.tokens + BM - 1) / BM + p.experts);
-        if (int4) grouped_tile_kernel<true><<<grid, GT, 0, l.stream>>>(p);
-        else grouped_tile_kernel<false><<<grid, GT, 0, l.stream>>>(p);
+        if (int4) { grouped_tile_kernel<true><<<grid, GT, 0, l.stream>>>(p); count_launch(); }
+        else { grouped_tile_kernel<false><<<grid, GT, 0, l.stream>>>(p); count_launch(); }
     } else {
         size_t total = (size_t)p.tokens * p.N;
         unsigned blocks = (unsigned)((total + 127) / 128);
-        if (int4) grouped_generic_kernel<true><<<blocks, 128, 0, l.stream>>>(p, p.tokens);
-        else grouped_generic_kernel<false><<<blocks, 128, 0, l.stream>>>(p, p.tokens);
+        if (int4) { grouped_generic_kernel<true><<<blocks, 128, 0, l.stream>>>(p, p.tokens); count_launch(); }
+        else { grouped_generic_kernel<false><<<blocks, 128, 0, l.stream>>>(p, p.tokens); count_launch(); }
     }
     if (zero_tail)
-        grouped_zero_tail_kernel<<<64, 256, 0, l.stream>>>(p.out, p.offsets, p.experts, out_rows, p.N);
+        grouped_zero_tail_kernel<<<64, 256, 0, l.stream>>>(p.out, p.offsets, p.experts, out_rows, p.N); count_launch();
     note_selection("%s: %s, %u experts over %u rows", name,
                    fast ? "128x128 register-tiled kernel" : "generic kernel", p.experts, p.tokens);
     return check_cuda(cudaGetLastError(), name);
@@ -263,7 +263,7 @@ int launch_segment_offsets(Launch &l)
     if (l.len[0] < rows || l.len[1] < rows + 1)
         return fail(AB_ERR_INVALID, "SegmentOffsets: Rows=%u, counts[%u], offsets[%u]", rows,
                     l.len[0], l.len[1]);
-    segment_offsets_kernel<<<1, 32, 0, l.stream>>>(ptr<const uint32_t>(l, 0), ptr<uint32_t>(l, 1), rows);
+    segment_offsets_kernel<<<1, 32, 0, l.stream>>>(ptr<const uint32_t>(l, 0), ptr<uint32_t>(l, 1), rows); count_launch();
     return check_cuda(cudaGetLastError(), "SegmentOffsets");
 }
 

@@ -203,14 +203,17 @@ static void run_gemv(const Launch &l, const Int4Plan &p, float *dst, uint32_t M,
     dim3 grid(p.tiles, p.splits);
     int4_gemv_kernel<MR><<<grid, kThreads, 0, l.stream>>>(
         ptr<const float>(l, 0), ptr<const uint4>(l, 1), ptr<const __half>(l, 2),
-        ptr<const __half>(l, 3), dst, M, N, K, p.kc, m0, mrows);
+        ptr<const __half>(l, 3), dst, M, N, K, p.kc, m0, mrows); count_launch();
 }
 
 static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint32_t K)
 {
     if (N == 0 || K == 0 || M == 0) return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u", name, M, N, K);
     Int4Plan p = plan_int4(M, N, K);
-    if (l.query_ws) { l.ws_need = p.ws; return AB_OK; }
+    // two or more rows of activations go to the tensor cores; one row stays on the CUDA cores
+    Int4MmaPlan mp = plan_int4_mma(M, N, K);
+    const bool use_mma = mp.ok && M >= 2;
+    if (l.query_ws) { l.ws_need = use_mma ? mp.ws : p.ws; return AB_OK; }
 
     uint64_t weights = (uint64_t)K * N;
     if (l.len[0] < (uint64_t)M * K || l.len[1] < (weights + 7) / 8 ||
@@ -227,8 +230,19 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
         size_t mn = (size_t)M * N;
         int4_generic_kernel<<<(unsigned)((mn + 127) / 128), 128, 0, l.stream>>>(
             ptr<const float>(l, 0), ptr<const uint32_t>(l, 1), ptr<const __half>(l, 2),
-            ptr<const __half>(l, 3), out, M, N, K);
+            ptr<const __half>(l, 3), out, M, N, K); count_launch();
         note_selection("%s: generic kernel, N=%u is not a multiple of %u", name, N, kGroup);
+        return check_cuda(cudaGetLastError(), name);
+    }
+    if (use_mma) {
+        if (mp.ws > l.ws_bytes || (mp.ws && !l.ws))
+            return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, mp.ws,
+                        l.ws_bytes);
+        int rc = run_int4_mma(l, mp, reinterpret_cast<float *>(l.ws), out, M, N, K);
+        if (rc) return rc;
+        note_selection("%s: tensor-core kernel (m16n8k16, f16 operands, f32 accumulate), %u column "
+                       "groups x %u K splits of %u rows, %u pass(es) of 16 activation rows", name,
+                       mp.groups, mp.splits, mp.kc, (M + 15) / 16);
         return check_cuda(cudaGetLastError(), name);
     }
     if (p.ws > l.ws_bytes || (p.ws && !l.ws))
@@ -243,7 +257,7 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     }
     if (p.splits > 1) {
         size_t mn = (size_t)M * N;
-        int4_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, l.stream>>>(dst, out, p.splits, mn);
+        int4_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, l.stream>>>(dst, out, p.splits, mn); count_launch();
     }
     note_selection("%s: streaming row kernel, %u column tiles x %u K splits of %u rows, %u row(s) "
                    "of activations per pass", name, p.tiles, p.splits, p.kc, M >= 4 ? 4 : M);

@@ -40,7 +40,7 @@ int launch_rmsnorm(Launch &l)
                     l.len[0], l.len[1], l.len[2]);
     if (rows == 0) return AB_OK;
     rmsnorm_kernel<<<rows, 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<const float>(l, 1),
-                                               ptr<float>(l, 2), width, eps);
+                                               ptr<float>(l, 2), width, eps); count_launch();
     return check_cuda(cudaGetLastError(), "RMSNorm");
 }
 
@@ -79,7 +79,7 @@ int launch_rope(Launch &l)
     size_t n = (size_t)rows * (rotary / 2);
     if (n == 0) return AB_OK;
     rope_kernel<<<blocks_for(n, 128), 128, 0, l.stream>>>(ptr<const uint32_t>(l, 0),
-                                                          ptr<float>(l, 1), rows, width, rotary, base);
+                                                          ptr<float>(l, 1), rows, width, rotary, base); count_launch();
     return check_cuda(cudaGetLastError(), "RoPE");
 }
 
@@ -105,8 +105,8 @@ static int elementwise3(Launch &l, bool swiglu, const char *name)
     if (l.len[0] < n || l.len[1] < n)
         return fail(AB_ERR_INVALID, "%s: out[%u] and inputs [%u] [%u]", name, l.len[2], l.len[0], l.len[1]);
     if (n == 0) return AB_OK;
-    if (swiglu) swiglu_kernel<<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<const float>(l, 1), ptr<float>(l, 2), n);
-    else add_kernel<<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<const float>(l, 1), ptr<float>(l, 2), n);
+    if (swiglu) { swiglu_kernel<<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<const float>(l, 1), ptr<float>(l, 2), n); count_launch(); }
+    else { add_kernel<<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<const float>(l, 1), ptr<float>(l, 2), n); count_launch(); }
     return check_cuda(cudaGetLastError(), name);
 }
 int launch_swiglu(Launch &l) { return elementwise3(l, true, "SwiGLU"); }
@@ -149,7 +149,7 @@ template <typename T> static int gather(Launch &l, const char *name)
                     name, rows, width, cap, l.len[0], l.len[1], l.len[2]);
     size_t n = (size_t)rows * width;
     if (n == 0) return AB_OK;
-    gather_rows_kernel<T><<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const T>(l, 0), ptr<const uint32_t>(l, 1), ptr<float>(l, 2), rows, width, cap);
+    gather_rows_kernel<T><<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const T>(l, 0), ptr<const uint32_t>(l, 1), ptr<float>(l, 2), rows, width, cap); count_launch();
     return check_cuda(cudaGetLastError(), name);
 }
 template <typename T> static int scatter(Launch &l, const char *name)
@@ -161,7 +161,7 @@ template <typename T> static int scatter(Launch &l, const char *name)
                     name, rows, width, cap, l.len[0], l.len[1], l.len[2]);
     size_t n = (size_t)rows * width;
     if (n == 0) return AB_OK;
-    scatter_rows_kernel<T><<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const T>(l, 0), ptr<const uint32_t>(l, 1), ptr<T>(l, 2), rows, width, cap);
+    scatter_rows_kernel<T><<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const T>(l, 0), ptr<const uint32_t>(l, 1), ptr<T>(l, 2), rows, width, cap); count_launch();
     return check_cuda(cudaGetLastError(), name);
 }
 int launch_gather_rows(Launch &l) { return gather<float>(l, "GatherRows"); }
@@ -205,7 +205,7 @@ int launch_sample_argmax(Launch &l)
     if (l.len[0] < (uint64_t)rows * vocab)
         return fail(AB_ERR_INVALID, "SampleArgmax: Vocab=%u rows=%u; logits[%u]", vocab, rows, l.len[0]);
     if (rows == 0) return AB_OK;
-    argmax_kernel<<<rows, 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<uint32_t>(l, 1), vocab);
+    argmax_kernel<<<rows, 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<uint32_t>(l, 1), vocab); count_launch();
     return check_cuda(cudaGetLastError(), "SampleArgmax");
 }
 
@@ -225,7 +225,7 @@ int launch_cast_f32_to_f16(Launch &l)
     if (l.query_ws) { l.ws_need = 0; return AB_OK; }
     size_t n = l.len[1];
     if (l.len[0] < n) return fail(AB_ERR_INVALID, "CastF32ToF16: in[%u] out[%u]", l.len[0], l.len[1]);
-    if (n) cast_f32_f16_kernel<<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<uint16_t>(l, 1), n);
+    if (n) { cast_f32_f16_kernel<<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<uint16_t>(l, 1), n); count_launch(); }
     return check_cuda(cudaGetLastError(), "CastF32ToF16");
 }
 int launch_cast_f16_to_f32(Launch &l)
@@ -233,8 +233,53 @@ int launch_cast_f16_to_f32(Launch &l)
     if (l.query_ws) { l.ws_need = 0; return AB_OK; }
     size_t n = l.len[1];
     if (l.len[0] < n) return fail(AB_ERR_INVALID, "CastF16ToF32: in[%u] out[%u]", l.len[0], l.len[1]);
-    if (n) cast_f16_f32_kernel<<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const __half>(l, 0), ptr<float>(l, 1), n);
+    if (n) { cast_f16_f32_kernel<<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const __half>(l, 0), ptr<float>(l, 1), n); count_launch(); }
     return check_cuda(cudaGetLastError(), "CastF16ToF32");
+}
+
+
+// ---------------------------------------------------------------- per-step inputs of a decode loop
+// What a caller's host loop writes before each step (docs/tutorial/11-batching-sequences.md:
+// 83-103), computed on the device so that a replayed step can feed the next one without a host
+// round trip: the sampled token becomes the input token, its position is the sequence's current
+// length, its cache slot is pages[s][pos / Block] * Block + pos % Block, and the length grows by one.
+__global__ void decode_step_inputs_kernel(const uint32_t *__restrict__ sampled,
+                                          const uint32_t *__restrict__ pages,
+                                          uint32_t *__restrict__ tokens, uint32_t *__restrict__ pos_q,
+                                          uint32_t *__restrict__ pos_k, uint32_t *__restrict__ slots,
+                                          uint32_t *__restrict__ lengths, uint32_t batch, uint32_t hq,
+                                          uint32_t hk, uint32_t block, uint32_t max_pages)
+{
+    const uint32_t s = blockIdx.x;
+    if (s >= batch) return;
+    const uint32_t pos = lengths[s];
+    for (uint32_t i = threadIdx.x; i < hq; i += blockDim.x) pos_q[s * hq + i] = pos;
+    for (uint32_t i = threadIdx.x; i < hk; i += blockDim.x) pos_k[s * hk + i] = pos;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        tokens[s] = sampled[s];
+        const uint32_t page = pos / block < max_pages ? pages[(size_t)s * max_pages + pos / block] : 0xffffffffu;
+        // past the page table's reach there is no slot: an id ScatterRows drops
+        slots[s] = page == 0xffffffffu ? 0xffffffffu : page * block + pos % block;
+        lengths[s] = pos + 1;
+    }
+}
+
+int launch_decode_step_inputs(Launch &l)
+{   // sampled, pages, tokens, pos_q, pos_k, slots, lengths; {Batch, QHeads, KVHeads, Block, MaxPages}
+    if (l.query_ws) { l.ws_need = 0; return AB_OK; }
+    uint32_t batch = u32_at(l.u, 0), hq = u32_at(l.u, 4), hk = u32_at(l.u, 8), block = u32_at(l.u, 12),
+             mp = u32_at(l.u, 16);
+    if (block == 0 || l.len[0] < batch || l.len[1] < (uint64_t)batch * mp || l.len[2] < batch ||
+        l.len[3] < (uint64_t)batch * hq || l.len[4] < (uint64_t)batch * hk || l.len[5] < batch ||
+        l.len[6] < batch)
+        return fail(AB_ERR_INVALID, "DecodeStepInputs: Batch=%u QHeads=%u KVHeads=%u Block=%u "
+                    "MaxPages=%u does not match the lengths block", batch, hq, hk, block, mp);
+    if (batch == 0) return AB_OK;
+    decode_step_inputs_kernel<<<batch, 64, 0, l.stream>>>(
+        ptr<const uint32_t>(l, 0), ptr<const uint32_t>(l, 1), ptr<uint32_t>(l, 2), ptr<uint32_t>(l, 3),
+        ptr<uint32_t>(l, 4), ptr<uint32_t>(l, 5), ptr<uint32_t>(l, 6), batch, hq, hk, block, mp); count_launch();
+    return check_cuda(cudaGetLastError(), "DecodeStepInputs");
 }
 
 // ---------------------------------------------------------------- quant.Int4Quantize on the device
@@ -302,7 +347,7 @@ int launch_int4_quantize(Launch &l)
                     "packed[%u] scales[%u] zeros[%u]", n, (n + 7) / 8, groups, l.len[1], l.len[2], l.len[3]);
     if (n == 0) return AB_OK;
     int4_quantize_kernel<<<blocks_for(groups, 8), 256, 0, l.stream>>>(
-        ptr<const float>(l, 0), n, ptr<uint32_t>(l, 1), ptr<uint16_t>(l, 2), ptr<uint16_t>(l, 3));
+        ptr<const float>(l, 0), n, ptr<uint32_t>(l, 1), ptr<uint16_t>(l, 2), ptr<uint16_t>(l, 3)); count_launch();
     return check_cuda(cudaGetLastError(), "Int4Quantize");
 }
 

@@ -1,0 +1,407 @@
+"""A Llama-style decode step built from the path's operators: what a caller of accel's tensor API
+records once and submits per token (docs/tutorial/09-a-decode-step.md, 11-batching-sequences.md),
+with every linear an int4 product and the KV cache paged.
+
+Per layer:  RMSNorm -> Int4MatMul x3 (q,k,v) -> RoPE(q), RoPE(k) -> ScatterRows(K), ScatterRows(V)
+            -> Attention (batched paged decode) -> Int4MatMul (wo) -> Add -> RMSNorm
+            -> Int4MatMul (gate), Int4MatMul (up) -> SwiGLU -> Int4MatMul (down) -> Add
+then        RMSNorm -> Int4MatMul (lm_head) -> Argmax.
+
+Every operator is one dispatch by reference kernel name through `ops.launch` (the C ABI's
+ab_launch); torch supplies device memory, streams, CUDA-graph capture and the NCCL process group.
+
+Tensor parallelism (one process per GPU): wq/wk/wv, gate/up and lm_head are split by output
+columns on 128-column group boundaries, so each shard's packing is bit-identical to the same
+columns of the unsharded matrix; heads and their KV cache follow the q/k/v split; wo and down are
+split by rows and their partial sums are all-reduced; the page table, lengths and norm gains are
+replicated.  The reference is single-device: sharding is an extension above the per-device plan."""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from . import runtime as rt
+from .blockpool import BlockPool
+from .quant import int4_column_split
+
+I32 = torch.int32
+
+
+@dataclass
+class ModelConfig:
+    layers: int = 32
+    d_model: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 32
+    head_dim: int = 128
+    ffn: int = 11008
+    vocab: int = 32000
+    eps: float = 1e-5
+    rope_base: float = 10000.0
+    block: int = 16               # positions per KV page
+    cache_dtype: torch.dtype = torch.float32
+
+    def int4_weights(self) -> int:
+        d, f = self.d_model, self.ffn
+        qkv = d * self.n_heads * self.head_dim + 2 * d * self.n_kv_heads * self.head_dim
+        per_layer = qkv + self.n_heads * self.head_dim * d + 3 * d * f
+        return self.layers * per_layer + d * self.vocab
+
+
+@dataclass
+class Shard:
+    """What rank `rank` of `tp` owns."""
+    tp: int
+    rank: int
+    heads: range          # query heads
+    kv_heads: range
+    ffn: range            # columns of gate/up = rows of down
+    vocab: range
+
+    @staticmethod
+    def plan(cfg: ModelConfig, tp: int, rank: int) -> "Shard":
+        if cfg.n_heads % tp or cfg.n_kv_heads % tp:
+            raise ValueError(f"{cfg.n_heads} query and {cfg.n_kv_heads} KV heads do not divide over {tp} ranks")
+        if (cfg.n_heads // tp * cfg.head_dim) % 128:
+            raise ValueError("a rank's q/k/v columns must be whole 128-column groups")
+        hq, hk = cfg.n_heads // tp, cfg.n_kv_heads // tp
+        fb, fe = int4_column_split(cfg.ffn, tp, rank)
+        vb, ve = int4_column_split(cfg.vocab, tp, rank)
+        return Shard(tp, rank, range(rank * hq, (rank + 1) * hq), range(rank * hk, (rank + 1) * hk),
+                     range(fb, fe), range(vb, ve))
+
+
+@dataclass
+class Int4Matrix:
+    codes: torch.Tensor      # int32 view of the u32 words, flat [K*N/8]
+    scales: torch.Tensor     # f16 flat [K*N/128]
+    zeros: torch.Tensor
+    K: int
+    N: int
+
+    @property
+    def nbytes(self) -> int:
+        return self.codes.numel() * 4 + self.scales.numel() * 2 + self.zeros.numel() * 2
+
+
+def shard_columns(codes, scales, zeros, K, N, b, e) -> Int4Matrix:
+    """Columns [b, e) of a packed [K, N] matrix; b and e are multiples of 128."""
+    c = codes.view(K, N // 8)[:, b // 8:e // 8].contiguous().view(-1)
+    s = scales.view(K, N // 128)[:, b // 128:e // 128].contiguous().view(-1)
+    z = zeros.view(K, N // 128)[:, b // 128:e // 128].contiguous().view(-1)
+    return Int4Matrix(c, s, z, K, e - b)
+
+
+def shard_rows(codes, scales, zeros, K, N, b, e) -> Int4Matrix:
+    """Rows [b, e) of a packed [K, N] matrix with N a multiple of 128 (groups never cross a row)."""
+    c = codes.view(K, N // 8)[b:e].contiguous().view(-1)
+    s = scales.view(K, N // 128)[b:e].contiguous().view(-1)
+    z = zeros.view(K, N // 128)[b:e].contiguous().view(-1)
+    return Int4Matrix(c, s, z, e - b, N)
+
+
+class Layer:
+    __slots__ = ("g1", "g2", "wq", "wk", "wv", "wo", "wg", "wu", "wd")
+
+
+class DecodeModel:
+    """Random-init weights of the given shape, quantized with quant.Int4Quantize.  Every rank draws
+    the full matrix from the same seed, quantizes it and keeps its shard, so the shards of all
+    ranks together are bit-for-bit the unsharded model."""
+
+    def __init__(self, cfg: ModelConfig, shard: Shard, device, seed: int = 1234, ops=rt,
+                 quantize=None, std: float = 0.02):
+        self.cfg, self.shard, self.device = cfg, shard, torch.device(device)
+        d, D = cfg.d_model, cfg.head_dim
+        gen = torch.Generator(device=self.device)
+        if quantize is None:
+            from .quant import int4_quantize_device as quantize
+        self._quantize = quantize
+
+        def full(k, n, tag):
+            gen.manual_seed(seed * 1000003 + tag)
+            w = torch.randn((k, n), generator=gen, device=self.device, dtype=torch.float32) * std
+            return self._quantize(w)
+
+        def gain(tag):
+            gen.manual_seed(seed * 1000003 + tag)
+            return 1.0 + 0.1 * torch.randn(d, generator=gen, device=self.device, dtype=torch.float32)
+
+        hq, hk, fr, vr = shard.heads, shard.kv_heads, shard.ffn, shard.vocab
+        self.layers: List[Layer] = []
+        for li in range(cfg.layers):
+            L = Layer()
+            t = 100 * li
+            L.g1, L.g2 = gain(t + 1), gain(t + 2)
+            nq, nkv = cfg.n_heads * D, cfg.n_kv_heads * D
+            L.wq = shard_columns(*full(d, nq, t + 3), d, nq, hq.start * D, hq.stop * D)
+            L.wk = shard_columns(*full(d, nkv, t + 4), d, nkv, hk.start * D, hk.stop * D)
+            L.wv = shard_columns(*full(d, nkv, t + 5), d, nkv, hk.start * D, hk.stop * D)
+            L.wo = shard_rows(*full(nq, d, t + 6), nq, d, hq.start * D, hq.stop * D)
+            L.wg = shard_columns(*full(d, cfg.ffn, t + 7), d, cfg.ffn, fr.start, fr.stop)
+            L.wu = shard_columns(*full(d, cfg.ffn, t + 8), d, cfg.ffn, fr.start, fr.stop)
+            L.wd = shard_rows(*full(cfg.ffn, d, t + 9), cfg.ffn, d, fr.start, fr.stop)
+            self.layers.append(L)
+        self.g_final = gain(999001)
+        self.lm_head = shard_columns(*full(d, cfg.vocab, 999002), d, cfg.vocab, vr.start, vr.stop)
+        gen.manual_seed(seed * 1000003 + 999003)
+        self.embedding = torch.randn((cfg.vocab, d), generator=gen, device=self.device,
+                                     dtype=torch.float32)
+
+    def int4_bytes(self) -> int:
+        n = self.lm_head.nbytes
+        for L in self.layers:
+            n += sum(m.nbytes for m in (L.wq, L.wk, L.wv, L.wo, L.wg, L.wu, L.wd))
+        return n
+
+
+def _u(fmt, *v) -> bytes:
+    return struct.pack(fmt, *v)
+
+
+class DecodeEngine:
+    """The recorded step and its state: per-layer paged K/V pools (one state per layer, as the
+    reference sizes them), the page table from a BlockPool, and static buffers so the step can be
+    captured once as a CUDA graph and replayed."""
+
+    def __init__(self, model: DecodeModel, batch: int, max_context: int, ops=rt, group=None):
+        cfg, sh = model.cfg, model.shard
+        self.model, self.cfg, self.shard, self.ops, self.group = model, cfg, sh, ops, group
+        self.batch = batch
+        dev = model.device
+        self.dev = dev
+        B, d, D = batch, cfg.d_model, cfg.head_dim
+        self.hq, self.hk = len(sh.heads), len(sh.kv_heads)
+        self.max_pages = (max_context + cfg.block - 1) // cfg.block
+        pool_blocks = B * self.max_pages
+        self.capacity = pool_blocks * cfg.block
+        self.pool = BlockPool(pool_blocks, cfg.block)
+        self.page_rows: List[List[int]] = [[] for _ in range(B)]
+        self.lengths_host = np.zeros(B, np.int64)
+        kv_shape = (self.capacity, self.hk, D)
+        self.k_cache = [torch.zeros(kv_shape, dtype=cfg.cache_dtype, device=dev) for _ in range(cfg.layers)]
+        self.v_cache = [torch.zeros(kv_shape, dtype=cfg.cache_dtype, device=dev) for _ in range(cfg.layers)]
+
+        z = lambda *s, dt=torch.float32: torch.zeros(s, dtype=dt, device=dev)
+        # per-step inputs (the small buffers a caller writes each step: token, q and k positions,
+        # slot, length; docs/tutorial/11-batching-sequences.md:83-103).  They are views of one
+        # buffer, each starting on a 256-byte boundary, so one host-to-device copy fills them all.
+        sizes = [B, B * self.hq, B * self.hk, B, B]
+        starts, at = [], 0
+        for n in sizes:
+            starts.append(at)
+            at += (n + 63) // 64 * 64
+        self.inputs = z(at, dt=I32)
+        self._in_starts, self._in_sizes = starts, sizes
+        view = lambda i: self.inputs[starts[i]:starts[i] + sizes[i]]
+        self.tokens, self.pos_q, self.pos_k, self.slots = view(0), view(1), view(2), view(3)
+        self.lengths = view(4)               # length AFTER this step's token is appended
+        self.pages = z(B, self.max_pages, dt=I32)
+        # activations
+        self.x, self.h, self.x2 = z(B, d), z(B, d), z(B, d)
+        self.q, self.k, self.v = z(B, self.hq * D), z(B, self.hk * D), z(B, self.hk * D)
+        self.attn = z(B, self.hq * D)
+        self.proj = z(B, d)
+        self.gate, self.up, self.act = z(B, len(sh.ffn)), z(B, len(sh.ffn)), z(B, len(sh.ffn))
+        self.logits_local = z(B, len(sh.vocab))
+        self.logits = z(B, cfg.vocab) if sh.tp > 1 else self.logits_local
+        self.next_tokens = z(B, dt=I32)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_step = 0
+        self._pin = None
+
+    # ------------------------------------------------------------------ cache bookkeeping (host)
+    def reserve(self, seq: int, n_positions: int):
+        """Grow sequence `seq`'s page row to address n_positions (tensor.BlockPool.Grow)."""
+        self.page_rows[seq] = self.pool.grow(self.page_rows[seq], n_positions)
+
+    def upload_pages(self):
+        host = np.zeros((self.batch, self.max_pages), np.int32)
+        for s, row in enumerate(self.page_rows):
+            host[s, :len(row)] = row
+        self.pages.copy_(torch.from_numpy(host))
+
+    def fill_context(self, context: int, seed: int = 7):
+        """Stands in for a prefill: reserves pages for `context` positions per sequence and fills
+        those K/V rows with seeded N(0,1) values (f32 or f16 as the cache is)."""
+        for s in range(self.batch):
+            self.reserve(s, context)
+        self.upload_pages()
+        gen = torch.Generator(device=self.dev)
+        rows = torch.tensor([self.page_rows[s][j // self.cfg.block] * self.cfg.block + j % self.cfg.block
+                             for s in range(self.batch) for j in range(context)],
+                            dtype=torch.long, device=self.dev)
+        for li in range(self.cfg.layers):
+            for ci, cache in enumerate((self.k_cache[li], self.v_cache[li])):
+                gen.manual_seed(seed * 7919 + li * 2 + ci)
+                # every rank draws all KV heads and keeps its own, so shards agree with tp = 1
+                full = torch.randn((rows.numel(), self.cfg.n_kv_heads, self.cfg.head_dim),
+                                   generator=gen, device=self.dev, dtype=torch.float32)
+                part = full[:, self.shard.kv_heads.start:self.shard.kv_heads.stop]
+                cache[rows] = part.to(cache.dtype)
+        self.lengths_host[:] = context
+
+    def step_inputs_host(self, token_ids: np.ndarray) -> np.ndarray:
+        """The per-step host buffers for the CURRENT lengths, laid out as `self.inputs` is:
+        tokens | positions of q rows | positions of k rows | slots | lengths + 1."""
+        B, blk = self.batch, self.cfg.block
+        pos = self.lengths_host.astype(np.int64)
+        slots = np.empty(B, np.int64)
+        for s in range(B):
+            p = int(pos[s])
+            if p // blk >= len(self.page_rows[s]):
+                raise RuntimeError(f"sequence {s} has no page for position {p}; reserve() first")
+            slots[s] = self.page_rows[s][p // blk] * blk + p % blk
+        out = np.zeros(self.inputs.numel(), np.int32)
+        parts = [np.asarray(token_ids, np.int64), np.repeat(pos, self.hq), np.repeat(pos, self.hk),
+                 slots, pos + 1]
+        for st, part in zip(self._in_starts, parts):
+            out[st:st + part.size] = part
+        return out
+
+    def set_inputs(self, token_ids: np.ndarray):
+        """Writes the per-step inputs for the current lengths (synchronous; for setup and tests)."""
+        self.inputs.copy_(torch.from_numpy(self.step_inputs_host(token_ids)))
+
+    def advance_on_device(self):
+        """Feeds the step's sampled tokens back as the next step's inputs without leaving the
+        device: next position = current length, its slot from the page table, length + 1."""
+        self.ops.launch("DecodeStepInputs",
+                        [self.next_tokens, self.pages, self.tokens, self.pos_q, self.pos_k,
+                         self.slots, self.lengths],
+                        _u("<IIIIIIII", self.batch, self.hq, self.hk, self.cfg.block,
+                           self.max_pages, 0, 0, 0))
+        self.lengths_host += 1
+
+    # ------------------------------------------------------------------ the recorded step
+    def _launch(self, name, bindings, uniform=None):
+        self.ops.launch(name, bindings, uniform)
+        self._count += 1
+
+    def _linear(self, a, w: Int4Matrix, out):
+        M = a.shape[0]
+        self._launch("QuantMatMulInt4", [a, w.codes, w.scales, w.zeros, out],
+                     _u("<IIII", M, w.N, w.K, 0))
+
+    def _all_reduce(self, t):
+        if self.shard.tp > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, group=self.group)
+
+    def record_step(self):
+        """Issues one decode step on the current stream.  Reads tokens/pos/slots/lengths/pages,
+        appends this token's K/V, writes next_tokens."""
+        cfg, B, D, d = self.cfg, self.batch, self.cfg.head_dim, self.cfg.d_model
+        self._count = 0
+        count = getattr(self.ops, "launch_count", lambda: 0)
+        kernels0 = count()
+        L = self._launch
+        scale = float(np.float32(1.0) / np.float32(np.sqrt(D)))
+        L("GatherRows", [self.model.embedding, self.tokens, self.x], _u("<IIII", B, d, cfg.vocab, 0))
+        x, x2 = self.x, self.x2
+        for li, lay in enumerate(self.model.layers):
+            L("RMSNorm", [x, lay.g1, self.h], _u("<IIfI", B, d, cfg.eps, 0))
+            self._linear(self.h, lay.wq, self.q)
+            self._linear(self.h, lay.wk, self.k)
+            self._linear(self.h, lay.wv, self.v)
+            L("RoPE", [self.pos_q, self.q], _u("<IIIf", B * self.hq, D, D, cfg.rope_base))
+            L("RoPE", [self.pos_k, self.k], _u("<IIIf", B * self.hk, D, D, cfg.rope_base))
+            f16 = cfg.cache_dtype == torch.float16
+            krows, vrows = self.k, self.v
+            if f16:
+                krows, vrows = self._k16, self._v16
+                L("CastF32ToF16", [self.k, krows])
+                L("CastF32ToF16", [self.v, vrows])
+            rp = _u("<IIII", B, self.hk * D, self.capacity, 0)
+            L("ScatterRowsF16" if f16 else "ScatterRows", [krows, self.slots, self.k_cache[li]], rp)
+            L("ScatterRowsF16" if f16 else "ScatterRows", [vrows, self.slots, self.v_cache[li]], rp)
+            L("AttentionDecodeBatchedF16" if f16 else "AttentionDecodeBatched",
+              [self.q, self.k_cache[li], self.v_cache[li], self.pages, self.lengths, self.attn],
+              _u("<IIIIIIfI", B, self.hq, self.hk, D, cfg.block, self.max_pages, scale, 0))
+            self._linear(self.attn, lay.wo, self.proj)
+            self._all_reduce(self.proj)
+            L("ElemAdd", [x, self.proj, x2])
+            x, x2 = x2, x
+            L("RMSNorm", [x, lay.g2, self.h], _u("<IIfI", B, d, cfg.eps, 0))
+            self._linear(self.h, lay.wg, self.gate)
+            self._linear(self.h, lay.wu, self.up)
+            L("SwiGLU", [self.gate, self.up, self.act])
+            self._linear(self.act, lay.wd, self.proj)
+            self._all_reduce(self.proj)
+            L("ElemAdd", [x, self.proj, x2])
+            x, x2 = x2, x
+        L("RMSNorm", [x, self.model.g_final, self.h], _u("<IIfI", B, d, cfg.eps, 0))
+        self._linear(self.h, self.model.lm_head, self.logits_local)
+        if self.shard.tp > 1:
+            # each rank owns a column range of the vocabulary: place it in a zeroed full-width
+            # buffer and sum across ranks (x + 0 = x exactly), then every rank takes the argmax
+            self.logits.zero_()
+            self.logits[:, self.shard.vocab.start:self.shard.vocab.stop].copy_(self.logits_local)
+            self._all_reduce(self.logits)
+        L("SampleArgmax", [self.logits, self.next_tokens], _u("<IIII", cfg.vocab, B, 0, 0))
+        self.launches_per_step = self._count                      # dispatches by kernel name
+        self.kernel_launches_per_step = count() - kernels0        # CUDA kernels they launched
+        self._final_x = x
+
+    def prepare(self):
+        if self.cfg.cache_dtype == torch.float16 and not hasattr(self, "_k16"):
+            self._k16 = torch.zeros_like(self.k, dtype=torch.float16)
+            self._v16 = torch.zeros_like(self.v, dtype=torch.float16)
+
+    def capture(self, warmup: int = 2):
+        """Runs the step eagerly (which also sizes the kernels' workspaces), then captures it."""
+        self.prepare()
+        s = torch.cuda.Stream(device=self.dev)
+        s.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(s):
+            for _ in range(warmup):
+                self.record_step()
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                self.record_step()
+        torch.cuda.current_stream(self.dev).wait_stream(s)
+        self.graph = g
+        self._graph_stream = s
+
+    def run_step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.prepare()
+            self.record_step()
+
+    # ------------------------------------------------------------------ the caller's loop
+    def step(self, token_ids: np.ndarray) -> np.ndarray:
+        """One end-to-end decode step as a caller makes it: host token ids in, host next-token ids
+        out.  The per-step inputs are staged in pinned memory and copied to the device, the
+        recorded step runs, and the argmax ids are read back."""
+        packed = self.step_inputs_host(token_ids)
+        if self._pin is None:
+            self._pin = torch.empty(packed.size, dtype=I32).pin_memory()
+            self._out_pin = torch.empty(self.batch, dtype=I32).pin_memory()
+        self._pin.numpy()[:] = packed
+        self.inputs.copy_(self._pin, non_blocking=True)
+        self.run_step()
+        self._out_pin.copy_(self.next_tokens, non_blocking=True)
+        torch.cuda.current_stream(self.dev).synchronize()
+        self.lengths_host += 1
+        return self._out_pin.numpy().copy()
+
+    @property
+    def h2d_bytes_per_step(self) -> int:
+        return 4 * self.inputs.numel()
+
+    @property
+    def d2h_bytes_per_step(self) -> int:
+        return 4 * self.batch
+
+    def kv_bytes_read_per_step(self) -> int:
+        """Algorithmic K/V bytes one step reads on this rank: every cached position of every
+        sequence, K and V, once per KV head, in every layer."""
+        e = 2 if self.cfg.cache_dtype == torch.float16 else 4
+        return int(self.cfg.layers * 2 * self.hk * self.cfg.head_dim * e * (self.lengths_host + 1).sum())

@@ -122,3 +122,8 @@ def launch(name: str, bindings: Sequence[torch.Tensor], uniform: Optional[bytes]
 
 def last_selection() -> str:
     return _lib.lib().ab_last_selection().decode()
+
+
+def launch_count() -> int:
+    """Kernels this library has launched (or recorded into a capture) so far in this process."""
+    return int(_lib.lib().ab_launch_count())

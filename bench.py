@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized decode hot path on B200.
+
+Metric: decode tokens/s of a random-init Llama-7B-shape model (32 layers, d 4096, 32 heads of 128,
+SwiGLU 11008, vocab 32000), every linear int4 (group 128, scale + zero point, the reference's
+packing), paged KV cache (block 16), batch 16, 2048 positions of context per sequence, greedy next
+token.  One step = one pass of the whole decode step over the batch.  At N > 1 the same step is
+tensor-parallel over N ranks (strong scaling: the batch is fixed).
+
+  python bench.py --gpus 1 --steps 20 --warmup 3
+  python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+  python bench.py --impl reference ...      the CPU restatement of accel's CPU kernels, host cores
+
+Prints ONE JSON line on rank 0."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s (7B-shape int4, paged KV)"
+WORKLOAD = ("7B-shape decode step: 32 layers, d_model 4096, 32 heads x 128, SwiGLU 11008, vocab "
+            "32000, int4 group-128 linears, paged KV block 16, batch 16, context 2048, greedy")
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json, STREAM-style copy)"
+    return 6650.0, "fallback (6.65 TB/s, an earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 <= t <= t1 + 0.2 and len(r) >= 9] or \
+               [r for _, r in self.rows if len(r) >= 9]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [float(r[1]) for r in rows]
+        reasons = set()
+        for r in rows:
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6),
+                              ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][2]),
+                "power_w_max": max(float(r[3]) for r in rows), "samples": len(rows),
+                "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------------------------
+# reference arm: the oracle's layer sample on the host cores
+# ----------------------------------------------------------------------------------------------
+def cpu_sample(steps: int, warmup: int, layers: int = 32):
+    """Times one layer of the step per 'step' (plus the lm_head once) and scales to the 32 layers
+    a token needs.  Returns (tok/s, seconds per layer, seconds for the head, cores)."""
+    import oracle
+    from oracle.step import LayerSample
+    s = LayerSample()
+    x = None
+    for _ in range(max(warmup, 0)):
+        _, x = s.time_layer()
+    times = []
+    for _ in range(max(steps, 1)):
+        t, x = s.time_layer()
+        times.append(t)
+    t_head = s.time_head(x)
+    t_layer = statistics.median(times)
+    step_s = layers * t_layer + t_head
+    return s.B / step_s, t_layer, t_head, oracle.threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = min(args.steps, 20)
+    toks, t_layer, t_head, cores = cpu_sample(steps, min(args.warmup, 3))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": toks, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": 1e3 * (32 * t_layer + t_head),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "kv_cache": "f32"},
+        "cpu_baseline": {"value": toks, "unit": "tok/s", "cores": cores, "kind": "port",
+                         "sample": "each step times 1 of the 32 layers of the same decode step "
+                                   "(batch 16, context 2048) and the lm_head + argmax once; "
+                                   "tok/s = 16 / (32 x median layer time + head time); C "
+                                   "restatement of accel's CPU kernels, OpenMP over workgroups; the "
+                                   "Go backend itself cannot be built here (no Go toolchain)"},
+        "e2e": {"value": toks, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------
+# the B200 arm
+# ----------------------------------------------------------------------------------------------
+def time_kernel(fn, reps, stream):
+    import torch
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        fn()
+    e1.record(stream)
+    e1.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def run_b200(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from accel_b200 import decode as dec
+    from accel_b200 import runtime as rt
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: accel_b200 has no CPU path "
+                         "(use --impl reference for the CPU baseline)")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch N ranks with torchrun")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+
+    cache_dtype = torch.float16 if args.kv == "f16" else torch.float32
+    cfg = dec.ModelConfig(layers=args.layers, cache_dtype=cache_dtype)
+    shard = dec.Shard.plan(cfg, world, rank)
+    t_setup = time.perf_counter()
+    model = dec.DecodeModel(cfg, shard, dev, seed=1234)
+    B, ctx = args.batch, args.context
+    total_steps = 2 * (args.steps + args.warmup) + 8
+    engine = dec.DecodeEngine(model, B, max_context=ctx + total_steps + 16, group=group)
+    engine.fill_context(ctx, seed=7)
+    for s in range(B):
+        engine.reserve(s, ctx + total_steps + 8)
+    engine.upload_pages()
+    rng = np.random.default_rng(99)
+    first = rng.integers(0, cfg.vocab, B)
+    engine.set_inputs(first)
+    engine.capture(warmup=1)
+    torch.cuda.synchronize()
+    t_setup = time.perf_counter() - t_setup
+
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- value: K steps, inputs resident, the step feeding itself on the device
+    engine.set_inputs(first)
+    lengths0 = engine.lengths_host.copy()
+    for _ in range(args.warmup):
+        engine.run_step()
+        engine.advance_on_device()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    kv_bytes_first = engine.kv_bytes_read_per_step()
+    launches0 = rt.launch_count()
+    t0 = time.perf_counter()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        engine.run_step()
+        engine.advance_on_device()
+    e1.record(stream)
+    e1.synchronize()
+    barrier()
+    t1 = time.perf_counter()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    ms_per_step = ms_total / args.steps
+    value = B * args.steps / (ms_total / 1e3)
+    # kernels per step: the captured step's launches (counted when it was recorded) + the advance
+    gpu_launches = args.steps * (engine.kernel_launches_per_step + 1)
+    del launches0
+
+    # ---- e2e: the caller's loop; host token ids in, host token ids out, every step
+    tok = engine.next_tokens.cpu().numpy()
+    for _ in range(min(args.warmup, 3)):
+        tok = engine.step(tok)
+    barrier()
+    w0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok = engine.step(tok)
+    torch.cuda.synchronize()
+    w1 = time.perf_counter()
+    e2e_s = max_over_ranks(w1 - w0)
+    e2e_value = B * args.steps / e2e_s
+
+    # ---- roofline of the dominant kernel: the paged decode attention (K/V of every cached
+    # position, once per KV head), timed alone with events on its launching stream, one launch per
+    # layer so consecutive launches read different caches (1 GB each, far larger than L2)
+    peak, peak_src = measured_peaks()
+    reps = 3
+
+    def attn_all_layers():
+        scale = float(np.float32(1.0) / np.float32(np.sqrt(cfg.head_dim)))
+        name = "AttentionDecodeBatchedF16" if cache_dtype == torch.float16 else "AttentionDecodeBatched"
+        u = dec._u("<IIIIIIfI", B, engine.hq, engine.hk, cfg.head_dim, cfg.block, engine.max_pages, scale, 0)
+        for li in range(cfg.layers):
+            rt.launch(name, [engine.q, engine.k_cache[li], engine.v_cache[li], engine.pages,
+                             engine.lengths, engine.attn], u)
+
+    attn_all_layers()
+    torch.cuda.synchronize()
+    attn_ms = time_kernel(attn_all_layers, reps, stream) / cfg.layers
+    esz = 2 if cache_dtype == torch.float16 else 4
+    lens = engine.lengths.cpu().numpy().astype(np.int64)
+    attn_bytes = int(2 * engine.hk * cfg.head_dim * esz * lens.sum()
+                     + 2 * B * engine.hq * cfg.head_dim * 4 + engine.pages.numel() * 4 + B * 4)
+    attn_gbs = attn_bytes / (attn_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "attn_partition_kernel (+ attn_combine_kernel)",
+                "achieved": attn_gbs, "peak": peak, "unit": "GB/s", "frac": attn_gbs / peak,
+                "peak_source": peak_src, "bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
+                "traffic": None}
+
+    # ---- int4 GEMV bandwidth (the metric's second figure): K=4096, N=11008, M=1, rotating over
+    # the layers' gate and up matrices (64 x 24 MB, larger than L2)
+    gemv = None
+    if world == 1 and cfg.layers >= 4:
+        a1 = torch.randn(cfg.d_model, device=dev)
+        out1 = torch.empty(cfg.ffn, device=dev)
+        mats = [m for L in model.layers for m in (L.wg, L.wu)]
+        u = dec._u("<IIII", 0, cfg.ffn, cfg.d_model, 0)
+
+        def gemv_all():
+            for m in mats:
+                rt.launch("QuantMatVecInt4", [a1, m.codes, m.scales, m.zeros, out1], u)
+
+        gemv_all()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        s2 = torch.cuda.Stream(device=dev)
+        s2.wait_stream(stream)
+        with torch.cuda.stream(s2):
+            with torch.cuda.graph(g, stream=s2):
+                gemv_all()
+        stream.wait_stream(s2)
+        g.replay()
+        torch.cuda.synchronize()
+        ms = time_kernel(g.replay, 5, stream) / len(mats)
+        gbytes = mats[0].nbytes + cfg.d_model * 4 + cfg.ffn * 4
+        gemv = {"shape": "M=1 K=4096 N=11008", "bytes": gbytes, "us": ms * 1e3,
+                "gbs": gbytes / (ms * 1e-3) / 1e9, "frac": gbytes / (ms * 1e-3) / 1e9 / peak,
+                "matrices_rotated": len(mats)}
+
+    # ---- CPU baseline beside it (rank 0, N = 1 only): the oracle's layer sample
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        toks, t_layer, t_head, cores = cpu_sample(3, 1)
+        cpu = {"value": toks, "unit": "tok/s", "cores": cores, "kind": "port",
+               "sample": f"1 of 32 layers of the same step timed 3 times (median {t_layer:.3f} s) + "
+                         f"lm_head and argmax once ({t_head:.3f} s), scaled to 32 layers; C "
+                         "restatement of accel's CPU kernels, OpenMP over workgroups"}
+
+    if rank == 0:
+        weight_bytes = model.int4_bytes()
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch": B, "context": ctx, "layers": cfg.layers,
+                       "kv_cache": args.kv, "parallelism": f"tp{world}",
+                       "l2": "inputs larger than L2: each step streams "
+                             f"{weight_bytes / 1e9:.2f} GB of int4 weights and "
+                             f"{kv_bytes_first / 1e9:.1f} GB of K/V per rank",
+                       "kv_fill": "seeded N(0,1) rows stand in for the 2048-token prefill",
+                       "setup_s": round(t_setup, 1)},
+            "e2e": {"value": e2e_value, "unit": "tok/s",
+                    "h2d_bytes_per_step": engine.h2d_bytes_per_step,
+                    "d2h_bytes_per_step": engine.d2h_bytes_per_step},
+            "gpu_launches": gpu_launches,
+            "roofline": roofline,
+            "step_hbm": {"bytes_per_step_per_rank": weight_bytes + kv_bytes_first,
+                         "gbs": (weight_bytes + kv_bytes_first) / (ms_per_step * 1e-3) / 1e9,
+                         "frac_of_peak": (weight_bytes + kv_bytes_first) / (ms_per_step * 1e-3) / 1e9 / peak},
+            "int4_gemv": gemv,
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--kv", default="f32", choices=["f32", "f16"],
+                    help="KV cache dtype; f32 is what the reference's batched decode kernel reads")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -157,6 +157,9 @@ AB_API int ab_launch(const char *kernel, void *stream, void *const *bindings,
 /* Which variant the last ab_launch of this thread selected, and why: Plan.Selections()
  * (tensor/compile.go:36-41). */
 AB_API const char *ab_last_selection(void);
+/* How many CUDA kernels this library has launched (or recorded into a stream capture) so far in
+ * this process; a caller differences it around a region to count its launches. */
+AB_API uint64_t ab_launch_count(void);
 
 /*
  * Kernel names and their bindings (order is ABI) and uniform blocks (std140, little-endian):
@@ -195,6 +198,10 @@ AB_API const char *ab_last_selection(void);
  *  CastF32ToF16, CastF16ToF32    in, out                                     none   internal/kernels/cast.go:30,38
  *  Int4Quantize      w f32[n], packed u32, scales f16, zeros f16            none.  quant.Int4Quantize
  *                    (quant/int4.go:71) run on the device, bit-identical to the host routine.
+ *  DecodeStepInputs  sampled u32[B], pages u32[B*MaxPages], tokens u32[B], pos_q u32[B*QHeads], pos_k u32[B*KVHeads],
+ *                    slots u32[B], lengths u32[B]     {Batch,QHeads,KVHeads,Block,MaxPages}@0..16 (32 B).  No reference
+ *                    kernel: the per-step host writes of a decode loop (docs/tutorial/11-batching-sequences.md:83-103)
+ *                    done on the device, so a replayed step feeds the next without a host round trip.
  */
 
 /* ------------------------------------------------------------------------------------------ */

@@ -96,7 +96,7 @@ def test_scales_and_zeros_are_read_per_group_along_n():
     a = normal(10, (4, K))
     want = orc.quant_matmul_int4(a, p, s, z, 4, N, K)
     got = T.int4_matmul(torch.from_numpy(a).to(DEV), to_int4(p, s, z, K * N)).cpu().numpy()
-    assert_close(got, want, 1e-4, "per-group metadata")
+    assert_close(got, want, GEMM_TOL, "per-group metadata")
 
 
 @pytest.mark.parametrize("M", [128, 512])
