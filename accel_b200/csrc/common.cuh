@@ -49,8 +49,7 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 // the tensor-core int4 kernel for small batches (int4_mma.cu), driven by the int4 launcher
 struct Int4MmaPlan { bool ok; uint32_t groups, splits, kc; size_t ws; };
 Int4MmaPlan plan_int4_mma(uint32_t M, uint32_t N, uint32_t K);
-int run_int4_mma(const Launch &l, const Int4MmaPlan &p, float *part, float *out, uint32_t M, uint32_t N,
-                 uint32_t K);
+int run_int4_mma(const Launch &l, const Int4MmaPlan &p, float *dst, uint32_t M, uint32_t N, uint32_t K);
 
 // launchers, one per reference kernel name (defined beside their kernels)
 int launch_quant_matvec_int4(Launch &);

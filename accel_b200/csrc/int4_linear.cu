@@ -147,14 +147,28 @@ int4_gemv_kernel(const float *__restrict__ a, const uint4 *__restrict__ bq,
     }
 }
 
+// Sums the K-split partials [splits][mn] into out: one float4 of outputs per thread, the splits'
+// loads independent of one another.
 __global__ void int4_reduce_kernel(const float *__restrict__ part, float *__restrict__ out,
                                    uint32_t splits, size_t mn)
 {
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= mn) return;
-    float v = 0.f;
-    for (uint32_t s = 0; s < splits; s++) v += part[(size_t)s * mn + i];
-    out[i] = v;
+    if (i + 4 <= mn) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (uint32_t s = 0; s < splits; s++) {
+            const float4 x = __ldcs(reinterpret_cast<const float4 *>(part + (size_t)s * mn + i));
+            v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+        }
+        *reinterpret_cast<float4 *>(out + i) = v;
+    } else {
+        for (size_t j = i; j < mn; j++) {
+            float v = 0.f;
+            for (uint32_t s = 0; s < splits; s++) v += part[(size_t)s * mn + j];
+            out[j] = v;
+        }
+    }
 }
 
 // Any shape: one thread per output, flat weight index, groups that straddle rows and a partial
@@ -238,8 +252,13 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
         if (mp.ws > l.ws_bytes || (mp.ws && !l.ws))
             return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, mp.ws,
                         l.ws_bytes);
-        int rc = run_int4_mma(l, mp, reinterpret_cast<float *>(l.ws), out, M, N, K);
+        float *mdst = mp.splits > 1 ? reinterpret_cast<float *>(l.ws) : out;
+        int rc = run_int4_mma(l, mp, mdst, M, N, K);
         if (rc) return rc;
+        if (mp.splits > 1) {
+            size_t mn = (size_t)M * N;
+            int4_reduce_kernel<<<(unsigned)((mn / 4 + 128) / 128), 128, 0, l.stream>>>(mdst, out, mp.splits, mn); count_launch();
+        }
         note_selection("%s: tensor-core kernel (m16n8k16, f16 operands, f32 accumulate), %u column "
                        "groups x %u K splits of %u rows, %u pass(es) of 16 activation rows", name,
                        mp.groups, mp.splits, mp.kc, (M + 15) / 16);
@@ -257,7 +276,7 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     }
     if (p.splits > 1) {
         size_t mn = (size_t)M * N;
-        int4_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, l.stream>>>(dst, out, p.splits, mn); count_launch();
+        int4_reduce_kernel<<<(unsigned)((mn / 4 + 128) / 128), 128, 0, l.stream>>>(dst, out, p.splits, mn); count_launch();
     }
     note_selection("%s: streaming row kernel, %u column tiles x %u K splits of %u rows, %u row(s) "
                    "of activations per pass", name, p.tiles, p.splits, p.kc, M >= 4 ? 4 : M);

@@ -211,6 +211,8 @@ class DecodeEngine:
         self.logits = z(B, cfg.vocab) if sh.tp > 1 else self.logits_local
         self.next_tokens = z(B, dt=I32)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.overlap = True          # run the independent linears of a layer side by side
+        self._side: List[torch.cuda.Stream] = []
         self.launches_per_step = 0
         self._pin = None
 
@@ -287,6 +289,25 @@ class DecodeEngine:
         self._launch("QuantMatMulInt4", [a, w.codes, w.scales, w.zeros, out],
                      _u("<IIII", M, w.N, w.K, 0))
 
+    def _parallel(self, branches):
+        """Runs independent branches of the step on side streams (graph branches once captured);
+        the first stays on the current stream.  On a CPU stand-in they simply run in order."""
+        if self.dev.type != "cuda" or not self.overlap or len(branches) == 1:
+            for fn in branches:
+                fn()
+            return
+        main = torch.cuda.current_stream(self.dev)
+        while len(self._side) < len(branches) - 1:
+            self._side.append(torch.cuda.Stream(device=self.dev))
+        for st in self._side[:len(branches) - 1]:
+            st.wait_stream(main)
+        branches[0]()
+        for fn, st in zip(branches[1:], self._side):
+            with torch.cuda.stream(st):
+                fn()
+        for st in self._side[:len(branches) - 1]:
+            main.wait_stream(st)
+
     def _all_reduce(self, t):
         if self.shard.tp > 1:
             import torch.distributed as dist
@@ -305,20 +326,33 @@ class DecodeEngine:
         x, x2 = self.x, self.x2
         for li, lay in enumerate(self.model.layers):
             L("RMSNorm", [x, lay.g1, self.h], _u("<IIfI", B, d, cfg.eps, 0))
-            self._linear(self.h, lay.wq, self.q)
-            self._linear(self.h, lay.wk, self.k)
-            self._linear(self.h, lay.wv, self.v)
-            L("RoPE", [self.pos_q, self.q], _u("<IIIf", B * self.hq, D, D, cfg.rope_base))
-            L("RoPE", [self.pos_k, self.k], _u("<IIIf", B * self.hk, D, D, cfg.rope_base))
             f16 = cfg.cache_dtype == torch.float16
-            krows, vrows = self.k, self.v
-            if f16:
-                krows, vrows = self._k16, self._v16
-                L("CastF32ToF16", [self.k, krows])
-                L("CastF32ToF16", [self.v, vrows])
             rp = _u("<IIII", B, self.hk * D, self.capacity, 0)
-            L("ScatterRowsF16" if f16 else "ScatterRows", [krows, self.slots, self.k_cache[li]], rp)
-            L("ScatterRowsF16" if f16 else "ScatterRows", [vrows, self.slots, self.v_cache[li]], rp)
+            scatter = "ScatterRowsF16" if f16 else "ScatterRows"
+
+            def q_branch():
+                self._linear(self.h, lay.wq, self.q)
+                L("RoPE", [self.pos_q, self.q], _u("<IIIf", B * self.hq, D, D, cfg.rope_base))
+
+            def k_branch():
+                self._linear(self.h, lay.wk, self.k)
+                L("RoPE", [self.pos_k, self.k], _u("<IIIf", B * self.hk, D, D, cfg.rope_base))
+                krows = self.k
+                if f16:
+                    krows = self._k16
+                    L("CastF32ToF16", [self.k, krows])
+                L(scatter, [krows, self.slots, self.k_cache[li]], rp)
+
+            def v_branch():
+                self._linear(self.h, lay.wv, self.v)
+                vrows = self.v
+                if f16:
+                    vrows = self._v16
+                    L("CastF32ToF16", [self.v, vrows])
+                L(scatter, [vrows, self.slots, self.v_cache[li]], rp)
+
+            # q, k and v depend only on h: three branches that may run side by side
+            self._parallel([q_branch, k_branch, v_branch])
             L("AttentionDecodeBatchedF16" if f16 else "AttentionDecodeBatched",
               [self.q, self.k_cache[li], self.v_cache[li], self.pages, self.lengths, self.attn],
               _u("<IIIIIIfI", B, self.hq, self.hk, D, cfg.block, self.max_pages, scale, 0))
@@ -327,8 +361,8 @@ class DecodeEngine:
             L("ElemAdd", [x, self.proj, x2])
             x, x2 = x2, x
             L("RMSNorm", [x, lay.g2, self.h], _u("<IIfI", B, d, cfg.eps, 0))
-            self._linear(self.h, lay.wg, self.gate)
-            self._linear(self.h, lay.wu, self.up)
+            self._parallel([lambda: self._linear(self.h, lay.wg, self.gate),
+                            lambda: self._linear(self.h, lay.wu, self.up)])
             L("SwiGLU", [self.gate, self.up, self.act])
             self._linear(self.act, lay.wd, self.proj)
             self._all_reduce(self.proj)
