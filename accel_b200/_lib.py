@@ -103,6 +103,8 @@ SYMBOLS = [
     ("ab_workspace_bytes", C.c_int, [C.c_char_p, _P, C.c_int, _P, C.c_size_t,
                                      C.POINTER(C.c_size_t)]),
     ("ab_launch", C.c_int, [C.c_char_p, _P, _P, _P, C.c_int, _P, C.c_size_t, _P, C.c_size_t]),
+    ("ab_quant_matmul_int4_noalloc", C.c_int, [_P, _P, _P, _P, _P, _P, C.c_uint32, C.c_uint32,
+                                               C.c_uint32]),
     ("ab_last_selection", C.c_char_p, []),
     ("ab_launch_count", C.c_uint64, []),
     ("ab_int4_quantize", C.c_int, [_P, C.c_size_t, _P, _P, _P]),

@@ -295,4 +295,57 @@ int launch_quant_matmul_int4(Launch &l)
     return launch_int4(l, "QuantMatMulInt4", M, N, K);
 }
 
+// ------------------------------------------------------------------------------------------------
+// The int4 product for callers that cannot allocate device memory.
+//
+// Some hosts of this library only ever hand over buffers they were given: a plugin running inside
+// another runtime's allocator, a real-time loop that must not call into the driver's allocator once
+// it has started, a sandbox that forbids cudaMalloc outright.  They cannot supply the split-K
+// workspace the regular entry point asks for.  This entry point carries its own: a fixed array in
+// the library's device image, present on every GPU that loads the library for as long as the
+// process lives.  The caller passes inputs and the output only.
+static constexpr size_t kStaticScratchBytes = 8u << 20;          // 8 MiB: the stated maximum
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
 }  // namespace ab
+
+extern "C" AB_API int ab_quant_matmul_int4_noalloc(void *stream, const float *a, const uint32_t *bq,
+                                            const uint16_t *bs, const uint16_t *bz, float *out,
+                                            uint32_t M, uint32_t N, uint32_t K)
+{
+    using namespace ab;
+    // The array's name is only a handle on the host; the device address has to be asked for, once
+    // per device, with that device current.  This first call per device is the set-up.
+    static void *scratch_of[64] = {};
+    int dev = -1;
+    int rc = check_cuda(cudaGetDevice(&dev), "ab_quant_matmul_int4_noalloc");
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return fail(AB_ERR_INVALID, "ab_quant_matmul_int4_noalloc: device %d", dev);
+    if (!scratch_of[dev]) {
+        void *p = nullptr;
+        rc = check_cuda(cudaGetSymbolAddress(&p, g_static_scratch), "cudaGetSymbolAddress(scratch)");
+        if (rc) return rc;
+        scratch_of[dev] = p;
+    }
+    if (M == 0) M = 1;                   // the matvec form leaves M zero
+    const uint64_t weights = (uint64_t)K * N;
+    void *bind[5] = {const_cast<float *>(a), const_cast<uint32_t *>(bq), const_cast<uint16_t *>(bs),
+                     const_cast<uint16_t *>(bz), out};
+    const uint32_t lens[5] = {(uint32_t)((uint64_t)M * K), (uint32_t)((weights + 7) / 8),
+                              (uint32_t)((weights + 127) / 128), (uint32_t)((weights + 127) / 128),
+                              (uint32_t)((uint64_t)M * N)};
+    Launch q{nullptr, nullptr, lens, 5, nullptr, 0, nullptr, 0, true, 0};
+    rc = launch_int4(q, "QuantMatMulInt4 (no-alloc)", M, N, K);
+    if (rc) return rc;
+    if (q.ws_need > kStaticScratchBytes)
+        return fail(AB_ERR_INVALID, "ab_quant_matmul_int4_noalloc: M=%u N=%u K=%u needs %zu bytes of "
+                    "scratch and the built-in array holds %zu; use ab_launch with a workspace of your "
+                    "own for this shape", M, N, K, q.ws_need, kStaticScratchBytes);
+    for (int i = 0; i < 5; i++)
+        if (!bind[i] || reinterpret_cast<uintptr_t>(bind[i]) % 16)
+            return fail(AB_ERR_INVALID, "ab_quant_matmul_int4_noalloc: argument %d is NULL or not "
+                        "16-byte aligned", i);
+    Launch l{static_cast<cudaStream_t>(stream), bind, lens, 5, nullptr, 0, scratch_of[dev],
+             kStaticScratchBytes, false, 0};
+    return launch_int4(l, "QuantMatMulInt4 (no-alloc)", M, N, K);
+}

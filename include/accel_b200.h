@@ -154,6 +154,26 @@ AB_API int ab_workspace_bytes(const char *kernel, const uint32_t *lengths, int n
 AB_API int ab_launch(const char *kernel, void *stream, void *const *bindings,
                      const uint32_t *lengths, int n_bindings, const void *uniform,
                      size_t uniform_bytes, void *workspace, size_t workspace_bytes);
+/*
+ * The int4 product (QuantMatMulInt4; M = 0 or 1 is the matvec) for callers that cannot allocate.
+ * No counterpart in the reference: accel's backends allocate through driver.Device.Alloc.  It is
+ * here for hosts that may only use memory handed to them (a plugin inside another runtime's
+ * allocator, a loop that must not enter the driver's allocator once running, a sandbox without
+ * cudaMalloc) and so cannot provide the split-K workspace ab_launch wants.  The scratch is an
+ * 8 MiB array built into the library's device image: every GPU that loads the library holds it
+ * until the process exits.  A shape that needs more is refused with AB_ERR_INVALID and a message
+ * naming the size; nothing is launched.  The call allocates nothing, on the device or through any
+ * library.  The first call on each device looks up the array's device address (with that device
+ * current); make that first call before starting any stream capture.  All calls share the one
+ * array, which keeps the previous call's partial sums (every element read is written first by
+ * the same call, so nothing needs clearing); two calls that overlap on the GPU (different
+ * streams) race on it, so keep calls to one stream or order them with events.
+ * a f32[M*K], bq/bs/bz the packed planes of the [K,N] matrix, out f32[M*N], all device pointers,
+ * 16-byte aligned; stream is a cudaStream_t of the current device.
+ */
+AB_API int ab_quant_matmul_int4_noalloc(void *stream, const float *a, const uint32_t *bq,
+                                        const uint16_t *bs, const uint16_t *bz, float *out,
+                                        uint32_t M, uint32_t N, uint32_t K);
 /* Which variant the last ab_launch of this thread selected, and why: Plan.Selections()
  * (tensor/compile.go:36-41). */
 AB_API const char *ab_last_selection(void);
