@@ -51,6 +51,12 @@ struct Int4MmaPlan { bool ok; uint32_t groups, splits, kc; size_t ws; };
 Int4MmaPlan plan_int4_mma(uint32_t M, uint32_t N, uint32_t K);
 int run_int4_mma(const Launch &l, const Int4MmaPlan &p, float *dst, uint32_t M, uint32_t N, uint32_t K);
 
+// the tcgen05 / TMEM int4 kernel (int4_tc.cu)
+struct Int4TcPlan { bool ok; uint32_t groups, splits, kc; int nmma; size_t ws; };
+Int4TcPlan plan_int4_tc(uint32_t M, uint32_t N, uint32_t K);
+int run_int4_tc(const Launch &l, const Int4TcPlan &p, float *dst, uint32_t M, uint32_t N, uint32_t K);
+int int4_tc_error_flag();       // nonzero once a bounded device-side wait has run out
+
 // launchers, one per reference kernel name (defined beside their kernels)
 int launch_quant_matvec_int4(Launch &);
 int launch_quant_matmul_int4(Launch &);

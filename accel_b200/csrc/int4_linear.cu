@@ -12,6 +12,8 @@
 // in f32: the per-weight work is one integer-to-float conversion and one FMA, and the zero-point
 // term costs one FMA per row and group.  A group with s == 0 contributes a[m][k]*z through the
 // second sum.  The summation order differs from the reference's, the values do not.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ab {
@@ -220,14 +222,39 @@ static void run_gemv(const Launch &l, const Int4Plan &p, float *dst, uint32_t M,
         ptr<const __half>(l, 3), dst, M, N, K, p.kc, m0, mrows); count_launch();
 }
 
+static int forced_path()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("AB_INT4_PATH");
+        v = !e ? 0 : (!strcmp(e, "tc") ? 1 : (!strcmp(e, "mma") ? 2 : (!strcmp(e, "simt") ? 3 : 0)));
+    }
+    return v;
+}
+
+static uint32_t tc_min_rows()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("AB_INT4_TC_MIN_ROWS");
+        v = e ? atoi(e) : 96;      // measured: the tcgen05 kernel wins from about a hundred rows
+    }
+    return (uint32_t)v;
+}
+
 static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint32_t K)
 {
     if (N == 0 || K == 0 || M == 0) return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u", name, M, N, K);
     Int4Plan p = plan_int4(M, N, K);
     // two or more rows of activations go to the tensor cores; one row stays on the CUDA cores
     Int4MmaPlan mp = plan_int4_mma(M, N, K);
-    const bool use_mma = mp.ok && M >= 2;
-    if (l.query_ws) { l.ws_need = use_mma ? mp.ws : p.ws; return AB_OK; }
+    // AB_INT4_PATH = tc | mma | simt overrides the choice (for measurements); tc_min_rows() is the
+    // batch size from which the tcgen05 kernel is used
+    Int4TcPlan tp = plan_int4_tc(M, N, K);
+    const int forced = forced_path();
+    const bool use_tc = tp.ok && (forced == 1 || (forced == 0 && M >= tc_min_rows()));
+    const bool use_mma = !use_tc && mp.ok && (forced == 2 || (forced == 0 && M >= 2));
+    if (l.query_ws) { l.ws_need = use_tc ? tp.ws : (use_mma ? mp.ws : p.ws); return AB_OK; }
 
     uint64_t weights = (uint64_t)K * N;
     if (l.len[0] < (uint64_t)M * K || l.len[1] < (weights + 7) / 8 ||
@@ -246,6 +273,22 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
             ptr<const float>(l, 0), ptr<const uint32_t>(l, 1), ptr<const __half>(l, 2),
             ptr<const __half>(l, 3), out, M, N, K); count_launch();
         note_selection("%s: generic kernel, N=%u is not a multiple of %u", name, N, kGroup);
+        return check_cuda(cudaGetLastError(), name);
+    }
+    if (use_tc) {
+        if (tp.ws > l.ws_bytes || (tp.ws && !l.ws))
+            return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, tp.ws,
+                        l.ws_bytes);
+        float *tdst = tp.splits > 1 ? reinterpret_cast<float *>(l.ws) : out;
+        int rc = run_int4_tc(l, tp, tdst, M, N, K);
+        if (rc) return rc;
+        if (tp.splits > 1) {
+            size_t mn = (size_t)M * N;
+            int4_reduce_kernel<<<(unsigned)((mn / 4 + 128) / 128), 128, 0, l.stream>>>(tdst, out, tp.splits, mn); count_launch();
+        }
+        note_selection("%s: tcgen05 kernel (M=128 x N=%d x K=16 MMAs, f16 operands, TMEM f32 "
+                       "accumulator), %u column groups x %u K splits of %u rows", name, tp.nmma,
+                       tp.groups, tp.splits, tp.kc);
         return check_cuda(cudaGetLastError(), name);
     }
     if (use_mma) {

@@ -164,7 +164,11 @@ def run_b200(args):
     dev = torch.device("cuda", local)
     group = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        import faulthandler
+        # a rank that never arrives must end the run with an error and a stack, not hang it
+        faulthandler.dump_traceback_later(int(os.environ.get("AB_BENCH_WATCHDOG_S", "600")), exit=True)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
         group = dist.group.WORLD
 
     cache_dtype = torch.float16 if args.kv == "f16" else torch.float32
@@ -175,6 +179,9 @@ def run_b200(args):
     B, ctx = args.batch, args.context
     total_steps = 2 * (args.steps + args.warmup) + 8
     engine = dec.DecodeEngine(model, B, max_context=ctx + total_steps + 16, group=group)
+    engine.overlap = world == 1 and not args.no_overlap
+    log = (lambda m: print(f"[rank {rank}] {m}", file=sys.stderr, flush=True)) if args.verbose else (lambda m: None)
+    log("engine built")
     engine.fill_context(ctx, seed=7)
     for s in range(B):
         engine.reserve(s, ctx + total_steps + 8)
@@ -182,8 +189,14 @@ def run_b200(args):
     rng = np.random.default_rng(99)
     first = rng.integers(0, cfg.vocab, B)
     engine.set_inputs(first)
-    engine.capture(warmup=1)
+    log("context filled")
+    if args.no_graph:
+        engine.prepare()
+        engine.record_step()
+    else:
+        engine.capture(warmup=1)
     torch.cuda.synchronize()
+    log("step captured")
     t_setup = time.perf_counter() - t_setup
 
     stream = torch.cuda.current_stream(dev)
@@ -233,6 +246,7 @@ def run_b200(args):
     gpu_launches = args.steps * (engine.kernel_launches_per_step + 1)
     del launches0
 
+    log(f"value timed: {ms_per_step:.3f} ms/step")
     # ---- e2e: the caller's loop; host token ids in, host token ids out, every step
     tok = engine.next_tokens.cpu().numpy()
     for _ in range(min(args.warmup, 3)):
@@ -246,6 +260,7 @@ def run_b200(args):
     e2e_s = max_over_ranks(w1 - w0)
     e2e_value = B * args.steps / e2e_s
 
+    log("e2e timed")
     # ---- roofline of the dominant kernel: the paged decode attention (K/V of every cached
     # position, once per KV head), timed alone with events on its launching stream, one launch per
     # layer so consecutive launches read different caches (1 GB each, far larger than L2)
@@ -355,6 +370,9 @@ def main():
     ap.add_argument("--kv", default="f32", choices=["f32", "f16"],
                     help="KV cache dtype; f32 is what the reference's batched decode kernel reads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-overlap", action="store_true", help="keep every operator on one stream")
+    ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

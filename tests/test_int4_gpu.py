@@ -66,6 +66,7 @@ def test_matches_the_oracle(M, K, N):
         assert "streaming row kernel" in runtime.last_selection()
     else:
         got = T.int4_matmul(torch.from_numpy(a).to(DEV), q).cpu().numpy()
+        assert "tensor-core kernel" in runtime.last_selection()
     assert_close(got, want, GEMM_TOL, f"int4 M={M} K={K} N={N}")
 
 
@@ -109,6 +110,7 @@ def test_full_size_against_a_binary64_product(M):
     a = normal(1, (M, K))
     want = (torch.from_numpy(a).to(DEV).double() @ torch.from_numpy(back).to(DEV).double()).cpu().numpy()
     got = T.int4_matmul(torch.from_numpy(a).to(DEV), to_int4(p, s, z, K * N)).cpu().numpy()
+    assert "tcgen05" in runtime.last_selection()        # large batches take the TMEM kernel
     assert_close(got, want, GEMM_TOL, f"full size M={M}")
     # and a sample of rows against the order-faithful oracle
     rows = [0, M // 2, M - 1]
