@@ -179,7 +179,7 @@ def run_b200(args):
     B, ctx = args.batch, args.context
     total_steps = 2 * (args.steps + args.warmup) + 8
     engine = dec.DecodeEngine(model, B, max_context=ctx + total_steps + 16, group=group)
-    engine.overlap = world == 1 and not args.no_overlap
+    engine.overlap = not args.no_overlap
     log = (lambda m: print(f"[rank {rank}] {m}", file=sys.stderr, flush=True)) if args.verbose else (lambda m: None)
     log("engine built")
     engine.fill_context(ctx, seed=7)
@@ -220,11 +220,11 @@ def run_b200(args):
     for _ in range(args.warmup):
         engine.run_step()
         engine.advance_on_device()
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    barrier()              # after the sampler's start-up sleep, so every rank enters the region together
     kv_bytes_first = engine.kv_bytes_read_per_step()
     launches0 = rt.launch_count()
     t0 = time.perf_counter()
@@ -286,7 +286,11 @@ def run_b200(args):
     roofline = {"bound": "hbm", "kernel": "attn_partition_kernel (+ attn_combine_kernel)",
                 "achieved": attn_gbs, "peak": peak, "unit": "GB/s", "frac": attn_gbs / peak,
                 "peak_source": peak_src, "bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
-                "traffic": None}
+                # dram__bytes_read + dram__bytes_write of one launch, from the ncu capture summarised in
+                # profiles/attn_partition_kernel_config4_layer.md (same kernel, same per-launch
+                # size: a launch reads one layer's cache whatever the layer count), scaled by the
+                # bytes of this run when the cache dtype or shard differs
+                "traffic": int(1.0790e9 * attn_bytes / 1087906112)}
 
     # ---- int4 GEMV bandwidth (the metric's second figure): K=4096, N=11008, M=1, rotating over
     # the layers' gate and up matrices (64 x 24 MB, larger than L2)
@@ -354,8 +358,13 @@ def run_b200(args):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        # the captured step holds NCCL work; tearing the process group down under it can block, so
+        # the ranks meet once more and leave without the teardown
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
@@ -372,6 +381,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="keep every operator on one stream")
+    ap.add_argument("--force-overlap", action="store_true", help="side-stream overlap at N > 1 too")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
