@@ -51,6 +51,22 @@ struct Int4MmaPlan { bool ok; uint32_t groups, splits, kc; size_t ws; };
 Int4MmaPlan plan_int4_mma(uint32_t M, uint32_t N, uint32_t K);
 int run_int4_mma(const Launch &l, const Int4MmaPlan &p, float *dst, uint32_t M, uint32_t N, uint32_t K);
 
+// the one-row streaming int4 kernel, K splits summed inside a cluster (int4_gemv.cu)
+struct Int4RowPlan { bool ok; int W; uint32_t tiles, splits, kc; size_t ws; };   // W groups per column tile
+Int4RowPlan plan_int4_row(uint32_t N, uint32_t K);
+int run_int4_row(const Launch &l, const Int4RowPlan &p, float *out, uint32_t N, uint32_t K);
+
+// the decode-batch int4 kernel: 16 rows per pass, K splits summed inside a cluster (int4_batch.cu)
+struct Int4BatchPlan { bool ok; int G; uint32_t tiles, splits, kc; };    // G groups per column tile
+Int4BatchPlan plan_int4_batch(uint32_t M, uint32_t N, uint32_t K);
+int run_int4_batch(const Launch &l, const Int4BatchPlan &p, float *out, uint32_t M, uint32_t N, uint32_t K);
+
+// the decode-batch int4 kernel on tcgen05 / TMEM (int4_decode_tc.cu)
+struct Int4DecodePlan { bool ok; int G; uint32_t tiles, splits, kc; };
+Int4DecodePlan plan_int4_decode(uint32_t M, uint32_t N, uint32_t K);
+int run_int4_decode(const Launch &l, const Int4DecodePlan &p, float *out, uint32_t M, uint32_t N, uint32_t K);
+int int4_decode_error_flag();
+
 // the tcgen05 / TMEM int4 kernel (int4_tc.cu)
 struct Int4TcPlan { bool ok; uint32_t groups, splits, kc; int nmma; size_t ws; };
 Int4TcPlan plan_int4_tc(uint32_t M, uint32_t N, uint32_t K);

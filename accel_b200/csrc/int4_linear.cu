@@ -227,7 +227,8 @@ static int forced_path()
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("AB_INT4_PATH");
-        v = !e ? 0 : (!strcmp(e, "tc") ? 1 : (!strcmp(e, "mma") ? 2 : (!strcmp(e, "simt") ? 3 : 0)));
+        v = !e ? 0 : (!strcmp(e, "tc") ? 1 : (!strcmp(e, "mma") ? 2 : (!strcmp(e, "simt") ? 3 :
+            (!strcmp(e, "batch") ? 4 : (!strcmp(e, "row") ? 5 : (!strcmp(e, "decode") ? 6 : 0))))));
     }
     return v;
 }
@@ -253,8 +254,19 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     Int4TcPlan tp = plan_int4_tc(M, N, K);
     const int forced = forced_path();
     const bool use_tc = tp.ok && (forced == 1 || (forced == 0 && M >= tc_min_rows()));
-    const bool use_mma = !use_tc && mp.ok && (forced == 2 || (forced == 0 && M >= 2));
-    if (l.query_ws) { l.ws_need = use_tc ? tp.ws : (use_mma ? mp.ws : p.ws); return AB_OK; }
+    Int4DecodePlan dp = plan_int4_decode(M, N, K);
+    const bool use_decode = !use_tc && dp.ok && forced == 6;
+    Int4BatchPlan bp = plan_int4_batch(M, N, K);
+    const bool use_batch = !use_tc && !use_decode && bp.ok && (forced == 4 || (forced == 0 && M >= 2));
+    const bool use_mma = !use_tc && !use_batch && mp.ok && (forced == 2 || (forced == 0 && M >= 2));
+    // one row: the streaming kernel that sums its own K splits (AB_INT4_PATH=simt keeps the older
+    // two-kernel form, which is also the fallback when no counter slot is free)
+    Int4RowPlan rp = plan_int4_row(N, K);
+    const bool use_row = !use_tc && !use_mma && !use_batch && !use_decode && rp.ok && M == 1 && forced != 3;
+    if (l.query_ws) {
+        l.ws_need = use_tc ? tp.ws : (use_batch || use_decode ? 0 : (use_mma ? mp.ws : (use_row ? 0 : p.ws)));
+        return AB_OK;
+    }
 
     uint64_t weights = (uint64_t)K * N;
     if (l.len[0] < (uint64_t)M * K || l.len[1] < (weights + 7) / 8 ||
@@ -291,6 +303,23 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
                        tp.groups, tp.splits, tp.kc);
         return check_cuda(cudaGetLastError(), name);
     }
+    if (use_decode) {
+        int rc = run_int4_decode(l, dp, out, M, N, K);
+        if (rc) return rc;
+        note_selection("%s: tcgen05 decode kernel (M=128 x N=16 x K=16 MMAs, f16 operands, TMEM f32 "
+                       "accumulator), %u tiles of %d column groups x a cluster of %u K splits of %u "
+                       "rows, %u pass(es) of 16 activation rows", name, dp.tiles, dp.G, dp.splits,
+                       dp.kc, (M + 15) / 16);
+        return check_cuda(cudaGetLastError(), name);
+    }
+    if (use_batch) {
+        int rc = run_int4_batch(l, bp, out, M, N, K);
+        if (rc) return rc;
+        note_selection("%s: tensor-core kernel (m16n8k16, f16 operands, f32 accumulate), %u tiles of "
+                       "%d column groups x a cluster of %u K splits of %u rows, %u pass(es) of 16 "
+                       "activation rows", name, bp.tiles, bp.G, bp.splits, bp.kc, (M + 15) / 16);
+        return check_cuda(cudaGetLastError(), name);
+    }
     if (use_mma) {
         if (mp.ws > l.ws_bytes || (mp.ws && !l.ws))
             return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, mp.ws,
@@ -305,6 +334,14 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
         note_selection("%s: tensor-core kernel (m16n8k16, f16 operands, f32 accumulate), %u column "
                        "groups x %u K splits of %u rows, %u pass(es) of 16 activation rows", name,
                        mp.groups, mp.splits, mp.kc, (M + 15) / 16);
+        return check_cuda(cudaGetLastError(), name);
+    }
+    if (use_row) {
+        int rc = run_int4_row(l, rp, out, N, K);
+        if (rc) return rc;
+        note_selection("%s: streaming row kernel (one mixed-precision FMA per weight), %u tiles of %d "
+                       "column groups x a cluster of %u K splits of %u rows", name, rp.tiles, rp.W,
+                       rp.splits, rp.kc);
         return check_cuda(cudaGetLastError(), name);
     }
     if (p.ws > l.ws_bytes || (p.ws && !l.ws))

@@ -66,7 +66,8 @@ def test_matches_the_oracle(M, K, N):
         assert "streaming row kernel" in runtime.last_selection()
     else:
         got = T.int4_matmul(torch.from_numpy(a).to(DEV), q).cpu().numpy()
-        assert "tensor-core kernel" in runtime.last_selection()
+        # the tensor-core kernels walk K in steps of 16 rows; other depths stay on the CUDA cores
+        assert ("tensor-core kernel" if K % 16 == 0 else "row kernel") in runtime.last_selection()
     assert_close(got, want, GEMM_TOL, f"int4 M={M} K={K} N={N}")
 
 
