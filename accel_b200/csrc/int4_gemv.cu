@@ -229,12 +229,13 @@ Int4RowPlan plan_int4_row(uint32_t N, uint32_t K)
     if (!p.ok) return p;
     const uint32_t gpr = N / kGroup, sms = (uint32_t)sm_count();
     static const uint32_t forced_w = env_u32("AB_INT4_ROW_GROUPS"), forced_s = env_u32("AB_INT4_SPLITS");
-    // two groups per tile unless that leaves the SMs short of CTAs even with the largest cluster
-    p.W = ((gpr + 1) / 2 * kRowMaxCluster >= 3 * sms) ? 2 : 1;
+    // measured: about two CTAs per SM and clusters of at most eight do best; two groups per tile
+    // for wide matrices (one scale sector serves both), one for narrow ones
+    p.W = gpr >= 64 ? 2 : 1;
     if (forced_w == 1 || forced_w == 2) p.W = (int)forced_w;
     p.tiles = (gpr + p.W - 1) / p.W;
-    // one wave of about four CTAs per SM, K ranges of at most 768 rows
-    uint32_t splits = 4u * sms / p.tiles;
+    uint32_t splits = 2u * sms / p.tiles;
+    if (splits > 8) splits = 8;
     if (forced_s) splits = forced_s;
     if (splits < 1) splits = 1;
     if (splits > (uint32_t)kRowMaxCluster) splits = kRowMaxCluster;

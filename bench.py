@@ -144,6 +144,57 @@ def time_kernel(fn, reps, stream):
     return e0.elapsed_time(e1) / reps
 
 
+def run_linear(args):
+    """One int4 product M x K x N on its own (the metric's second figure and the sweep over the
+    batch size): a CUDA graph of the product over 8 different weight matrices (larger than L2
+    together), timed with CUDA events over 10 replays.  Prints one JSON line."""
+    import torch
+
+    from accel_b200 import quant
+    from accel_b200 import runtime as rt
+    M, K, N = (int(v) for v in args.linear.split(","))
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    torch.manual_seed(7)
+    nm = max(2, min(8, (1 << 30) // (K * N // 2)))
+    mats = [quant.int4_quantize_device(torch.randn(K, N, device=dev) * 0.02) for _ in range(nm)]
+    a = torch.randn(M, K, device=dev)
+    out = torch.empty(M, N, device=dev)
+    u = rt.gemm_dims(M if M > 1 else 0, N, K)
+    name = "QuantMatMulInt4" if M > 1 else "QuantMatVecInt4"
+    x = a if M > 1 else a[0]
+
+    def body():
+        for c, sc, z in mats:
+            rt.launch(name, [x, c, sc, z, out], u)
+
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        body()
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            body()
+    torch.cuda.current_stream().wait_stream(s)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        g.replay()
+    e1.record()
+    e1.synchronize()
+    us = e0.elapsed_time(e1) / (10 * nm) * 1e3
+    nbytes = K * N // 2 + 2 * (K * N // 128) * 2 + M * K * 4 + M * N * 4
+    peak, src = measured_peaks()
+    print(json.dumps({"metric": "int4 linear", "shape": {"M": M, "K": K, "N": N}, "us": us,
+                      "bytes": nbytes, "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / peak,
+                      "tflops": 2.0 * M * K * N / us / 1e6, "peak_source": src, "matrices_rotated": nm,
+                      "kernel": rt.last_selection()}))
+
+
 def run_b200(args):
     import numpy as np
     import torch
@@ -383,8 +434,12 @@ def main():
     ap.add_argument("--no-overlap", action="store_true", help="keep every operator on one stream")
     ap.add_argument("--force-overlap", action="store_true", help="side-stream overlap at N > 1 too")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--linear", default=None, metavar="M,K,N",
+                    help="time one int4 product on its own instead of the decode step")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.linear:
+        run_linear(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

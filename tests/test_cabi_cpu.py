@@ -48,10 +48,16 @@ def test_an_unknown_kernel_is_a_refusal_not_a_fallback():
 
 
 def test_workspace_query_and_argument_checks_need_no_gpu():
-    # QuantMatVecInt4 at K=4096, N=4096 splits K and therefore needs partial sums
+    # QuantMatVecInt4 at K=4096, N=4096 adds its K splits inside a thread-block cluster: no scratch
     need = runtime.workspace_bytes("QuantMatVecInt4", [4096, 2097152, 131072, 131072, 4096],
                                    runtime.gemm_dims(0, 4096, 4096))
-    assert need > 0 and need % (4096 * 4) == 0
+    assert need == 0
+    # 16 rows against the 4096 x 32000 vocabulary matrix do not fit one wave of clusters: that
+    # product splits K across CTAs and needs one partial [M, N] tile per split
+    M, K, N = 16, 4096, 32000
+    need = runtime.workspace_bytes("QuantMatMulInt4", [M * K, K * N // 8, K * N // 128, K * N // 128, M * N],
+                                   runtime.gemm_dims(M, N, K))
+    assert need > 0 and need % (M * N * 4) == 0
     with pytest.raises(_lib.AccelError, match="takes 5 bindings"):
         runtime.workspace_bytes("QuantMatVecInt4", [1, 2], runtime.gemm_dims(0, 4096, 4096))
     with pytest.raises(_lib.AccelError, match="uniform block"):
