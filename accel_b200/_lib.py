@@ -15,6 +15,7 @@ AB_ERR_DEVICE_LOST = -4
 AB_ERR_BUSY = -5
 AB_ERR_CUDA = -6
 AB_ERR_NO_DEVICE = -7
+AB_ERR_TIMEOUT = -8
 
 AB_MEMORY_DEVICE = 0
 AB_MEMORY_HOST_VISIBLE = 1
@@ -107,6 +108,11 @@ SYMBOLS = [
                                                C.c_uint32]),
     ("ab_last_selection", C.c_char_p, []),
     ("ab_launch_count", C.c_uint64, []),
+    ("ab_peer_allreduce_buffer_bytes", C.c_size_t, [C.c_uint32]),
+    ("ab_peer_allreduce_state_bytes", C.c_size_t, []),
+    ("ab_peer_allreduce_f32", C.c_int, [_P, C.POINTER(_P), _P, C.c_int, C.c_int, _P, _P, C.c_uint32,
+                                        C.c_uint32]),
+    ("ab_peer_allreduce_error", C.c_int, [_P, C.POINTER(C.c_uint32)]),
     ("ab_int4_quantize", C.c_int, [_P, C.c_size_t, _P, _P, _P]),
     ("ab_int4_nibble", C.c_uint32, [_P, C.c_size_t]),
     ("ab_int4_dequantize", C.c_int, [_P, _P, _P, C.c_size_t, _P]),

@@ -318,6 +318,7 @@ const char *ab_error_string(int code)
     case AB_ERR_BUSY: return "busy";
     case AB_ERR_CUDA: return "CUDA error";
     case AB_ERR_NO_DEVICE: return "no CUDA device";
+    case AB_ERR_TIMEOUT: return "a bounded wait for a peer ran out";
     default: return "unknown status";
     }
 }

@@ -1,0 +1,167 @@
+// One-shot all-reduce (sum, f32) over NVLink peer memory, for the row-parallel products of a
+// tensor-parallel decode step: 256 KiB per call, 64 calls per step, where a library all-reduce is
+// bound by its launch and protocol latency, not by the links.
+//
+// Every rank owns one buffer that all ranks can address (the caller maps it: CUDA IPC or the
+// virtual-memory API; this file only sees pointers):
+//
+//   [flags: 64 x u32][data A: `capacity` floats][data B: `capacity` floats]
+//
+// A call with epoch e (1, 2, ...) uses data half e & 1:
+//   1. every CTA copies its slice of the input into the rank's OWN buffer;
+//   2. the last CTA of the rank to finish that copy stores e into flag[rank] of every peer
+//      (release, system scope);
+//   3. every CTA waits until all of its own flags are >= e (acquire, system scope; BOUNDED: after
+//      kSpinLimit polls the CTA records an error in the rank's state and returns without reading);
+//   4. every CTA adds its slice over all ranks' buffers in rank order (plain peer loads that bypass
+//      L1; every rank adds in the same order, so all ranks hold bit-identical sums) and writes the
+//      output, which may be the input.
+// Two halves are enough: a peer can only be two calls ahead of a rank that has not finished reading
+// if that rank had signalled the call in between, which it does after its reads (calls of one rank
+// are ordered on its stream).  The epoch lives in device memory and is advanced by the kernel, so
+// the call can be captured in a CUDA graph and replayed.
+//
+// No reference counterpart: accel is single-device.  No multicast, no TMA: plain loads and stores.
+#include "common.cuh"
+
+namespace ab {
+
+static constexpr int kArThreads = 256;
+static constexpr int kArMaxRanks = 8;
+static constexpr uint32_t kArFlagWords = 64;
+static constexpr uint32_t kArSpinLimit = 1u << 22;       // about a second of polling
+
+struct ArState { uint32_t epoch, arrived, done, error; };
+struct ArPeers { float *buf[kArMaxRanks]; };
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float4 ld_peer(const float4 *p)
+{
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// n4 = elements / 4; capacity4 = floats per data half / 4
+__global__ void __launch_bounds__(kArThreads)
+peer_allreduce_kernel(ArPeers peers, ArState *state, int rank, int world, const float4 *in,
+                      float4 *out, uint32_t n4, uint32_t capacity4)
+{
+    __shared__ int s_last, s_fail;
+    const uint32_t e = *reinterpret_cast<volatile uint32_t *>(&state->epoch) + 1;
+    const size_t half = kArFlagWords / 4 + (size_t)(e & 1) * capacity4;      // in float4 units
+    float4 *mine = reinterpret_cast<float4 *>(peers.buf[rank]) + half;
+    const uint32_t stride = gridDim.x * kArThreads;
+
+    for (uint32_t i = blockIdx.x * kArThreads + threadIdx.x; i < n4; i += stride) mine[i] = in[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        s_fail = 0;
+        s_last = atomicAdd(&state->arrived, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x < (unsigned)world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t *>(peers.buf[threadIdx.x]) + rank, e);
+    }
+    if (threadIdx.x < (unsigned)world) {
+        const uint32_t *flag = reinterpret_cast<const uint32_t *>(peers.buf[rank]) + threadIdx.x;
+        uint32_t polls = 0;
+        while ((int32_t)(ld_acquire_sys(flag) - e) < 0) {
+            if (++polls >= kArSpinLimit) { s_fail = 1; break; }
+        }
+    }
+    __syncthreads();
+    if (s_fail) {
+        if (threadIdx.x == 0) atomicExch(&state->error, e);
+    } else {
+        for (uint32_t i = blockIdx.x * kArThreads + threadIdx.x; i < n4; i += stride) {
+            float4 v[kArMaxRanks];
+#pragma unroll
+            for (int r = 0; r < kArMaxRanks; r++)
+                if (r < world) v[r] = ld_peer(reinterpret_cast<const float4 *>(peers.buf[r]) + half + i);
+            float4 s = v[0];
+#pragma unroll
+            for (int r = 1; r < kArMaxRanks; r++)
+                if (r < world) { s.x += v[r].x; s.y += v[r].y; s.z += v[r].z; s.w += v[r].w; }
+            out[i] = s;
+        }
+    }
+    // the last CTA to leave advances the epoch and re-arms the counters for the next call
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&state->done, 1u) == gridDim.x - 1) {
+            state->arrived = 0;
+            state->done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(&state->epoch) = e;
+        }
+    }
+}
+
+}  // namespace ab
+
+extern "C" AB_API size_t ab_peer_allreduce_buffer_bytes(uint32_t capacity_floats)
+{
+    return (size_t)ab::kArFlagWords * 4 + (size_t)2 * ((capacity_floats + 3) / 4 * 4) * 4;
+}
+
+extern "C" AB_API size_t ab_peer_allreduce_state_bytes(void) { return sizeof(ab::ArState); }
+
+extern "C" AB_API int ab_peer_allreduce_f32(void *stream, void *const *peer_buffers, void *state, int rank,
+                                            int world, const float *in, float *out, uint32_t n,
+                                            uint32_t capacity_floats)
+{
+    using namespace ab;
+    if (world < 1 || world > kArMaxRanks || rank < 0 || rank >= world)
+        return fail(AB_ERR_INVALID, "ab_peer_allreduce_f32: rank %d of %d (at most %d ranks)", rank, world,
+                    kArMaxRanks);
+    if (!peer_buffers || !state || !in || !out)
+        return fail(AB_ERR_INVALID, "ab_peer_allreduce_f32: NULL argument");
+    const uint32_t cap = (capacity_floats + 3) / 4 * 4;
+    if (n == 0 || n % 4 || n > cap)
+        return fail(AB_ERR_INVALID, "ab_peer_allreduce_f32: %u elements (a multiple of 4, at most the "
+                    "buffer's capacity of %u)", n, cap);
+    if (reinterpret_cast<uintptr_t>(in) % 16 || reinterpret_cast<uintptr_t>(out) % 16)
+        return fail(AB_ERR_INVALID, "ab_peer_allreduce_f32: input and output must be 16-byte aligned");
+    ArPeers peers{};
+    for (int r = 0; r < world; r++) {
+        if (!peer_buffers[r] || reinterpret_cast<uintptr_t>(peer_buffers[r]) % 16)
+            return fail(AB_ERR_INVALID, "ab_peer_allreduce_f32: buffer of rank %d is NULL or unaligned", r);
+        peers.buf[r] = static_cast<float *>(peer_buffers[r]);
+    }
+    const uint32_t n4 = n / 4;
+    // every CTA must be resident at once (they wait for peers, not for each other, but a peer's
+    // signal needs ALL of that peer's CTAs to have copied): at most one CTA per SM
+    uint32_t grid = (n4 + kArThreads - 1) / kArThreads;
+    const uint32_t sms = (uint32_t)sm_count();
+    if (grid > sms) grid = sms;
+    peer_allreduce_kernel<<<grid, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        peers, static_cast<ArState *>(state), rank, world, reinterpret_cast<const float4 *>(in),
+        reinterpret_cast<float4 *>(out), n4, cap / 4);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "ab_peer_allreduce_f32");
+}
+
+extern "C" AB_API int ab_peer_allreduce_error(const void *state, uint32_t *failed_call)
+{
+    using namespace ab;
+    ArState h{};
+    int rc = check_cuda(cudaMemcpy(&h, state, sizeof h, cudaMemcpyDeviceToHost), "ab_peer_allreduce_error");
+    if (rc) return rc;
+    if (failed_call) *failed_call = h.error;
+    if (h.error) return fail(AB_ERR_TIMEOUT, "ab_peer_allreduce: call %u gave up waiting for its peers", h.error);
+    return AB_OK;
+}

@@ -168,9 +168,15 @@ class DecodeEngine:
     reference sizes them), the page table from a BlockPool, and static buffers so the step can be
     captured once as a CUDA graph and replayed."""
 
-    def __init__(self, model: DecodeModel, batch: int, max_context: int, ops=rt, group=None):
+    def __init__(self, model: DecodeModel, batch: int, max_context: int, ops=rt, group=None,
+                 collective: str = "nccl"):
+        """collective: how the row-parallel products are summed over the ranks: "nccl" (the
+        process group's all-reduce) or "peer" (this library's one-shot kernel over NVLink peer
+        memory, peer.PeerAllReduce; GPUs only)."""
         cfg, sh = model.cfg, model.shard
         self.model, self.cfg, self.shard, self.ops, self.group = model, cfg, sh, ops, group
+        self.collective = collective
+        self._peer = None
         self.batch = batch
         dev = model.device
         self.dev = dev
@@ -210,6 +216,9 @@ class DecodeEngine:
         self.logits_local = z(B, len(sh.vocab))
         self.logits = z(B, cfg.vocab) if sh.tp > 1 else self.logits_local
         self.next_tokens = z(B, dt=I32)
+        if sh.tp > 1 and collective == "peer":
+            from .peer import PeerAllReduce
+            self._peer = PeerAllReduce(B * max(d, cfg.vocab), dev, group)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.overlap = True          # run the independent linears of a layer side by side
         self._side: List[torch.cuda.Stream] = []
@@ -310,6 +319,10 @@ class DecodeEngine:
 
     def _all_reduce(self, t):
         if self.shard.tp > 1:
+            if self._peer is not None:
+                self._peer.all_reduce_(t)
+                self._count += 1
+                return
             import torch.distributed as dist
             dist.all_reduce(t, group=self.group)
 

@@ -1,0 +1,75 @@
+"""One-shot all-reduce over NVLink peer memory for the tensor-parallel decode step.
+
+`PeerAllReduce` owns this rank's buffer (flags + two data halves), maps every peer's buffer, and
+launches `ab_peer_allreduce_f32` (csrc/peer_allreduce.cu) on the caller's stream.  The mapping is
+done by torch's symmetric-memory allocator (CUDA virtual-memory handles exchanged between the
+ranks of a process group); the kernel only sees the resulting pointers.  Multicast objects are
+not used: the library's loads and stores are plain peer accesses.
+
+accel is single-device: there is no reference counterpart (the tensor-parallel layer sits above
+the per-device plan, see decode.py)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+class PeerAllReduce:
+    def __init__(self, capacity_floats: int, device: torch.device, group=None):
+        """Collective: every rank of `group` (default: the world) constructs one, with the same
+        capacity (the largest element count a call will carry).  Without a process group the
+        object is a single rank (the sum is a copy through the rank's own buffer)."""
+        L = _lib.lib()
+        if not dist.is_initialized():
+            self.group, self.rank, self.world = None, 0, 1
+            self.capacity = (int(capacity_floats) + 3) // 4 * 4
+            nbytes = int(L.ab_peer_allreduce_buffer_bytes(self.capacity))
+            self._buf = torch.zeros(nbytes // 4, dtype=torch.float32, device=device)
+            self._ptrs = (C.c_void_p * 1)(self._buf.data_ptr())
+            self._state = torch.zeros(int(L.ab_peer_allreduce_state_bytes()) // 4, dtype=torch.int32, device=device)
+            return
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        if self.world > 8:
+            raise _lib.AccelError(_lib.AB_ERR_INVALID, f"PeerAllReduce: {self.world} ranks (at most 8)")
+        self.capacity = (int(capacity_floats) + 3) // 4 * 4
+        nbytes = int(L.ab_peer_allreduce_buffer_bytes(self.capacity))
+        try:
+            symm.set_backend("CUDA")
+        except Exception:
+            pass                                   # already chosen by an earlier allocation
+        self._buf = symm.empty(nbytes // 4, dtype=torch.float32, device=device)
+        self._buf.zero_()
+        self._hdl = symm.rendezvous(self._buf, self.group)
+        ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+        if len(ptrs) != self.world or ptrs[self.rank] != self._buf.data_ptr():
+            raise _lib.AccelError(_lib.AB_ERR_INVALID, "PeerAllReduce: the allocator's peer table does not "
+                                  "match this rank's buffer")
+        self._ptrs = (C.c_void_p * self.world)(*ptrs)
+        self._state = torch.zeros(int(L.ab_peer_allreduce_state_bytes()) // 4, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)                   # every rank's flags are zero before any call
+
+    def all_reduce_(self, t: torch.Tensor, stream=None) -> torch.Tensor:
+        """Sums `t` (f32, contiguous, a multiple of 4 elements, at most the capacity) over the
+        ranks in place; every rank ends with the same bits."""
+        if t.dtype != torch.float32 or not t.is_contiguous() or not t.is_cuda:
+            raise _lib.AccelError(_lib.AB_ERR_INVALID, "PeerAllReduce: a contiguous f32 CUDA tensor is required")
+        s = stream if stream is not None else torch.cuda.current_stream(t.device)
+        _lib.check(_lib.lib().ab_peer_allreduce_f32(
+            C.c_void_p(s.cuda_stream), self._ptrs, C.c_void_p(self._state.data_ptr()), self.rank, self.world,
+            C.c_void_p(t.data_ptr()), C.c_void_p(t.data_ptr()), t.numel(), self.capacity))
+        return t
+
+    def check(self) -> None:
+        """Synchronous: raises when a call of this rank gave up waiting for its peers."""
+        _lib.check(_lib.lib().ab_peer_allreduce_error(C.c_void_p(self._state.data_ptr()), None))

@@ -229,7 +229,8 @@ def run_b200(args):
     model = dec.DecodeModel(cfg, shard, dev, seed=1234)
     B, ctx = args.batch, args.context
     total_steps = 2 * (args.steps + args.warmup) + 8
-    engine = dec.DecodeEngine(model, B, max_context=ctx + total_steps + 16, group=group)
+    engine = dec.DecodeEngine(model, B, max_context=ctx + total_steps + 16, group=group,
+                              collective=args.collective)
     engine.overlap = not args.no_overlap
     log = (lambda m: print(f"[rank {rank}] {m}", file=sys.stderr, flush=True)) if args.verbose else (lambda m: None)
     log("engine built")
@@ -389,7 +390,7 @@ def run_b200(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch": B, "context": ctx, "layers": cfg.layers,
-                       "kv_cache": args.kv, "parallelism": f"tp{world}",
+                       "kv_cache": args.kv, "parallelism": f"tp{world}", "collective": (args.collective if world > 1 else "none"),
                        "l2": "inputs larger than L2: each step streams "
                              f"{weight_bytes / 1e9:.2f} GB of int4 weights and "
                              f"{kv_bytes_first / 1e9:.1f} GB of K/V per rank",
@@ -434,6 +435,9 @@ def main():
     ap.add_argument("--no-overlap", action="store_true", help="keep every operator on one stream")
     ap.add_argument("--force-overlap", action="store_true", help="side-stream overlap at N > 1 too")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="all-reduce of the row-parallel products at N > 1: this library's one-shot "
+                         "kernel over NVLink peer memory, or NCCL")
     ap.add_argument("--linear", default=None, metavar="M,K,N",
                     help="time one int4 product on its own instead of the decode step")
     args = ap.parse_args()

@@ -31,7 +31,8 @@ typedef enum ab_status {
     AB_ERR_DEVICE_LOST = -4,  /* sticky: driver.ErrDeviceLost (internal/driver/plan.go:385-391)  */
     AB_ERR_BUSY = -5,         /* a submission of this executable is still in flight              */
     AB_ERR_CUDA = -6,         /* a CUDA call failed for a reason that is not loss                */
-    AB_ERR_NO_DEVICE = -7     /* no CUDA device or driver                                        */
+    AB_ERR_NO_DEVICE = -7,    /* no CUDA device or driver                                        */
+    AB_ERR_TIMEOUT = -8       /* a bounded device-side wait for a peer ran out; nothing is lost   */
 } ab_status;
 
 AB_API const char *ab_error_string(int code);
@@ -256,6 +257,31 @@ AB_API int ab_blockpool_positions(ab_blockpool *p, int n_pages);
  * zeros are bit-identical to the same columns of the unsharded matrix. */
 AB_API int ab_int4_column_split(uint32_t n_cols, int parts, int rank, uint32_t *begin,
                                 uint32_t *end);
+
+/* ---- One-shot all-reduce over NVLink peer memory (tensor-parallel decode) -----------------
+ * No reference counterpart: accel is single-device (the tensor-parallel layer sits above the
+ * per-device plan).  Sums `n` f32 values (a multiple of 4) over `world` <= 8 ranks, one process per
+ * GPU, and leaves the same bits on every rank (ranks are added in rank order).  `out` may be `in`.
+ *
+ * Each rank allocates ab_peer_allreduce_buffer_bytes(capacity) bytes that every rank can address
+ * (CUDA IPC, the virtual-memory API, or a symmetric-memory allocator), zeroed before the first
+ * call on any rank, and passes all ranks' mappings of them, in rank order, as peer_buffers (a HOST
+ * array of `world` device pointers, 16-byte aligned).  `state` is
+ * ab_peer_allreduce_state_bytes() of this rank's own zeroed device memory; it holds the call
+ * counter, so a call can be captured in a CUDA graph and replayed.  Calls of one rank must be
+ * ordered on one stream, and every rank must make the same sequence of calls with the same n.
+ * The kernels of different ranks wait for one another over NVLink: every rank must run on a GPU
+ * of its own.  The wait is bounded (about a second of polling); a rank whose peers never arrive
+ * records the failing call in `state`, writes no output and returns normally, and
+ * ab_peer_allreduce_error reports AB_ERR_TIMEOUT from then on.  Loads and stores are plain (no
+ * multicast, no TMA). */
+AB_API size_t ab_peer_allreduce_buffer_bytes(uint32_t capacity_floats);
+AB_API size_t ab_peer_allreduce_state_bytes(void);
+AB_API int ab_peer_allreduce_f32(void *stream, void *const *peer_buffers, void *state, int rank,
+                                 int world, const float *in, float *out, uint32_t n,
+                                 uint32_t capacity_floats);
+/* AB_OK, or AB_ERR_TIMEOUT with *failed_call = the 1-based call that gave up (synchronous). */
+AB_API int ab_peer_allreduce_error(const void *state, uint32_t *failed_call);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,64 @@
+"""Run under torchrun by test_peer_allreduce_gpu.py (one rank per GPU): the one-shot peer
+all-reduce against the process group's all-reduce, eagerly and replayed from a CUDA graph."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, __file__.rsplit("/", 2)[0])
+from accel_b200.peer import PeerAllReduce  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    ar = PeerAllReduce(16 * 32000, dev)
+    worst = 0.0
+    for n in (4, 65536, 16 * 32000, 1000 * 4):
+        for it in range(5):
+            g = torch.Generator(device=dev).manual_seed(1000 * rank + it)
+            x = torch.randn(n, device=dev, generator=g)
+            want = x.clone()
+            dist.all_reduce(want)
+            got = ar.all_reduce_(x.clone())
+            torch.cuda.synchronize()
+            worst = max(worst, float((got - want).abs().max() / want.abs().max().clamp_min(1e-30)))
+            gathered = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(gathered, got)
+            assert all(torch.equal(gathered[0], t) for t in gathered), "ranks disagree on the bits"
+    # 64 calls per replay, as a decode step makes them
+    x = torch.randn(16, 4096, device=dev)
+    ref = x.clone()
+    for _ in range(64 * 3 + 64):
+        dist.all_reduce(ref)
+        ref /= world
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        def body():
+            for _ in range(64):
+                ar.all_reduce_(x)
+                x.div_(world)
+        body()                                   # warm-up: 64 calls
+        s.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=s):
+            body()
+        for _ in range(3):
+            gr.replay()
+    torch.cuda.synchronize()
+    ar.check()
+    err = float((x - ref).abs().max() / ref.abs().max())
+    if rank == 0:
+        print(f"OK world={world} worst_rel_err={worst:.3e} replayed_rel_err={err:.3e}", flush=True)
+    assert worst < 1e-5 and err < 1e-4
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()
