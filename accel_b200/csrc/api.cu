@@ -112,6 +112,9 @@ static const KernelEntry kKernels[] = {
     {"CastF16ToF32", 2, 0, launch_cast_f16_to_f32},
     {"Int4Quantize", 4, 0, launch_int4_quantize},
     {"DecodeStepInputs", 7, 32, launch_decode_step_inputs},
+    {"AddRMSNorm", 5, 16, launch_add_rmsnorm},
+    {"RopeScatterQKV", 8, 32, launch_rope_scatter_qkv},
+    {"RopeScatterQKVF16", 8, 32, launch_rope_scatter_qkv_f16},
 };
 static constexpr int kKernelCount = (int)(sizeof(kKernels) / sizeof(kKernels[0]));
 

@@ -101,6 +101,9 @@ int launch_cast_f32_to_f16(Launch &);
 int launch_cast_f16_to_f32(Launch &);
 int launch_int4_quantize(Launch &);
 int launch_decode_step_inputs(Launch &);
+int launch_add_rmsnorm(Launch &);
+int launch_rope_scatter_qkv(Launch &);
+int launch_rope_scatter_qkv_f16(Launch &);
 
 // f32 -> f16 with the reference's rule: round to nearest even, except that every magnitude below
 // 2^-24 becomes a signed zero (internal/kernel/narrow.go:82-83); IEEE rounds (2^-25, 2^-24) up.

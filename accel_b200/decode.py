@@ -177,6 +177,10 @@ class DecodeEngine:
         self.model, self.cfg, self.shard, self.ops, self.group = model, cfg, sh, ops, group
         self.collective = collective
         self._peer = None
+        # fused support kernels (AddRMSNorm, RopeScatterQKV: extensions of this library, each
+        # bit-identical to the chain of reference operators it replaces); an operator table that
+        # only knows the reference names, like the oracle's, gets the chain
+        self.fuse = ops is rt
         self.batch = batch
         dev = model.device
         self.dev = dev
@@ -337,18 +341,37 @@ class DecodeEngine:
         scale = float(np.float32(1.0) / np.float32(np.sqrt(D)))
         L("GatherRows", [self.model.embedding, self.tokens, self.x], _u("<IIII", B, d, cfg.vocab, 0))
         x, x2 = self.x, self.x2
+        f16 = cfg.cache_dtype == torch.float16
+        rp = _u("<IIII", B, self.hk * D, self.capacity, 0)
+        scatter = "ScatterRowsF16" if f16 else "ScatterRows"
+        norm_u = _u("<IIfI", B, d, cfg.eps, 0)
+
+        def add_norm(gain):
+            """x <- x + proj, h <- RMSNorm(x) * gain"""
+            nonlocal x, x2
+            if self.fuse:
+                L("AddRMSNorm", [x, self.proj, gain, x2, self.h], norm_u)
+                x, x2 = x2, x
+            else:
+                L("ElemAdd", [x, self.proj, x2])
+                x, x2 = x2, x
+                L("RMSNorm", [x, gain, self.h], norm_u)
+
         for li, lay in enumerate(self.model.layers):
-            L("RMSNorm", [x, lay.g1, self.h], _u("<IIfI", B, d, cfg.eps, 0))
-            f16 = cfg.cache_dtype == torch.float16
-            rp = _u("<IIII", B, self.hk * D, self.capacity, 0)
-            scatter = "ScatterRowsF16" if f16 else "ScatterRows"
+            if li == 0:
+                L("RMSNorm", [x, lay.g1, self.h], norm_u)
+            else:
+                add_norm(lay.g1)                 # the previous layer's second residual add
 
             def q_branch():
                 self._linear(self.h, lay.wq, self.q)
-                L("RoPE", [self.pos_q, self.q], _u("<IIIf", B * self.hq, D, D, cfg.rope_base))
+                if not self.fuse:
+                    L("RoPE", [self.pos_q, self.q], _u("<IIIf", B * self.hq, D, D, cfg.rope_base))
 
             def k_branch():
                 self._linear(self.h, lay.wk, self.k)
+                if self.fuse:
+                    return
                 L("RoPE", [self.pos_k, self.k], _u("<IIIf", B * self.hk, D, D, cfg.rope_base))
                 krows = self.k
                 if f16:
@@ -358,6 +381,8 @@ class DecodeEngine:
 
             def v_branch():
                 self._linear(self.h, lay.wv, self.v)
+                if self.fuse:
+                    return
                 vrows = self.v
                 if f16:
                     vrows = self._v16
@@ -366,22 +391,22 @@ class DecodeEngine:
 
             # q, k and v depend only on h: three branches that may run side by side
             self._parallel([q_branch, k_branch, v_branch])
+            if self.fuse:
+                L("RopeScatterQKVF16" if f16 else "RopeScatterQKV",
+                  [self.pos_q, self.pos_k, self.slots, self.q, self.k, self.v, self.k_cache[li], self.v_cache[li]],
+                  _u("<IIIIIIfI", B, self.hq, self.hk, D, D, self.capacity, cfg.rope_base, 0))
             L("AttentionDecodeBatchedF16" if f16 else "AttentionDecodeBatched",
               [self.q, self.k_cache[li], self.v_cache[li], self.pages, self.lengths, self.attn],
               _u("<IIIIIIfI", B, self.hq, self.hk, D, cfg.block, self.max_pages, scale, 0))
             self._linear(self.attn, lay.wo, self.proj)
             self._all_reduce(self.proj)
-            L("ElemAdd", [x, self.proj, x2])
-            x, x2 = x2, x
-            L("RMSNorm", [x, lay.g2, self.h], _u("<IIfI", B, d, cfg.eps, 0))
+            add_norm(lay.g2)
             self._parallel([lambda: self._linear(self.h, lay.wg, self.gate),
                             lambda: self._linear(self.h, lay.wu, self.up)])
             L("SwiGLU", [self.gate, self.up, self.act])
             self._linear(self.act, lay.wd, self.proj)
             self._all_reduce(self.proj)
-            L("ElemAdd", [x, self.proj, x2])
-            x, x2 = x2, x
-        L("RMSNorm", [x, self.model.g_final, self.h], _u("<IIfI", B, d, cfg.eps, 0))
+        add_norm(self.model.g_final)
         self._linear(self.h, self.model.lm_head, self.logits_local)
         if self.shard.tp > 1:
             # each rank owns a column range of the vocabulary: place it in a zeroed full-width

@@ -223,6 +223,15 @@ AB_API uint64_t ab_launch_count(void);
  *                    slots u32[B], lengths u32[B]     {Batch,QHeads,KVHeads,Block,MaxPages}@0..16 (32 B).  No reference
  *                    kernel: the per-step host writes of a decode loop (docs/tutorial/11-batching-sequences.md:83-103)
  *                    done on the device, so a replayed step feeds the next without a host round trip.
+ *  AddRMSNorm        x, delta, w, sum f32[rows*width], norm f32[rows*width]  RowDims (16 B).  No reference kernel: ElemAdd
+ *                    (elementwise.go:22) followed by RMSNorm (norm.go:46) in one launch, sum = x + delta, norm =
+ *                    RMSNorm(sum) * w; bit-identical to the two dispatches.  Width <= 8192.
+ *  RopeScatterQKV, RopeScatterQKVF16   pos_q u32[B*QHeads], pos_k u32[B*KVHeads], slots u32[B], q f32 (in place),
+ *                    k f32 (in place), v f32, k_cache, v_cache (f32 / f16 [Capacity, KVHeads, HeadDim])
+ *                    {Batch,QHeads,KVHeads,HeadDim,RotaryDim,Capacity,Base f32}@0..24 (32 B).  No reference kernel:
+ *                    RoPE on q and on k (elementwise.go:267), then ScatterRows of k and v into the paged cache at
+ *                    each row's slot (elementwise.go:182; F16: through CastF32ToF16, cast.go:30), in one launch;
+ *                    bit-identical to the four (six) dispatches.
  */
 
 /* ------------------------------------------------------------------------------------------ */

@@ -68,6 +68,22 @@ def launch(name, bindings, uniform=None, lengths=None, workspace=None):
         rows = b[1].numel()
         out = orc.sample_argmax(_np(b[0]).reshape(rows, vocab))
         b[1].copy_(torch.from_numpy(out.view(np.int32)))
+    elif name == "SegmentOffsets":
+        rows = struct.unpack("<I", u[:4])[0]
+        b[1].copy_(torch.from_numpy(orc.segment_offsets(_np(b[0], np.uint32)[:rows]).view(np.int32)))
+    elif name == "GroupedMatMulInt4":
+        # the extension's definition: dequantize each expert's planes (quant.Int4Dequantize), then
+        # the reference GroupedMatMul
+        E, tokens, K, N = struct.unpack("<IIII", u[:16])
+        per = K * N
+        w = np.empty((E, K, N), np.float32)
+        codes, sc, zr = _np(b[1], np.uint32), _np(b[2], np.uint16), _np(b[3], np.uint16)
+        for e in range(E):
+            w[e] = orc.int4_dequantize(codes[e * per // 8:(e + 1) * per // 8], sc[e * per // 128:(e + 1) * per // 128],
+                                       zr[e * per // 128:(e + 1) * per // 128], per).reshape(K, N)
+        out = orc.grouped_matmul(_np(b[0]).reshape(tokens, K), w, _np(b[4], np.uint32), tokens, E, K, N,
+                                 out=_np(b[5]).reshape(tokens, N).copy())
+        b[5].view(-1).copy_(torch.from_numpy(out.ravel()))
     elif name == "CastF32ToF16":
         b[1].view(-1).copy_(torch.from_numpy(orc.to_f16_bits(_np(b[0])).view(np.float16)))
     elif name == "DecodeStepInputs":

@@ -98,3 +98,32 @@ def test_graph_replay_and_device_advance_equal_the_host_loop():
         b.advance_on_device()
     assert np.array_equal(np.array(out_a), np.array(out_b))
     assert a.launches_per_step == b.launches_per_step > 0
+
+
+@pytest.mark.parametrize("cache", ["f32", "f16"])
+def test_fused_support_kernels_equal_the_chain_of_reference_operators(cache):
+    """AddRMSNorm and RopeScatterQKV against ElemAdd, RMSNorm, RoPE, (CastF32ToF16,) ScatterRows:
+    the same step recorded both ways gives the same bits: tokens, logits and caches."""
+    cfg = small_cfg(torch.float16 if cache == "f16" else torch.float32)
+    shard = dec.Shard.plan(cfg, 1, 0)
+    model = dec.DecodeModel(cfg, shard, DEV, seed=9, std=0.08)
+    batch, steps = 3, 6
+    fused = dec.DecodeEngine(model, batch, max_context=64)
+    chain = dec.DecodeEngine(model, batch, max_context=64)
+    assert fused.fuse
+    chain.fuse = False
+    for e in (fused, chain):
+        e.fill_context(9, seed=4)
+        for s in range(batch):
+            e.reserve(s, 9 + steps + 1)
+        e.upload_pages()
+    tok_f = tok_c = np.arange(batch) + 3
+    for t in range(steps):
+        tok_f = fused.step(tok_f)
+        tok_c = chain.step(tok_c)
+        assert np.array_equal(tok_f, tok_c), t
+        assert torch.equal(fused.logits, chain.logits), t
+    assert fused.launches_per_step < chain.launches_per_step
+    for li in range(cfg.layers):
+        assert torch.equal(fused.k_cache[li], chain.k_cache[li])
+        assert torch.equal(fused.v_cache[li], chain.v_cache[li])
