@@ -46,7 +46,9 @@ def expert_range(experts: int, world: int, rank: int) -> range:
 
 class ExpertParallelFFN:
     def __init__(self, experts: int, d_model: int, ffn: int, device, group=None, seed: int = 77,
-                 std: float = 0.02, ops=rt, quantize=None):
+                 std: float = 0.02, ops=rt, quantize=None, init_on_device: bool = False):
+        """init_on_device: draw the random weights with the device's generator (fast at full size;
+        the values then depend on the device type, not on the number of ranks)."""
         import torch.distributed as dist
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -54,6 +56,7 @@ class ExpertParallelFFN:
         self.E, self.d, self.ffn, self.ops = experts, d_model, ffn, ops
         self.device = torch.device(device)
         self.local = expert_range(experts, self.world, self.rank)
+        self._init_dev = self.device if init_on_device else torch.device("cpu")
         if quantize is None:
             from . import quant
             quantize = quant.int4_quantize_device
@@ -66,8 +69,8 @@ class ExpertParallelFFN:
         experts."""
         planes = []
         for e in self.local:
-            g = torch.Generator(device="cpu").manual_seed(seed * 1000003 + which * 1009 + e)
-            w = (torch.randn(K, N, generator=g) * std).to(self.device)
+            g = torch.Generator(device=self._init_dev).manual_seed(seed * 1000003 + which * 1009 + e)
+            w = (torch.randn(K, N, generator=g, device=self._init_dev) * std).to(self.device)
             planes.append(quantize(w))
         cat = lambda i: torch.cat([p[i].reshape(-1) for p in planes])
         return ExpertWeights(cat(0), cat(1), cat(2), K, N)

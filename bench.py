@@ -195,6 +195,60 @@ def run_linear(args):
                       "kernel": rt.last_selection()}))
 
 
+def run_moe(args):
+    """Config 5: the expert half of a MoE layer, 8 experts, 4096 tokens x top-2 = 8192 routed rows,
+    d 4096, expert FFN 14336 (gate, up, SwiGLU, down), int4 experts; per-expert counts from a
+    seeded multinomial (top-2 distinctness per token is not modelled by the config).  At N > 1 the
+    experts are split over the ranks and the rows travel by all-to-all; the 8192 rows are split
+    evenly over the ranks (strong scaling).  Prints one JSON line."""
+    import torch
+    import torch.distributed as dist
+
+    from accel_b200 import moe
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    E, d, ffn, rows_total = 8, 4096, 14336, 8192
+    layer = moe.ExpertParallelFFN(E, d, ffn, dev, seed=5, init_on_device=True)
+    g = torch.Generator().manual_seed(5)
+    expert_all = torch.multinomial(torch.ones(E), rows_total, replacement=True, generator=g).to(torch.int32)
+    lo, hi = rank * rows_total // world, (rank + 1) * rows_total // world
+    x = torch.randn(hi - lo, d, device=dev)
+    expert = expert_all[lo:hi].to(dev)
+    for _ in range(max(args.warmup, 1)):
+        layer.forward(x, expert)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = layer.forward(x, expert)
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    flops = 3 * 2.0 * rows_total * d * ffn
+    if rank == 0:
+        print(json.dumps({"metric": "grouped int4 MoE FFN", "value": flops / ms / 1e9, "unit": "TFLOP/s",
+                          "ms_per_layer": ms, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                          "rows_per_s": rows_total / ms * 1e3, "scaling": "strong",
+                          "config": {"workload": "8 experts, 8192 routed rows, d 4096, ffn 14336, int4 group 128",
+                                     "parallelism": f"ep{world}", "counts": "seeded multinomial over 8 experts"},
+                          "checksum": float(out.double().abs().sum().item())}))
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
+
+
 def run_b200(args):
     import numpy as np
     import torch
@@ -438,11 +492,15 @@ def main():
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="all-reduce of the row-parallel products at N > 1: this library's one-shot "
                          "kernel over NVLink peer memory, or NCCL")
+    ap.add_argument("--moe", action="store_true",
+                    help="time the expert-parallel grouped int4 FFN (config 5) instead of the decode step")
     ap.add_argument("--linear", default=None, metavar="M,K,N",
                     help="time one int4 product on its own instead of the decode step")
     args = ap.parse_args()
     if args.linear:
         run_linear(args)
+    elif args.moe:
+        run_moe(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -20,10 +20,11 @@ DEV = "cuda:0"
 
 def test_one_rank_matches_the_oracle():
     E, D, FFN, rows = 4, 256, 384, 150
-    gpu = moe.ExpertParallelFFN(E, D, FFN, DEV, seed=8, std=0.05)
+    gpu = moe.ExpertParallelFFN(E, D, FFN, DEV, seed=8, std=0.05)          # quantized on the device
     cpu = moe.ExpertParallelFFN(E, D, FFN, "cpu", seed=8, std=0.05, ops=oracle_ops, quantize=oracle_ops.quantize)
-    for a, b in ((gpu.gate, cpu.gate), (gpu.down, cpu.down)):          # same experts, same packing
+    for a, b in ((gpu.gate, cpu.gate), (gpu.up, cpu.up), (gpu.down, cpu.down)):   # same experts, same packing
         assert torch.equal(a.codes.cpu(), b.codes) and torch.equal(a.scales.cpu(), b.scales)
+        assert torch.equal(a.zeros.cpu(), b.zeros)
     g = torch.Generator().manual_seed(1)
     x = torch.randn(rows, D, generator=g)
     expert = torch.randint(0, E, (rows,), generator=g, dtype=torch.int32)
