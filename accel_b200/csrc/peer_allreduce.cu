@@ -111,6 +111,113 @@ peer_allreduce_kernel(ArPeers peers, ArState *state, int rank, int world, const 
     }
 }
 
+// The same all-reduce with the decode layer's next two operators done by its summing stage:
+//   sum_out = residual + (sum over ranks of in),   norm_out = RMSNorm(sum_out) * gain
+// (ElemAdd, internal/kernels/elementwise.go:22, then RMSNorm, internal/kernels/norm.go:46).  One CTA
+// per row: the row's sum of squares never leaves the CTA.  Element tid + 256 j belongs to thread
+// tid, the per-thread and cross-warp orders are those of the AddRMSNorm kernel, and ranks are added
+// in rank order, so the result is bit-identical to the plain all-reduce followed by AddRMSNorm.
+// All of a thread's peer loads (ranks x PER) are issued before the first is used: one NVLink round
+// trip, not one per rank.
+template <int PER>
+__global__ void __launch_bounds__(kArThreads)
+peer_allreduce_add_rmsnorm_kernel(ArPeers peers, ArState *state, int rank, int world, const float *in,
+                                  const float *residual, const float *gain, float *sum_out, float *norm_out,
+                                  uint32_t width, float eps, uint32_t capacity)
+{
+    __shared__ int s_last, s_fail;
+    __shared__ float red[8];
+    const uint32_t e = *reinterpret_cast<volatile uint32_t *>(&state->epoch) + 1;
+    const size_t half = kArFlagWords + (size_t)(e & 1) * capacity;           // in floats
+    const size_t base = (size_t)blockIdx.x * width;
+    float *mine = peers.buf[rank] + half + base;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const uint32_t i = threadIdx.x + kArThreads * j;
+        if (i < width) mine[i] = in[base + i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        s_fail = 0;
+        s_last = atomicAdd(&state->arrived, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x < (unsigned)world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t *>(peers.buf[threadIdx.x]) + rank, e);
+    }
+    if (threadIdx.x < (unsigned)world) {
+        const uint32_t *flag = reinterpret_cast<const uint32_t *>(peers.buf[rank]) + threadIdx.x;
+        uint32_t polls = 0;
+        while ((int32_t)(ld_acquire_sys(flag) - e) < 0) {
+            if (++polls >= kArSpinLimit) { s_fail = 1; break; }
+        }
+    }
+    __syncthreads();
+    if (s_fail) {
+        if (threadIdx.x == 0) atomicExch(&state->error, e);
+    } else {
+        float v[PER];
+        {
+            float p[kArMaxRanks][PER];
+#pragma unroll
+            for (int r = 0; r < kArMaxRanks; r++)
+#pragma unroll
+                for (int j = 0; j < PER; j++) {
+                    const uint32_t i = threadIdx.x + kArThreads * j;
+                    p[r][j] = 0.f;
+                    if (r < world && i < width)
+                        asm volatile("ld.relaxed.sys.global.f32 %0, [%1];"
+                                     : "=f"(p[r][j]) : "l"(peers.buf[r] + half + base + i) : "memory");
+                }
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                float s = p[0][j];
+#pragma unroll
+                for (int r = 1; r < kArMaxRanks; r++)
+                    if (r < world) s += p[r][j];
+                v[j] = s;
+            }
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const uint32_t i = threadIdx.x + kArThreads * j;
+            if (i < width) {
+                v[j] = __fadd_rn(residual[base + i], v[j]);
+                sum_out[base + i] = v[j];
+                acc = fmaf(v[j], v[j], acc);
+            } else {
+                v[j] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sh);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        float total = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) total += red[i];
+        const float scale = (float)(1.0 / sqrt((double)(total / (float)width + eps)));
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const uint32_t i = threadIdx.x + kArThreads * j;
+            if (i < width) norm_out[base + i] = v[j] * scale * gain[i];
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&state->done, 1u) == gridDim.x - 1) {
+            state->arrived = 0;
+            state->done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(&state->epoch) = e;
+        }
+    }
+}
+
 }  // namespace ab
 
 extern "C" AB_API size_t ab_peer_allreduce_buffer_bytes(uint32_t capacity_floats)
@@ -164,4 +271,45 @@ extern "C" AB_API int ab_peer_allreduce_error(const void *state, uint32_t *faile
     if (failed_call) *failed_call = h.error;
     if (h.error) return fail(AB_ERR_TIMEOUT, "ab_peer_allreduce: call %u gave up waiting for its peers", h.error);
     return AB_OK;
+}
+
+extern "C" AB_API int ab_peer_allreduce_add_rmsnorm_f32(void *stream, void *const *peer_buffers, void *state,
+                                                        int rank, int world, const float *in,
+                                                        const float *residual, const float *gain,
+                                                        float *sum_out, float *norm_out, uint32_t rows,
+                                                        uint32_t width, uint32_t eps_bits,
+                                                        uint32_t capacity_floats)
+{
+    using namespace ab;
+    if (world < 1 || world > kArMaxRanks || rank < 0 || rank >= world)
+        return fail(AB_ERR_INVALID, "ab_peer_allreduce_add_rmsnorm_f32: rank %d of %d (at most %d ranks)", rank,
+                    world, kArMaxRanks);
+    if (!peer_buffers || !state || !in || !residual || !gain || !sum_out || !norm_out)
+        return fail(AB_ERR_INVALID, "ab_peer_allreduce_add_rmsnorm_f32: NULL argument");
+    const uint32_t cap = (capacity_floats + 3) / 4 * 4;
+    if (rows == 0 || width == 0 || (uint64_t)rows * width > cap)
+        return fail(AB_ERR_INVALID, "ab_peer_allreduce_add_rmsnorm_f32: %u rows of %u against a buffer of %u floats",
+                    rows, width, cap);
+    if (width > (uint32_t)kArThreads * 16 || rows > (uint32_t)sm_count())
+        return fail(AB_ERR_INVALID, "ab_peer_allreduce_add_rmsnorm_f32: Width=%u (at most %u), Rows=%u (at most one "
+                    "CTA per SM, %d); use ab_peer_allreduce_f32 and AddRMSNorm", width, kArThreads * 16, rows,
+                    sm_count());
+    ArPeers peers{};
+    for (int r = 0; r < world; r++) {
+        if (!peer_buffers[r] || reinterpret_cast<uintptr_t>(peer_buffers[r]) % 16)
+            return fail(AB_ERR_INVALID, "ab_peer_allreduce_add_rmsnorm_f32: buffer of rank %d is NULL or unaligned", r);
+        peers.buf[r] = static_cast<float *>(peer_buffers[r]);
+    }
+    float eps;
+    memcpy(&eps, &eps_bits, 4);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ArState *sp = static_cast<ArState *>(state);
+    if (width <= (uint32_t)kArThreads * 4)
+        peer_allreduce_add_rmsnorm_kernel<4><<<rows, kArThreads, 0, st>>>(peers, sp, rank, world, in, residual, gain,
+                                                                          sum_out, norm_out, width, eps, cap);
+    else
+        peer_allreduce_add_rmsnorm_kernel<16><<<rows, kArThreads, 0, st>>>(peers, sp, rank, world, in, residual, gain,
+                                                                           sum_out, norm_out, width, eps, cap);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "ab_peer_allreduce_add_rmsnorm_f32");
 }

@@ -347,8 +347,15 @@ class DecodeEngine:
         norm_u = _u("<IIfI", B, d, cfg.eps, 0)
 
         def add_norm(gain):
-            """x <- x + proj, h <- RMSNorm(x) * gain"""
+            """proj <- sum of proj over the ranks; x <- x + proj; h <- RMSNorm(x) * gain"""
             nonlocal x, x2
+            if self.fuse and self._peer is not None:
+                # the all-reduce's summing stage adds the residual and normalises: one launch
+                self._peer.all_reduce_add_rms_norm(self.proj, x, gain, x2, self.h, cfg.eps)
+                self._count += 1
+                x, x2 = x2, x
+                return
+            self._all_reduce(self.proj)
             if self.fuse:
                 L("AddRMSNorm", [x, self.proj, gain, x2, self.h], norm_u)
                 x, x2 = x2, x
@@ -399,13 +406,11 @@ class DecodeEngine:
               [self.q, self.k_cache[li], self.v_cache[li], self.pages, self.lengths, self.attn],
               _u("<IIIIIIfI", B, self.hq, self.hk, D, cfg.block, self.max_pages, scale, 0))
             self._linear(self.attn, lay.wo, self.proj)
-            self._all_reduce(self.proj)
             add_norm(lay.g2)
             self._parallel([lambda: self._linear(self.h, lay.wg, self.gate),
                             lambda: self._linear(self.h, lay.wu, self.up)])
             L("SwiGLU", [self.gate, self.up, self.act])
             self._linear(self.act, lay.wd, self.proj)
-            self._all_reduce(self.proj)
         add_norm(self.model.g_final)
         self._linear(self.h, self.model.lm_head, self.logits_local)
         if self.shard.tp > 1:

@@ -70,6 +70,18 @@ class PeerAllReduce:
             C.c_void_p(t.data_ptr()), C.c_void_p(t.data_ptr()), t.numel(), self.capacity))
         return t
 
+    def all_reduce_add_rms_norm(self, t, residual, gain, sum_out, norm_out, eps: float, stream=None):
+        """sum_out = residual + all-reduce(t), norm_out = RMSNorm(sum_out) * gain, in one launch;
+        t, residual, sum_out, norm_out are [rows, width] f32, gain [width]."""
+        import struct
+        rows, width = t.shape
+        s = stream if stream is not None else torch.cuda.current_stream(t.device)
+        p = lambda x: C.c_void_p(x.data_ptr())
+        eps_bits = struct.unpack("<I", struct.pack("<f", eps))[0]
+        _lib.check(_lib.lib().ab_peer_allreduce_add_rmsnorm_f32(
+            C.c_void_p(s.cuda_stream), self._ptrs, p(self._state), self.rank, self.world, p(t), p(residual),
+            p(gain), p(sum_out), p(norm_out), rows, width, eps_bits, self.capacity))
+
     def check(self) -> None:
         """Synchronous: raises when a call of this rank gave up waiting for its peers."""
         _lib.check(_lib.lib().ab_peer_allreduce_error(C.c_void_p(self._state.data_ptr()), None))

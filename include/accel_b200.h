@@ -289,6 +289,16 @@ AB_API size_t ab_peer_allreduce_state_bytes(void);
 AB_API int ab_peer_allreduce_f32(void *stream, void *const *peer_buffers, void *state, int rank,
                                  int world, const float *in, float *out, uint32_t n,
                                  uint32_t capacity_floats);
+/* The same call with the decode layer's next two operators done by its summing stage (one CTA per
+ * row): sum_out = residual + all-reduce(in), norm_out = RMSNorm(sum_out) * gain, bit-identical to
+ * ab_peer_allreduce_f32 followed by the AddRMSNorm kernel.  eps_bits is the f32 epsilon's bit
+ * pattern (no float crosses the boundary by value).  Width <= 4096, rows <= one per SM; it counts
+ * as one call of the same sequence as ab_peer_allreduce_f32 (same buffers, same state). */
+AB_API int ab_peer_allreduce_add_rmsnorm_f32(void *stream, void *const *peer_buffers, void *state,
+                                             int rank, int world, const float *in,
+                                             const float *residual, const float *gain, float *sum_out,
+                                             float *norm_out, uint32_t rows, uint32_t width,
+                                             uint32_t eps_bits, uint32_t capacity_floats);
 /* AB_OK, or AB_ERR_TIMEOUT with *failed_call = the 1-based call that gave up (synchronous). */
 AB_API int ab_peer_allreduce_error(const void *state, uint32_t *failed_call);
 

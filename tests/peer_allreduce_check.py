@@ -29,6 +29,21 @@ def main():
             gathered = [torch.empty_like(got) for _ in range(world)]
             dist.all_gather(gathered, got)
             assert all(torch.equal(gathered[0], t) for t in gathered), "ranks disagree on the bits"
+    # the fused form: residual + all-reduce, then RMSNorm, against the plain call and torch
+    from accel_b200 import runtime as rt
+    for rows, width in ((16, 4096), (3, 1000), (16, 256)):
+        g = torch.Generator(device=dev).manual_seed(77 + rank)
+        part = torch.randn(rows, width, device=dev, generator=g)
+        g0 = torch.Generator(device=dev).manual_seed(5)              # the same on every rank
+        res = torch.randn(rows, width, device=dev, generator=g0)
+        gain = torch.rand(width, device=dev, generator=g0) + 0.5
+        s1, n1 = torch.empty_like(part), torch.empty_like(part)
+        ar.all_reduce_add_rms_norm(part, res, gain, s1, n1, 1e-5)
+        summed = ar.all_reduce_(part.clone())
+        s2, n2 = torch.empty_like(part), torch.empty_like(part)
+        rt.launch("AddRMSNorm", [res, summed, gain, s2, n2], rt.row_dims(rows, width, 1e-5))
+        torch.cuda.synchronize()
+        assert torch.equal(s1, s2) and torch.equal(n1, n2), (rows, width)
     # 64 calls per replay, as a decode step makes them
     x = torch.randn(16, 4096, device=dev)
     ref = x.clone()
