@@ -218,6 +218,138 @@ peer_allreduce_add_rmsnorm_kernel(ArPeers peers, ArState *state, int rank, int w
     }
 }
 
+// ---- in-place forms: the input already lies in the rank's own buffer -----------------------------
+// The producer (the row-parallel product) writes its partial result straight into a region of the
+// rank's buffer, so the all-reduce has nothing to copy and no grid-wide rendezvous of its own: the
+// kernel boundary has already completed the region.  One thread signals every peer, every CTA waits
+// for all flags (bounded, as above) and sums its slice of the region over the ranks.
+// The caller owns the regions and must not rewrite one until another all-reduce call has passed in
+// between (a peer may still be reading it until it has signalled its next call): two regions used
+// alternately are enough.
+__device__ __forceinline__ bool signal_and_wait(const ArPeers &peers, int rank, int world, uint32_t e, int *s_fail)
+{
+    if (threadIdx.x == 0) *s_fail = 0;
+    __syncthreads();
+    if (blockIdx.x == 0 && threadIdx.x < (unsigned)world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t *>(peers.buf[threadIdx.x]) + rank, e);
+    }
+    if (threadIdx.x < (unsigned)world) {
+        const uint32_t *flag = reinterpret_cast<const uint32_t *>(peers.buf[rank]) + threadIdx.x;
+        uint32_t polls = 0;
+        while ((int32_t)(ld_acquire_sys(flag) - e) < 0) {
+            if (++polls >= kArSpinLimit) { *s_fail = 1; break; }
+        }
+    }
+    __syncthreads();
+    return *s_fail == 0;
+}
+
+__device__ __forceinline__ void finish_call(ArState *state, uint32_t e)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&state->done, 1u) == gridDim.x - 1) {
+            state->done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(&state->epoch) = e;
+        }
+    }
+}
+
+// offset4: the region's start inside the buffer, in float4 units (flags included)
+__global__ void __launch_bounds__(kArThreads)
+peer_allreduce_inplace_kernel(ArPeers peers, ArState *state, int rank, int world, size_t offset4, float4 *out,
+                              uint32_t n4)
+{
+    __shared__ int s_fail;
+    const uint32_t e = *reinterpret_cast<volatile uint32_t *>(&state->epoch) + 1;
+    if (!signal_and_wait(peers, rank, world, e, &s_fail)) {
+        if (threadIdx.x == 0) atomicExch(&state->error, e);
+    } else {
+        const uint32_t stride = gridDim.x * kArThreads;
+        for (uint32_t i = blockIdx.x * kArThreads + threadIdx.x; i < n4; i += stride) {
+            float4 v[kArMaxRanks];
+#pragma unroll
+            for (int r = 0; r < kArMaxRanks; r++)
+                if (r < world) v[r] = ld_peer(reinterpret_cast<const float4 *>(peers.buf[r]) + offset4 + i);
+            float4 s = v[0];
+#pragma unroll
+            for (int r = 1; r < kArMaxRanks; r++)
+                if (r < world) { s.x += v[r].x; s.y += v[r].y; s.z += v[r].z; s.w += v[r].w; }
+            out[i] = s;
+        }
+    }
+    finish_call(state, e);
+}
+
+// One CTA per row; sum_out = residual + sum over ranks, norm_out = RMSNorm(sum_out) * gain, with the
+// element-to-thread map and the reduction orders of the AddRMSNorm kernel.
+template <int PER>
+__global__ void __launch_bounds__(kArThreads)
+peer_allreduce_inplace_add_rmsnorm_kernel(ArPeers peers, ArState *state, int rank, int world, size_t offset,
+                                          const float *residual, const float *gain, float *sum_out,
+                                          float *norm_out, uint32_t width, float eps)
+{
+    __shared__ int s_fail;
+    __shared__ float red[8];
+    const uint32_t e = *reinterpret_cast<volatile uint32_t *>(&state->epoch) + 1;
+    const size_t base = (size_t)blockIdx.x * width;
+    if (!signal_and_wait(peers, rank, world, e, &s_fail)) {
+        if (threadIdx.x == 0) atomicExch(&state->error, e);
+    } else {
+        float v[PER];
+        {
+            float p[kArMaxRanks][PER];
+#pragma unroll
+            for (int r = 0; r < kArMaxRanks; r++)
+#pragma unroll
+                for (int j = 0; j < PER; j++) {
+                    const uint32_t i = threadIdx.x + kArThreads * j;
+                    p[r][j] = 0.f;
+                    if (r < world && i < width)
+                        asm volatile("ld.relaxed.sys.global.f32 %0, [%1];"
+                                     : "=f"(p[r][j]) : "l"(peers.buf[r] + offset + base + i) : "memory");
+                }
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                float s = p[0][j];
+#pragma unroll
+                for (int r = 1; r < kArMaxRanks; r++)
+                    if (r < world) s += p[r][j];
+                v[j] = s;
+            }
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const uint32_t i = threadIdx.x + kArThreads * j;
+            if (i < width) {
+                v[j] = __fadd_rn(residual[base + i], v[j]);
+                sum_out[base + i] = v[j];
+                acc = fmaf(v[j], v[j], acc);
+            } else {
+                v[j] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sh);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        float total = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) total += red[i];
+        const float scale = (float)(1.0 / sqrt((double)(total / (float)width + eps)));
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const uint32_t i = threadIdx.x + kArThreads * j;
+            if (i < width) norm_out[base + i] = v[j] * scale * gain[i];
+        }
+    }
+    finish_call(state, e);
+}
+
 }  // namespace ab
 
 extern "C" AB_API size_t ab_peer_allreduce_buffer_bytes(uint32_t capacity_floats)
@@ -312,4 +444,82 @@ extern "C" AB_API int ab_peer_allreduce_add_rmsnorm_f32(void *stream, void *cons
                                                                            sum_out, norm_out, width, eps, cap);
     count_launch();
     return check_cuda(cudaGetLastError(), "ab_peer_allreduce_add_rmsnorm_f32");
+}
+
+static int peer_table(const char *what, void *const *peer_buffers, int rank, int world, ab::ArPeers &peers)
+{
+    using namespace ab;
+    if (world < 1 || world > kArMaxRanks || rank < 0 || rank >= world)
+        return fail(AB_ERR_INVALID, "%s: rank %d of %d (at most %d ranks)", what, rank, world, kArMaxRanks);
+    if (!peer_buffers) return fail(AB_ERR_INVALID, "%s: NULL argument", what);
+    for (int r = 0; r < world; r++) {
+        if (!peer_buffers[r] || reinterpret_cast<uintptr_t>(peer_buffers[r]) % 16)
+            return fail(AB_ERR_INVALID, "%s: buffer of rank %d is NULL or unaligned", what, r);
+        peers.buf[r] = static_cast<float *>(peer_buffers[r]);
+    }
+    return AB_OK;
+}
+
+extern "C" AB_API size_t ab_peer_allreduce_region_offset_bytes(uint32_t capacity_floats)
+{   // where caller-owned regions may start: behind the flags and the two halves of the copying form
+    return ab_peer_allreduce_buffer_bytes(capacity_floats);
+}
+
+extern "C" AB_API int ab_peer_allreduce_inplace_f32(void *stream, void *const *peer_buffers, void *state, int rank,
+                                                    int world, size_t region_offset_bytes, float *out, uint32_t n,
+                                                    size_t buffer_bytes)
+{
+    using namespace ab;
+    const char *what = "ab_peer_allreduce_inplace_f32";
+    ArPeers peers{};
+    int rc = peer_table(what, peer_buffers, rank, world, peers);
+    if (rc) return rc;
+    if (!state || !out || reinterpret_cast<uintptr_t>(out) % 16) return fail(AB_ERR_INVALID, "%s: NULL or unaligned argument", what);
+    if (n == 0 || n % 4 || region_offset_bytes % 16 || region_offset_bytes < kArFlagWords * 4 ||
+        region_offset_bytes + (size_t)n * 4 > buffer_bytes)
+        return fail(AB_ERR_INVALID, "%s: %u elements (a multiple of 4) at byte %zu of a buffer of %zu bytes", what,
+                    n, region_offset_bytes, buffer_bytes);
+    const uint32_t n4 = n / 4;
+    uint32_t grid = (n4 + kArThreads - 1) / kArThreads;
+    const uint32_t sms = (uint32_t)sm_count();
+    if (grid > sms) grid = sms;
+    peer_allreduce_inplace_kernel<<<grid, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        peers, static_cast<ArState *>(state), rank, world, region_offset_bytes / 16, reinterpret_cast<float4 *>(out), n4);
+    count_launch();
+    return check_cuda(cudaGetLastError(), what);
+}
+
+extern "C" AB_API int ab_peer_allreduce_inplace_add_rmsnorm_f32(void *stream, void *const *peer_buffers, void *state,
+                                                                int rank, int world, size_t region_offset_bytes,
+                                                                const float *residual, const float *gain,
+                                                                float *sum_out, float *norm_out, uint32_t rows,
+                                                                uint32_t width, uint32_t eps_bits,
+                                                                size_t buffer_bytes)
+{
+    using namespace ab;
+    const char *what = "ab_peer_allreduce_inplace_add_rmsnorm_f32";
+    ArPeers peers{};
+    int rc = peer_table(what, peer_buffers, rank, world, peers);
+    if (rc) return rc;
+    if (!state || !residual || !gain || !sum_out || !norm_out) return fail(AB_ERR_INVALID, "%s: NULL argument", what);
+    if (rows == 0 || width == 0 || region_offset_bytes % 16 || region_offset_bytes < kArFlagWords * 4 ||
+        region_offset_bytes + (size_t)rows * width * 4 > buffer_bytes)
+        return fail(AB_ERR_INVALID, "%s: %u rows of %u at byte %zu of a buffer of %zu bytes", what, rows, width,
+                    region_offset_bytes, buffer_bytes);
+    if (width > (uint32_t)kArThreads * 16 || rows > (uint32_t)sm_count())
+        return fail(AB_ERR_INVALID, "%s: Width=%u (at most %u), Rows=%u (at most one CTA per SM, %d)", what, width,
+                    kArThreads * 16, rows, sm_count());
+    float eps;
+    memcpy(&eps, &eps_bits, 4);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ArState *sp = static_cast<ArState *>(state);
+    const size_t off = region_offset_bytes / 4;
+    if (width <= (uint32_t)kArThreads * 4)
+        peer_allreduce_inplace_add_rmsnorm_kernel<4><<<rows, kArThreads, 0, st>>>(peers, sp, rank, world, off, residual,
+                                                                                  gain, sum_out, norm_out, width, eps);
+    else
+        peer_allreduce_inplace_add_rmsnorm_kernel<16><<<rows, kArThreads, 0, st>>>(peers, sp, rank, world, off, residual,
+                                                                                   gain, sum_out, norm_out, width, eps);
+    count_launch();
+    return check_cuda(cudaGetLastError(), what);
 }

@@ -220,9 +220,14 @@ class DecodeEngine:
         self.logits_local = z(B, len(sh.vocab))
         self.logits = z(B, cfg.vocab) if sh.tp > 1 else self.logits_local
         self.next_tokens = z(B, dt=I32)
+        self._proj = [self.proj, self.proj]      # where wo and down write their partial results
         if sh.tp > 1 and collective == "peer":
+            # the row-parallel products write straight into this rank's peer buffer: two regions
+            # used alternately (wo, down), a third for the vocabulary logits
             from .peer import PeerAllReduce
-            self._peer = PeerAllReduce(B * max(d, cfg.vocab), dev, group)
+            self._peer = PeerAllReduce(4, dev, group, regions=(B * d, B * d, B * cfg.vocab))
+            self._proj = [self._peer.region(0).view(B, d), self._peer.region(1).view(B, d)]
+            self.logits_padded = self._peer.region(2).view(B, cfg.vocab)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.overlap = True          # run the independent linears of a layer side by side
         self._side: List[torch.cuda.Stream] = []
@@ -323,10 +328,6 @@ class DecodeEngine:
 
     def _all_reduce(self, t):
         if self.shard.tp > 1:
-            if self._peer is not None:
-                self._peer.all_reduce_(t)
-                self._count += 1
-                return
             import torch.distributed as dist
             dist.all_reduce(t, group=self.group)
 
@@ -346,21 +347,27 @@ class DecodeEngine:
         scatter = "ScatterRowsF16" if f16 else "ScatterRows"
         norm_u = _u("<IIfI", B, d, cfg.eps, 0)
 
-        def add_norm(gain):
-            """proj <- sum of proj over the ranks; x <- x + proj; h <- RMSNorm(x) * gain"""
+        def add_norm(gain, which):
+            """x <- x + (sum over the ranks of the partial product `which`); h <- RMSNorm(x) * gain"""
             nonlocal x, x2
-            if self.fuse and self._peer is not None:
+            proj = self._proj[which]
+            if self._peer is not None and self.fuse:
                 # the all-reduce's summing stage adds the residual and normalises: one launch
-                self._peer.all_reduce_add_rms_norm(self.proj, x, gain, x2, self.h, cfg.eps)
+                self._peer.all_reduce_region_add_rms_norm(which, x, gain, x2, self.h, cfg.eps)
                 self._count += 1
                 x, x2 = x2, x
                 return
-            self._all_reduce(self.proj)
+            if self._peer is not None:
+                self._peer.all_reduce_region(which, self.proj)
+                self._count += 1
+                proj = self.proj
+            else:
+                self._all_reduce(proj)
             if self.fuse:
-                L("AddRMSNorm", [x, self.proj, gain, x2, self.h], norm_u)
+                L("AddRMSNorm", [x, proj, gain, x2, self.h], norm_u)
                 x, x2 = x2, x
             else:
-                L("ElemAdd", [x, self.proj, x2])
+                L("ElemAdd", [x, proj, x2])
                 x, x2 = x2, x
                 L("RMSNorm", [x, gain, self.h], norm_u)
 
@@ -368,7 +375,7 @@ class DecodeEngine:
             if li == 0:
                 L("RMSNorm", [x, lay.g1, self.h], norm_u)
             else:
-                add_norm(lay.g1)                 # the previous layer's second residual add
+                add_norm(lay.g1, 1)              # the previous layer's second residual add
 
             def q_branch():
                 self._linear(self.h, lay.wq, self.q)
@@ -405,20 +412,26 @@ class DecodeEngine:
             L("AttentionDecodeBatchedF16" if f16 else "AttentionDecodeBatched",
               [self.q, self.k_cache[li], self.v_cache[li], self.pages, self.lengths, self.attn],
               _u("<IIIIIIfI", B, self.hq, self.hk, D, cfg.block, self.max_pages, scale, 0))
-            self._linear(self.attn, lay.wo, self.proj)
-            add_norm(lay.g2)
+            self._linear(self.attn, lay.wo, self._proj[0])
+            add_norm(lay.g2, 0)
             self._parallel([lambda: self._linear(self.h, lay.wg, self.gate),
                             lambda: self._linear(self.h, lay.wu, self.up)])
             L("SwiGLU", [self.gate, self.up, self.act])
-            self._linear(self.act, lay.wd, self.proj)
-        add_norm(self.model.g_final)
+            self._linear(self.act, lay.wd, self._proj[1])
+        add_norm(self.model.g_final, 1)
         self._linear(self.h, self.model.lm_head, self.logits_local)
         if self.shard.tp > 1:
             # each rank owns a column range of the vocabulary: place it in a zeroed full-width
             # buffer and sum across ranks (x + 0 = x exactly), then every rank takes the argmax
-            self.logits.zero_()
-            self.logits[:, self.shard.vocab.start:self.shard.vocab.stop].copy_(self.logits_local)
-            self._all_reduce(self.logits)
+            if self._peer is not None:
+                self.logits_padded.zero_()
+                self.logits_padded[:, self.shard.vocab.start:self.shard.vocab.stop].copy_(self.logits_local)
+                self._peer.all_reduce_region(2, self.logits)
+                self._count += 1
+            else:
+                self.logits.zero_()
+                self.logits[:, self.shard.vocab.start:self.shard.vocab.stop].copy_(self.logits_local)
+                self._all_reduce(self.logits)
         L("SampleArgmax", [self.logits, self.next_tokens], _u("<IIII", cfg.vocab, B, 0, 0))
         self.launches_per_step = self._count                      # dispatches by kernel name
         self.kernel_launches_per_step = count() - kernels0        # CUDA kernels they launched

@@ -46,13 +46,16 @@ def expert_range(experts: int, world: int, rank: int) -> range:
 
 class ExpertParallelFFN:
     def __init__(self, experts: int, d_model: int, ffn: int, device, group=None, seed: int = 77,
-                 std: float = 0.02, ops=rt, quantize=None, init_on_device: bool = False):
+                 std: float = 0.02, ops=rt, quantize=None, init_on_device: bool = False,
+                 parallel: bool = True):
         """init_on_device: draw the random weights with the device's generator (fast at full size;
-        the values then depend on the device type, not on the number of ranks)."""
+        the values then depend on the device type, not on the number of ranks).
+        parallel=False: own every expert and ignore the process group (the single-rank answer)."""
         import torch.distributed as dist
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        on = parallel and dist.is_initialized()
+        self.world = dist.get_world_size(group) if on else 1
+        self.rank = dist.get_rank(group) if on else 0
         self.E, self.d, self.ffn, self.ops = experts, d_model, ffn, ops
         self.device = torch.device(device)
         self.local = expert_range(experts, self.world, self.rank)

@@ -20,15 +20,22 @@ from . import _lib
 
 
 class PeerAllReduce:
-    def __init__(self, capacity_floats: int, device: torch.device, group=None):
+    def __init__(self, capacity_floats: int, device: torch.device, group=None, regions=()):
         """Collective: every rank of `group` (default: the world) constructs one, with the same
-        capacity (the largest element count a call will carry).  Without a process group the
-        object is a single rank (the sum is a copy through the rank's own buffer)."""
+        capacity (the largest element count a copying call will carry) and the same `regions`
+        (element counts of caller-owned parts of the buffer for the in-place calls).  Without a
+        process group the object is a single rank (the sum is a copy through its own buffer)."""
         L = _lib.lib()
+        self.capacity = (int(capacity_floats) + 3) // 4 * 4
+        at = int(L.ab_peer_allreduce_region_offset_bytes(self.capacity))
+        self._region_at = []
+        for n in regions:
+            at = (at + 255) // 256 * 256
+            self._region_at.append((at, int(n)))
+            at += int(n) * 4
+        self.nbytes = nbytes = (at + 255) // 256 * 256
         if not dist.is_initialized():
             self.group, self.rank, self.world = None, 0, 1
-            self.capacity = (int(capacity_floats) + 3) // 4 * 4
-            nbytes = int(L.ab_peer_allreduce_buffer_bytes(self.capacity))
             self._buf = torch.zeros(nbytes // 4, dtype=torch.float32, device=device)
             self._ptrs = (C.c_void_p * 1)(self._buf.data_ptr())
             self._state = torch.zeros(int(L.ab_peer_allreduce_state_bytes()) // 4, dtype=torch.int32, device=device)
@@ -41,8 +48,6 @@ class PeerAllReduce:
         self.world = dist.get_world_size(self.group)
         if self.world > 8:
             raise _lib.AccelError(_lib.AB_ERR_INVALID, f"PeerAllReduce: {self.world} ranks (at most 8)")
-        self.capacity = (int(capacity_floats) + 3) // 4 * 4
-        nbytes = int(L.ab_peer_allreduce_buffer_bytes(self.capacity))
         try:
             symm.set_backend("CUDA")
         except Exception:
@@ -69,6 +74,37 @@ class PeerAllReduce:
             C.c_void_p(s.cuda_stream), self._ptrs, C.c_void_p(self._state.data_ptr()), self.rank, self.world,
             C.c_void_p(t.data_ptr()), C.c_void_p(t.data_ptr()), t.numel(), self.capacity))
         return t
+
+    def region(self, i: int) -> torch.Tensor:
+        """Region i of this rank's own buffer: write the partial result here (it is an ordinary
+        device tensor), then call one of the in-place forms."""
+        at, n = self._region_at[i]
+        return self._buf[at // 4:at // 4 + n]
+
+    def all_reduce_region(self, i: int, out: torch.Tensor, stream=None) -> torch.Tensor:
+        """out = sum over the ranks of region i (out.numel() elements, a multiple of 4)."""
+        at, n = self._region_at[i]
+        if out.numel() > n or out.dtype != torch.float32 or not out.is_contiguous():
+            raise _lib.AccelError(_lib.AB_ERR_INVALID, "PeerAllReduce: out must be contiguous f32 within the region")
+        s = stream if stream is not None else torch.cuda.current_stream(out.device)
+        _lib.check(_lib.lib().ab_peer_allreduce_inplace_f32(
+            C.c_void_p(s.cuda_stream), self._ptrs, C.c_void_p(self._state.data_ptr()), self.rank, self.world, at,
+            C.c_void_p(out.data_ptr()), out.numel(), self.nbytes))
+        return out
+
+    def all_reduce_region_add_rms_norm(self, i: int, residual, gain, sum_out, norm_out, eps: float, stream=None):
+        """sum_out = residual + (sum over the ranks of region i), norm_out = RMSNorm(sum_out) * gain."""
+        import struct
+        at, n = self._region_at[i]
+        rows, width = residual.shape
+        if rows * width > n:
+            raise _lib.AccelError(_lib.AB_ERR_INVALID, "PeerAllReduce: the rows do not fit the region")
+        s = stream if stream is not None else torch.cuda.current_stream(residual.device)
+        p = lambda x: C.c_void_p(x.data_ptr())
+        eps_bits = struct.unpack("<I", struct.pack("<f", eps))[0]
+        _lib.check(_lib.lib().ab_peer_allreduce_inplace_add_rmsnorm_f32(
+            C.c_void_p(s.cuda_stream), self._ptrs, p(self._state), self.rank, self.world, at, p(residual), p(gain),
+            p(sum_out), p(norm_out), rows, width, eps_bits, self.nbytes))
 
     def all_reduce_add_rms_norm(self, t, residual, gain, sum_out, norm_out, eps: float, stream=None):
         """sum_out = residual + all-reduce(t), norm_out = RMSNorm(sum_out) * gain, in one launch;

@@ -299,6 +299,22 @@ AB_API int ab_peer_allreduce_add_rmsnorm_f32(void *stream, void *const *peer_buf
                                              const float *residual, const float *gain, float *sum_out,
                                              float *norm_out, uint32_t rows, uint32_t width,
                                              uint32_t eps_bits, uint32_t capacity_floats);
+/* In-place forms: the rank's partial result already lies in a region of its own buffer (the
+ * producing kernel wrote it there), so nothing is copied and the call is a signal, a bounded wait
+ * and the sum.  Regions start at or behind ab_peer_allreduce_region_offset_bytes(capacity) and are
+ * the caller's to lay out, at the same offset on every rank; a region must not be rewritten until
+ * another all-reduce call of this sequence has been made in between (a peer may still be reading
+ * it until it has signalled its next call): two regions used alternately are enough.  buffer_bytes
+ * is the size every rank allocated.  The calls belong to the same sequence as the copying forms. */
+AB_API size_t ab_peer_allreduce_region_offset_bytes(uint32_t capacity_floats);
+AB_API int ab_peer_allreduce_inplace_f32(void *stream, void *const *peer_buffers, void *state, int rank,
+                                         int world, size_t region_offset_bytes, float *out, uint32_t n,
+                                         size_t buffer_bytes);
+AB_API int ab_peer_allreduce_inplace_add_rmsnorm_f32(void *stream, void *const *peer_buffers, void *state,
+                                                     int rank, int world, size_t region_offset_bytes,
+                                                     const float *residual, const float *gain,
+                                                     float *sum_out, float *norm_out, uint32_t rows,
+                                                     uint32_t width, uint32_t eps_bits, size_t buffer_bytes);
 /* AB_OK, or AB_ERR_TIMEOUT with *failed_call = the 1-based call that gave up (synchronous). */
 AB_API int ab_peer_allreduce_error(const void *state, uint32_t *failed_call);
 

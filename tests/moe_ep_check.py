@@ -24,15 +24,8 @@ def main():
     x = torch.randn(rows, D, generator=g).to(dev)
     expert = torch.randint(0, E, (rows,), generator=g, dtype=torch.int32).to(dev)
     got = ep.forward(x, expert)
-    # the single-rank answer: a second object that owns every expert (no process group in its eyes)
-    alone = object.__new__(moe.ExpertParallelFFN)
-    alone.group, alone.world, alone.rank = None, 1, 0
-    alone.E, alone.d, alone.ffn, alone.ops, alone.device = E, D, FFN, ep.ops, dev
-    alone.local = range(E)
-    from accel_b200 import quant
-    alone.gate = alone._make(21, 0, D, FFN, 0.05, quant.int4_quantize_device)
-    alone.up = alone._make(21, 1, D, FFN, 0.05, quant.int4_quantize_device)
-    alone.down = alone._make(21, 2, FFN, D, 0.05, quant.int4_quantize_device)
+    # the single-rank answer: a second object that owns every expert and ignores the process group
+    alone = moe.ExpertParallelFFN(E, D, FFN, dev, seed=21, std=0.05, parallel=False)
     want = alone.forward(x, expert)
     torch.cuda.synchronize()
     assert torch.equal(got, want), float((got - want).abs().max())

@@ -15,7 +15,7 @@ def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
-    ar = PeerAllReduce(16 * 32000, dev)
+    ar = PeerAllReduce(16 * 32000, dev, regions=(16 * 4096, 16 * 4096, 1000))
     worst = 0.0
     for n in (4, 65536, 16 * 32000, 1000 * 4):
         for it in range(5):
@@ -44,6 +44,24 @@ def main():
         rt.launch("AddRMSNorm", [res, summed, gain, s2, n2], rt.row_dims(rows, width, 1e-5))
         torch.cuda.synchronize()
         assert torch.equal(s1, s2) and torch.equal(n1, n2), (rows, width)
+    # the in-place forms: the partial result is written into a region of the rank's own buffer
+    for which, (rows, width) in ((0, (16, 4096)), (1, (5, 1000)), (0, (16, 4096))):
+        g = torch.Generator(device=dev).manual_seed(300 + 10 * which + rank)
+        part = torch.randn(rows, width, device=dev, generator=g)
+        g0 = torch.Generator(device=dev).manual_seed(6)
+        res = torch.randn(rows, width, device=dev, generator=g0)
+        gain = torch.rand(width, device=dev, generator=g0) + 0.5
+        ar.region(which)[:rows * width].copy_(part.view(-1))
+        plain = ar.all_reduce_region(which, torch.empty(rows * width, device=dev)).view(rows, width)
+        other = 1 - which                          # a region is rewritten only after another call
+        ar.region(other)[:rows * width].copy_(part.view(-1))
+        s1, n1 = torch.empty_like(part), torch.empty_like(part)
+        ar.all_reduce_region_add_rms_norm(other, res, gain, s1, n1, 1e-5)
+        copied = ar.all_reduce_(part.clone())
+        s2, n2 = torch.empty_like(part), torch.empty_like(part)
+        rt.launch("AddRMSNorm", [res, copied, gain, s2, n2], rt.row_dims(rows, width, 1e-5))
+        torch.cuda.synchronize()
+        assert torch.equal(plain, copied) and torch.equal(s1, s2) and torch.equal(n1, n2), (which, rows, width)
     # 64 calls per replay, as a decode step makes them
     x = torch.randn(16, 4096, device=dev)
     ref = x.clone()
@@ -94,10 +112,25 @@ def main():
 
     t_peer = per_call_us(lambda y: ar.all_reduce_(y))
     t_nccl = per_call_us(lambda y: dist.all_reduce(y))
+    gain = torch.ones(4096, device=dev)
+    s_out, n_out = torch.empty(16, 4096, device=dev), torch.empty(16, 4096, device=dev)
+    flip = [0]
+
+    def fused_inplace(y):
+        flip[0] ^= 1
+        ar.all_reduce_region_add_rms_norm(flip[0], y, gain, s_out, n_out, 1e-5)
+
+    def nccl_then_norm(y):
+        dist.all_reduce(y)
+        rt.launch("AddRMSNorm", [y, y, gain, s_out, n_out], rt.row_dims(16, 4096, 1e-5))
+
+    t_fused = per_call_us(fused_inplace)
+    t_chain = per_call_us(nccl_then_norm)
     ar.check()
     if rank == 0:
         print(f"OK world={world} worst_rel_err={worst:.3e} replayed_rel_err={err:.3e} "
-              f"us_per_256KiB_call peer={t_peer:.2f} nccl={t_nccl:.2f}", flush=True)
+              f"us_per_256KiB_call peer_copying={t_peer:.2f} nccl={t_nccl:.2f} "
+              f"peer_inplace_add_rmsnorm={t_fused:.2f} nccl_then_add_rmsnorm={t_chain:.2f}", flush=True)
     assert worst < 1e-5 and err < 1e-4
     dist.barrier()
     torch.cuda.synchronize()
