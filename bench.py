@@ -283,8 +283,22 @@ def run_b200(args):
     model = dec.DecodeModel(cfg, shard, dev, seed=1234)
     B, ctx = args.batch, args.context
     total_steps = 2 * (args.steps + args.warmup) + 8
-    engine = dec.DecodeEngine(model, B, max_context=ctx + total_steps + 16, group=group,
-                              collective=args.collective)
+    collective, why = (args.collective if world > 1 else "none"), ""
+    engine = None
+    if collective == "peer":
+        # mapping the peers' buffers is a collective of its own; if any rank cannot, all use NCCL
+        try:
+            engine = dec.DecodeEngine(model, B, max_context=ctx + total_steps + 16, group=group,
+                                      collective="peer")
+            ok = 1
+        except Exception as e:                     # noqa: BLE001 - reported in the JSON line
+            ok, why = 0, f"{type(e).__name__}: {e}"[:160]
+        flag = torch.tensor([ok], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 0:
+            collective, engine = f"nccl (peer memory unavailable{': ' + why if why else ' on another rank'})", None
+    if engine is None:
+        engine = dec.DecodeEngine(model, B, max_context=ctx + total_steps + 16, group=group, collective="nccl")
     engine.overlap = not args.no_overlap
     log = (lambda m: print(f"[rank {rank}] {m}", file=sys.stderr, flush=True)) if args.verbose else (lambda m: None)
     log("engine built")
@@ -437,6 +451,16 @@ def run_b200(args):
                          f"lm_head and argmax once ({t_head:.3f} s), scaled to 32 layers; C "
                          "restatement of accel's CPU kernels, OpenMP over workgroups"}
 
+    # a peer all-reduce that gave up waiting (bounded) left wrong sums behind: say so
+    peer_timeouts = 0
+    if getattr(engine, "_peer", None) is not None:
+        try:
+            engine._peer.check()
+        except Exception:                          # noqa: BLE001
+            peer_timeouts = 1
+        t = torch.tensor([peer_timeouts], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+        peer_timeouts = int(t.item())
     if rank == 0:
         weight_bytes = model.int4_bytes()
         line = {
@@ -444,7 +468,7 @@ def run_b200(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch": B, "context": ctx, "layers": cfg.layers,
-                       "kv_cache": args.kv, "parallelism": f"tp{world}", "collective": (args.collective if world > 1 else "none"),
+                       "kv_cache": args.kv, "parallelism": f"tp{world}", "collective": collective,
                        "l2": "inputs larger than L2: each step streams "
                              f"{weight_bytes / 1e9:.2f} GB of int4 weights and "
                              f"{kv_bytes_first / 1e9:.1f} GB of K/V per rank",
@@ -459,6 +483,7 @@ def run_b200(args):
                          "gbs": (weight_bytes + kv_bytes_first) / (ms_per_step * 1e-3) / 1e9,
                          "frac_of_peak": (weight_bytes + kv_bytes_first) / (ms_per_step * 1e-3) / 1e9 / peak},
             "int4_gemv": gemv,
+            "peer_allreduce_ranks_timed_out": peer_timeouts,
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
