@@ -230,10 +230,8 @@ __device__ __forceinline__ bool signal_and_wait(const ArPeers &peers, int rank, 
 {
     if (threadIdx.x == 0) *s_fail = 0;
     __syncthreads();
-    if (blockIdx.x == 0 && threadIdx.x < (unsigned)world) {
-        __threadfence_system();
+    if (blockIdx.x == 0 && threadIdx.x < (unsigned)world)      // the release is cumulative at system scope
         st_release_sys(reinterpret_cast<uint32_t *>(peers.buf[threadIdx.x]) + rank, e);
-    }
     if (threadIdx.x < (unsigned)world) {
         const uint32_t *flag = reinterpret_cast<const uint32_t *>(peers.buf[rank]) + threadIdx.x;
         uint32_t polls = 0;
@@ -299,26 +297,28 @@ peer_allreduce_inplace_add_rmsnorm_kernel(ArPeers peers, ArState *state, int ran
     if (!signal_and_wait(peers, rank, world, e, &s_fail)) {
         if (threadIdx.x == 0) atomicExch(&state->error, e);
     } else {
-        float v[PER];
-        {
-            float p[kArMaxRanks][PER];
-#pragma unroll
-            for (int r = 0; r < kArMaxRanks; r++)
-#pragma unroll
-                for (int j = 0; j < PER; j++) {
-                    const uint32_t i = threadIdx.x + kArThreads * j;
-                    p[r][j] = 0.f;
-                    if (r < world && i < width)
-                        asm volatile("ld.relaxed.sys.global.f32 %0, [%1];"
-                                     : "=f"(p[r][j]) : "l"(peers.buf[r] + offset + base + i) : "memory");
-                }
+        // rank r + 1's row is in flight while rank r's is added: ranks in order, one NVLink round
+        // trip plus the issue time of the loads
+        float v[PER], cur[PER], nxt[PER];
+        auto fetch = [&](float (&dst)[PER], int r) {
 #pragma unroll
             for (int j = 0; j < PER; j++) {
-                float s = p[0][j];
+                const uint32_t i = threadIdx.x + kArThreads * j;
+                dst[j] = 0.f;
+                if (i < width)
+                    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];"
+                                 : "=f"(dst[j]) : "l"(peers.buf[r] + offset + base + i) : "memory");
+            }
+        };
+        fetch(cur, 0);
 #pragma unroll
-                for (int r = 1; r < kArMaxRanks; r++)
-                    if (r < world) s += p[r][j];
-                v[j] = s;
+        for (int j = 0; j < PER; j++) v[j] = 0.f;
+        for (int r = 0; r < world; r++) {
+            if (r + 1 < world) fetch(nxt, r + 1);
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                v[j] = r == 0 ? cur[j] : v[j] + cur[j];
+                cur[j] = nxt[j];
             }
         }
         float acc = 0.f;
