@@ -127,3 +127,20 @@ def test_fused_support_kernels_equal_the_chain_of_reference_operators(cache):
     for li in range(cfg.layers):
         assert torch.equal(fused.k_cache[li], chain.k_cache[li])
         assert torch.equal(fused.v_cache[li], chain.v_cache[li])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_tensor_parallel_step_on_the_gpus_matches_one_gpu():
+    """Both collectives (NCCL; the peer all-reduce that also adds the residual and normalises),
+    eager and from a replayed graph, against the unsharded step (child processes under torchrun)."""
+    import os
+    import subprocess
+    import sys
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                          "--master-addr", "127.0.0.1", "--master-port", "29617", os.path.join(here, "tp_check.py")],
+                         env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-3000:])
+    assert "OK world=" in out.stdout
