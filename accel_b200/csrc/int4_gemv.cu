@@ -86,8 +86,9 @@ int4_row_kernel(const float *__restrict__ a, const uint4 *__restrict__ bq, const
     constexpr int kRowsPerInstr = kRowThreads / kLanes;    // rows per CTA-wide load
     constexpr int kCols = 128 * W;
     constexpr int kMetaIt = kRowMaxKc / kRowThreads;
-    __shared__ float s_a[kRowMaxKc];                       // activations of the K range
-    __shared__ __half2 s_sz[W][kRowMaxKc];                 // {scale, zero} per group and row
+    __shared__ unsigned short s_cs[W][kRowMaxKc];          // f16(a s) per group and row of the K range
+    __shared__ float s_zw[W][kRowThreads / 32];            // per-warp parts of the correction
+    __shared__ float s_zc[W];                              // sum_k (a s)_f16 (16 + z): subtracted at the end
     __shared__ __align__(16) float s_red[kRowsPerInstr][kCols];
     __shared__ __align__(16) float s_sum[kCols];           // this CTA's partial row, read by the cluster
     const int tid = threadIdx.x, rl = tid / kLanes, c = tid % kLanes;
@@ -128,59 +129,76 @@ int4_row_kernel(const float *__restrict__ a, const uint4 *__restrict__ bq, const
         const uint32_t r = rl + u * kRowsPerInstr;
         cw[u] = (col_on && r < nrows) ? ldg_row(base + (size_t)r * row_u4) : make_uint4(0, 0, 0, 0);
     }
+    // f16(a s) once per (row, group), not once per thread that uses it; the correction
+    // sum_k (a s)_f16 (16 + z) (or -a z where the scale is 0) is summed here too, in a fixed order
+    {
+        float zpart[W];
 #pragma unroll
-    for (int i = 0; i < kMetaIt; i++) {
-        const uint32_t r = tid + i * kRowThreads;
-        if (r < nrows) {
-            s_a[r] = av[i];
+        for (int w = 0; w < W; w++) zpart[w] = 0.f;
 #pragma unroll
-            for (int w = 0; w < W; w++)
-                s_sz[w][r] = __halves2half2(__ushort_as_half((unsigned short)(sv[i] >> (16 * w))),
-                                            __ushort_as_half((unsigned short)(zv[i] >> (16 * w))));
+        for (int i = 0; i < kMetaIt; i++) {
+            const uint32_t r = tid + i * kRowThreads;
+            if (r < nrows) {
+#pragma unroll
+                for (int w = 0; w < W; w++) {
+                    const float sc = __half2float(__ushort_as_half((unsigned short)(sv[i] >> (16 * w))));
+                    const float zr = __half2float(__ushort_as_half((unsigned short)(zv[i] >> (16 * w))));
+                    const __half csh = __float2half_rn(av[i] * sc);
+                    s_cs[w][r] = __half_as_ushort(csh);
+                    zpart[w] = sc == 0.f ? fmaf(-av[i], zr, zpart[w]) : fmaf(__half2float(csh), 16.f + zr, zpart[w]);
+                }
+            }
+        }
+#pragma unroll
+        for (int w = 0; w < W; w++) {
+#pragma unroll
+            for (int sh = 16; sh > 0; sh >>= 1) zpart[w] += __shfl_xor_sync(0xffffffffu, zpart[w], sh);
+            if ((tid & 31) == 0) s_zw[w][tid >> 5] = zpart[w];
         }
     }
     __syncthreads();
+    if (tid < W) s_zc[tid] = (s_zw[tid][0] + s_zw[tid][1]) + (s_zw[tid][2] + s_zw[tid][3]);
 
-    // 2. the loop: the next batch of loads goes out before this one is used
+    // 2. the loop: two register batches used in turn; a batch's loads go out before the other is used
     float acc[32];
 #pragma unroll
     for (int i = 0; i < 32; i++) acc[i] = 0.f;
-    float zc = 0.f;
     const int grp = c >> 2;                                  // which of the tile's groups
     const uint32_t magic = opaque(0x4C004C00u);
-
-    for (uint32_t r0 = 0; r0 < nrows; r0 += kRowsPerInstr * kRowUnroll) {
-        uint4 nxt[kRowUnroll];
+    constexpr uint32_t kStep = kRowsPerInstr * kRowUnroll;
+    auto fetch = [&](uint4 (&dst)[kRowUnroll], uint32_t r0) {
 #pragma unroll
         for (int u = 0; u < kRowUnroll; u++) {
-            const uint32_t r = r0 + kRowsPerInstr * kRowUnroll + rl + u * kRowsPerInstr;
-            nxt[u] = (col_on && r < nrows) ? ldg_row(base + (size_t)r * row_u4) : make_uint4(0, 0, 0, 0);
+            const uint32_t r = r0 + rl + u * kRowsPerInstr;
+            dst[u] = (col_on && r < nrows) ? ldg_row(base + (size_t)r * row_u4) : make_uint4(0, 0, 0, 0);
         }
+    };
+    auto consume = [&](const uint4 (&src)[kRowUnroll], uint32_t r0) {
 #pragma unroll
         for (int u = 0; u < kRowUnroll; u++) {
             const uint32_t r = r0 + rl + u * kRowsPerInstr;
             if (r < nrows) {
-                const float2 sz = __half22float2(s_sz[grp][r]);
-                const float x = s_a[r];
-                const __half csh = __float2half_rn(x * sz.x);
-                // what is subtracted at the end: (a s)_f16 (16 + z), or -a z where the scale is 0
-                zc = sz.x == 0.f ? fmaf(-x, sz.y, zc) : fmaf(__half2float(csh), 16.f + sz.y, zc);
-                const unsigned short cs = __half_as_ushort(csh);
-                fma_word(cw[u].x, cs, magic, acc);
-                fma_word(cw[u].y, cs, magic, acc + 8);
-                fma_word(cw[u].z, cs, magic, acc + 16);
-                fma_word(cw[u].w, cs, magic, acc + 24);
+                const unsigned short cs = s_cs[grp][r];
+                fma_word(src[u].x, cs, magic, acc);
+                fma_word(src[u].y, cs, magic, acc + 8);
+                fma_word(src[u].z, cs, magic, acc + 16);
+                fma_word(src[u].w, cs, magic, acc + 24);
             }
         }
-#pragma unroll
-        for (int u = 0; u < kRowUnroll; u++) cw[u] = nxt[u];
+    };
+    uint4 cw2[kRowUnroll];
+    for (uint32_t r0 = 0; r0 < nrows; r0 += 2 * kStep) {
+        fetch(cw2, r0 + kStep);
+        consume(cw, r0);
+        fetch(cw, r0 + 2 * kStep);
+        consume(cw2, r0 + kStep);
     }
 
     // 3. the row-lanes hold partial sums of the same columns: through shared memory (each 16-byte
     //    store rotated inside its 32-column block, so that the lanes of a row hit different banks)
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
-        const float4 v = make_float4(acc[j] - zc, acc[j + 1] - zc, acc[j + 2] - zc, acc[j + 3] - zc);
+        const float4 v = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
         *reinterpret_cast<float4 *>(&s_red[rl][c * 32 + ((j + 4 * c) & 31)]) = v;
     }
     __syncthreads();
@@ -189,6 +207,7 @@ int4_row_kernel(const float *__restrict__ a, const uint4 *__restrict__ bq, const
         float v = 0.f;
 #pragma unroll
         for (int i = 0; i < kRowsPerInstr; i++) v += s_red[i][at];
+        v -= s_zc[col >> 7];
         if (splits == 1) {
             if (g0 * kGroup + col < N) out[g0 * kGroup + col] = v;
         } else {

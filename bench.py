@@ -195,6 +195,75 @@ def run_linear(args):
                       "kernel": rt.last_selection()}))
 
 
+def run_attention(args):
+    """Config 3: paged-KV decode attention on its own: 32 sequences, one query token each, 32 query
+    heads over 8 KV heads (GQA), head dim 128, block 16, context lengths uniform in [512, 4096],
+    block table = disjoint runs of a seeded permutation of a shared pool.  Several caches (larger
+    than L2 together) are rotated inside one CUDA graph; f32 (the reference's batched kernel) and
+    f16 (this library's extension) caches.  Prints one JSON line."""
+    import numpy as np
+    import torch
+
+    from accel_b200 import runtime as rt
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    B, qH, kvH, D, block, max_pages = 32, 32, 8, 128, 16, 256
+    rng = np.random.default_rng(3)
+    lengths = rng.integers(512, 4097, B).astype(np.int64)
+    need = (lengths + block - 1) // block
+    pool = int(need.sum()) + 8
+    perm = rng.permutation(pool).astype(np.int32)
+    pages = np.zeros((B, max_pages), np.int32)
+    at = 0
+    for i, n in enumerate(need):
+        pages[i, :n] = perm[at:at + n]
+        at += n
+    peak, src = measured_peaks()
+    scale = float(np.float32(1.0) / np.float32(np.sqrt(D)))
+    u = rt.batched_dims(B, qH, kvH, D, block, max_pages, scale)
+    q = torch.randn(B, qH, D, device=dev)
+    out = torch.empty(B, qH, D, device=dev)
+    pg = torch.from_numpy(pages).to(dev)
+    ln = torch.from_numpy(lengths.astype(np.int32)).to(dev)
+    result = {}
+    for dt, name in ((torch.float32, "AttentionDecodeBatched"), (torch.float16, "AttentionDecodeBatchedF16")):
+        caches = [(torch.randn(pool * block, kvH, D, device=dev).to(dt), torch.randn(pool * block, kvH, D, device=dev).to(dt))
+                  for _ in range(4)]
+
+        def body():
+            for k, v in caches:
+                rt.launch(name, [q, k, v, pg, ln, out], u)
+
+        st = torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st):
+            body()
+            st.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                body()
+        torch.cuda.current_stream().wait_stream(st)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            g.replay()
+        e1.record()
+        e1.synchronize()
+        us = e0.elapsed_time(e1) / (10 * len(caches)) * 1e3
+        esz = 2 if dt == torch.float16 else 4
+        nbytes = int(2 * kvH * D * esz * lengths.sum() + 2 * B * qH * D * 4 + pages.size * 4 + B * 4)
+        result["f16" if esz == 2 else "f32"] = {"us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3,
+                                                "frac_of_hbm_peak": nbytes / us / 1e3 / peak}
+        del caches
+    print(json.dumps({"metric": "paged decode attention", "config": {
+        "workload": "32 sequences x 1 query, 32 q heads / 8 KV heads, head dim 128, block 16, "
+                    "context lengths uniform in [512, 4096] (seed 3)", "positions": int(lengths.sum())},
+        "peak_source": src, **result}))
+
+
 def run_moe(args):
     """Config 5: the expert half of a MoE layer, 8 experts, 4096 tokens x top-2 = 8192 routed rows,
     d 4096, expert FFN 14336 (gate, up, SwiGLU, down), int4 experts; per-expert counts from a
@@ -517,6 +586,8 @@ def main():
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="all-reduce of the row-parallel products at N > 1: this library's one-shot "
                          "kernel over NVLink peer memory, or NCCL")
+    ap.add_argument("--attention", action="store_true",
+                    help="time the paged decode attention of config 3 on its own, f32 and f16 caches")
     ap.add_argument("--moe", action="store_true",
                     help="time the expert-parallel grouped int4 FFN (config 5) instead of the decode step")
     ap.add_argument("--linear", default=None, metavar="M,K,N",
@@ -524,6 +595,8 @@ def main():
     args = ap.parse_args()
     if args.linear:
         run_linear(args)
+    elif args.attention:
+        run_attention(args)
     elif args.moe:
         run_moe(args)
     elif args.impl == "reference":
