@@ -19,6 +19,8 @@
 // tokens and tokens with no position write zeros.
 #include <math_constants.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ab {
@@ -232,6 +234,197 @@ attn_partition_kernel(const AttnParams p)
     }
 }
 
+// ---- grouped-query heads: half a warp per position ------------------------------------------------
+// With G query heads sharing a KV head, the warp-per-position form spends most of its issue slots on
+// shuffles: 5 per (position, head) to sum a dot product over 32 lanes.  Here 16 lanes own a position
+// (8 elements each, 32 contiguous bytes of an f32 row), a warp works on two positions at once, and
+// the G partial dot products of a lane are summed by a butterfly that halves the number of values a
+// lane carries at every step, then handed back to all 16 lanes: G + log2(16) + 1 shuffles for two
+// positions x G heads instead of 10 G.  Each half-warp carries its own running (max, sum, output);
+// the halves are merged with the warps.
+template <typename T> struct Vec8;
+template <> struct Vec8<float> {
+    static __device__ __forceinline__ void load(const float *p, float (&v)[8])
+    {
+        asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "l"(p));
+        asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(p + 4));
+    }
+};
+template <> struct Vec8<__half> {
+    static __device__ __forceinline__ void load(const __half *p, float (&v)[8])
+    {
+        uint4 raw;
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "l"(p));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+};
+
+static constexpr int kStreams = 2 * kWarps;      // half-warps: independent running softmax states
+static constexpr int kGqaUnroll = 2;             // steps per iteration: 4 positions per warp in flight
+
+// grid = (parts, kv_heads, rows); head_dim a multiple of 8, at most 128
+template <typename T, int G>
+__global__ void __launch_bounds__(kAttnThreads)
+attn_partition_gqa_kernel(const AttnParams p)
+{
+    const uint32_t part = blockIdx.x, row = blockIdx.z, kvh = blockIdx.y;
+    const uint32_t hq0 = kvh * G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sl = lane & 15, half = lane >> 4;
+    const uint32_t D = p.head_dim;
+    const bool lane_on = (uint32_t)sl * 8 < D;
+
+    const RowView rv = row_view(p, row);
+    const uint32_t begin = part * kPartition;
+    if (rv.zero) {
+        if (part == 0) {
+            for (uint32_t i = threadIdx.x; i < G * D; i += kAttnThreads)
+                p.out[((size_t)row * p.q_heads + hq0) * D + i] = 0.f;
+        }
+        return;
+    }
+    if (begin >= rv.len && !(part == 0)) return;     // partition 0 always reports (len 0 -> NaN)
+    const uint32_t end = min(rv.len, begin + kPartition);
+
+    const T *kc = reinterpret_cast<const T *>(p.k);
+    const T *vc = reinterpret_cast<const T *>(p.v);
+    const size_t row_stride = (size_t)p.kv_heads * D;
+    const size_t head_off = (size_t)kvh * D + (size_t)sl * 8;
+
+    float qv[G][8];
+#pragma unroll
+    for (int g = 0; g < G; g++)
+#pragma unroll
+        for (int e = 0; e < 8; e++)
+            qv[g][e] = lane_on ? p.q[((size_t)row * p.q_heads + hq0 + g) * D + sl * 8 + e] * p.scale_log2 : 0.f;
+
+    float m[G], l[G], o[G][8];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        m[g] = kNegBig; l[g] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[g][e] = 0.f;
+    }
+
+    // position of (step u, half h) in an iteration: j0 + kWarps * (2u + h)
+    for (uint32_t j0 = begin + warp; j0 < end; j0 += kWarps * 2 * kGqaUnroll) {
+        float kv[kGqaUnroll][8], vv[kGqaUnroll][8];
+        bool ok[kGqaUnroll];
+#pragma unroll
+        for (int u = 0; u < kGqaUnroll; u++) {
+            const uint32_t j = j0 + kWarps * (2 * u + half);
+            ok[u] = j < end;
+#pragma unroll
+            for (int e = 0; e < 8; e++) kv[u][e] = vv[u][e] = 0.f;
+            if (ok[u] && lane_on) {
+                const size_t phys = p.mode == kContiguous
+                                        ? (size_t)j
+                                        : (size_t)__ldg(rv.pages + j / p.block) * p.block + j % p.block;
+                const size_t off = phys * row_stride + head_off;
+                Vec8<T>::load(kc + off, kv[u]);
+                Vec8<T>::load(vc + off, vv[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kGqaUnroll; u++) {
+            // partial dot products of this lane's 8 elements, one per head
+            float s[G];
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                float a = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; e++) a = fmaf(qv[g][e], kv[u][e], a);
+                s[g] = a;
+            }
+            // butterfly over the 16 lanes: every step halves the values a lane carries
+            int sh = 8;
+#pragma unroll
+            for (int n = G; n > 1; n >>= 1, sh >>= 1) {
+                const bool upper = (lane & sh) != 0;
+#pragma unroll
+                for (int i = 0; i < n / 2; i++) {
+                    const float send = upper ? s[i] : s[i + n / 2];
+                    const float keep = upper ? s[i + n / 2] : s[i];
+                    s[i] = keep + __shfl_xor_sync(0xffffffffu, send, sh);
+                }
+            }
+#pragma unroll
+            for (; sh >= 1; sh >>= 1) s[0] += __shfl_xor_sync(0xffffffffu, s[0], sh);
+            // head g's sum now sits in the lanes whose top bits spell g: hand it to all 16
+            float sc[G];
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                int src = 0, bit = 8;
+#pragma unroll
+                for (int n = G; n > 1; n >>= 1, bit >>= 1)
+                    if (g & (n >> 1)) src |= bit;
+                sc[g] = __shfl_sync(0xffffffffu, s[0], (lane & 16) | src);
+            }
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                if (ok[u]) {                         // uniform over the half-warp
+                    const float mx = fmaxf(m[g], sc[g]);
+                    const float alpha = exp2f(m[g] - mx), e = exp2f(sc[g] - mx);
+                    m[g] = mx;
+                    l[g] = fmaf(l[g], alpha, e);
+#pragma unroll
+                    for (int q = 0; q < 8; q++) o[g][q] = fmaf(e, vv[u][q], o[g][q] * alpha);
+                }
+            }
+        }
+    }
+
+    // merge the half-warps of every warp
+    __shared__ float sm_m[kStreams][G], sm_l[kStreams][G];
+    __shared__ float4 sm_o[kStreams][G][32];
+    const int stream = warp * 2 + half;
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        if (sl == 0) { sm_m[stream][g] = m[g]; sm_l[stream][g] = l[g]; }
+        sm_o[stream][g][2 * sl] = make_float4(o[g][0], o[g][1], o[g][2], o[g][3]);
+        sm_o[stream][g][2 * sl + 1] = make_float4(o[g][4], o[g][5], o[g][6], o[g][7]);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const bool out_on = (uint32_t)lane * 4 < D;
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float mx = sm_m[0][g];
+#pragma unroll
+            for (int w = 1; w < kStreams; w++) mx = fmaxf(mx, sm_m[w][g]);
+            float lt = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < kStreams; w++) {
+                const float f = exp2f(sm_m[w][g] - mx);
+                lt = fmaf(sm_l[w][g], f, lt);
+                const float4 ow = sm_o[w][g][lane];
+                acc.x = fmaf(ow.x, f, acc.x); acc.y = fmaf(ow.y, f, acc.y);
+                acc.z = fmaf(ow.z, f, acc.z); acc.w = fmaf(ow.w, f, acc.w);
+            }
+            const size_t qrow = (size_t)row * p.q_heads + hq0 + g;
+            if (p.parts == 1) {
+                if (out_on) {
+                    float4 r4 = make_float4(acc.x / lt, acc.y / lt, acc.z / lt, acc.w / lt);
+                    *reinterpret_cast<float4 *>(p.out + qrow * D + lane * 4) = r4;
+                }
+            } else {
+                if (out_on)
+                    *reinterpret_cast<float4 *>(p.part_o + (qrow * p.parts + part) * D + lane * 4) = acc;
+                if (lane == 0) p.part_ml[qrow * p.parts + part] = make_float2(mx, lt);
+            }
+        }
+    }
+}
+
 // grid = (q_heads, rows); one thread per output element.
 __global__ void attn_combine_kernel(const AttnParams p)
 {
@@ -281,18 +474,38 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
     // a group width with no instantiation runs one query head per CTA (K/V re-read per head)
     const int G = (group == 2 || group == 4 || group == 8) ? (int)group : 1;
     dim3 grid(p.parts, G == 1 ? p.q_heads : p.kv_heads, p.rows);
+    // grouped heads: half a warp per position when the head dimension allows 8 elements per lane
+    static const bool gqa_off = getenv("AB_ATTN_WARP_PER_POSITION") != nullptr;      // for measurements
+    const bool gqa = G > 1 && p.head_dim % 8 == 0 && !gqa_off;
+    // an f16 cache without grouping: 16 lanes x 16 bytes cover a row, where a full warp would issue
+    // 8-byte loads
+    const bool half_rows = sizeof(T) == 2 && group == 1 && p.head_dim % 8 == 0 && !gqa_off;
     switch (G) {
-    case 1: attn_partition_kernel<T, 1><<<grid, kAttnThreads, 0, l.stream>>>(p); count_launch(); break;
-    case 2: attn_partition_kernel<T, 2><<<grid, kAttnThreads, 0, l.stream>>>(p); count_launch(); break;
-    case 4: attn_partition_kernel<T, 4><<<grid, kAttnThreads, 0, l.stream>>>(p); count_launch(); break;
-    default: attn_partition_kernel<T, 8><<<grid, kAttnThreads, 0, l.stream>>>(p); count_launch(); break;
+    case 1:
+        if (half_rows) attn_partition_gqa_kernel<T, 1><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        else attn_partition_kernel<T, 1><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        break;
+    case 2:
+        if (gqa) attn_partition_gqa_kernel<T, 2><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        else attn_partition_kernel<T, 2><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        break;
+    case 4:
+        if (gqa) attn_partition_gqa_kernel<T, 4><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        else attn_partition_kernel<T, 4><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        break;
+    default:
+        if (gqa) attn_partition_gqa_kernel<T, 8><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        else attn_partition_kernel<T, 8><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        break;
     }
+    count_launch();
     if (p.parts > 1) {
         dim3 cgrid(p.q_heads, p.rows);
         attn_combine_kernel<<<cgrid, 128, 0, l.stream>>>(p); count_launch();
     }
     note_selection("%s: split-K decode, %u partition(s) of %d positions, %u query head(s) sharing "
-                   "each K/V read, %u row(s)", name, p.parts, kPartition, group, p.rows);
+                   "each K/V read, %u row(s), %s per position", name, p.parts, kPartition, group, p.rows,
+                   (gqa || (G == 1 && half_rows)) ? "half a warp" : "a warp");
     return check_cuda(cudaGetLastError(), name);
 }
 

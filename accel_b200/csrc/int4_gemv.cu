@@ -249,19 +249,24 @@ Int4RowPlan plan_int4_row(uint32_t N, uint32_t K)
     const uint32_t gpr = N / kGroup, sms = (uint32_t)sm_count();
     static const uint32_t forced_w = env_u32("AB_INT4_ROW_GROUPS"), forced_s = env_u32("AB_INT4_SPLITS");
     // measured: about two CTAs per SM and clusters of at most eight do best; two groups per tile
-    // for wide matrices (one scale sector serves both), one for narrow ones
-    p.W = gpr >= 64 ? 2 : 1;
-    if (forced_w == 1 || forced_w == 2) p.W = (int)forced_w;
-    p.tiles = (gpr + p.W - 1) / p.W;
-    uint32_t splits = 2u * sms / p.tiles;
-    if (splits > 8) splits = 8;
-    if (forced_s) splits = forced_s;
-    if (splits < 1) splits = 1;
-    if (splits > (uint32_t)kRowMaxCluster) splits = kRowMaxCluster;
-    uint32_t kc = ((K + splits - 1) / splits + 15) / 16 * 16;
-    if (kc > kRowMaxKc) kc = kRowMaxKc;
-    p.kc = kc;
-    p.splits = (K + kc - 1) / kc;
+    // for wide matrices (one scale sector serves both), one for narrow ones, unless the K ranges
+    // (at most 768 rows) then make more CTAs than fit at once (three per SM at 168 registers)
+    auto lay = [&](int W) {
+        p.W = W;
+        p.tiles = (gpr + W - 1) / W;
+        uint32_t splits = 2u * sms / p.tiles;
+        if (splits > 8) splits = 8;
+        if (forced_s) splits = forced_s;
+        if (splits < 1) splits = 1;
+        if (splits > (uint32_t)kRowMaxCluster) splits = kRowMaxCluster;
+        uint32_t kc = ((K + splits - 1) / splits + 15) / 16 * 16;
+        if (kc > kRowMaxKc) kc = kRowMaxKc;
+        p.kc = kc;
+        p.splits = (K + kc - 1) / kc;
+    };
+    lay(gpr >= 64 ? 2 : 1);
+    if (p.W == 1 && p.tiles * p.splits > 3 * sms) lay(2);
+    if (forced_w == 1 || forced_w == 2) lay((int)forced_w);
     p.ok = p.splits <= (uint32_t)kRowMaxCluster;          // deeper K: another kernel takes it
     p.ws = 0;
     return p;
