@@ -269,10 +269,10 @@ template <> struct Vec8<__half> {
 };
 
 static constexpr int kStreams = 2 * kWarps;      // half-warps: independent running softmax states
-static constexpr int kGqaUnroll = 2;             // steps per iteration: 4 positions per warp in flight
 
 // grid = (parts, kv_heads, rows); head_dim a multiple of 8, at most 128
-template <typename T, int G>
+// kGqaUnroll = steps per iteration: 2 x kGqaUnroll positions per warp in flight
+template <typename T, int G, int kGqaUnroll>
 __global__ void __launch_bounds__(kAttnThreads)
 attn_partition_gqa_kernel(const AttnParams p)
 {
@@ -333,6 +333,7 @@ attn_partition_gqa_kernel(const AttnParams p)
                 Vec8<T>::load(vc + off, vv[u]);
             }
         }
+        float sc[kGqaUnroll][G];
 #pragma unroll
         for (int u = 0; u < kGqaUnroll; u++) {
             // partial dot products of this lane's 8 elements, one per head
@@ -359,26 +360,34 @@ attn_partition_gqa_kernel(const AttnParams p)
 #pragma unroll
             for (; sh >= 1; sh >>= 1) s[0] += __shfl_xor_sync(0xffffffffu, s[0], sh);
             // head g's sum now sits in the lanes whose top bits spell g: hand it to all 16
-            float sc[G];
 #pragma unroll
             for (int g = 0; g < G; g++) {
                 int src = 0, bit = 8;
 #pragma unroll
                 for (int n = G; n > 1; n >>= 1, bit >>= 1)
                     if (g & (n >> 1)) src |= bit;
-                sc[g] = __shfl_sync(0xffffffffu, s[0], (lane & 16) | src);
+                sc[u][g] = __shfl_sync(0xffffffffu, s[0], (lane & 16) | src);
             }
+        }
+        // one rescale of the running state per head and iteration, then the positions' terms
 #pragma unroll
-            for (int g = 0; g < G; g++) {
-                if (ok[u]) {                         // uniform over the half-warp
-                    const float mx = fmaxf(m[g], sc[g]);
-                    const float alpha = exp2f(m[g] - mx), e = exp2f(sc[g] - mx);
-                    m[g] = mx;
-                    l[g] = fmaf(l[g], alpha, e);
+        for (int g = 0; g < G; g++) {
+            float mx = m[g];
 #pragma unroll
-                    for (int q = 0; q < 8; q++) o[g][q] = fmaf(e, vv[u][q], o[g][q] * alpha);
-                }
+            for (int u = 0; u < kGqaUnroll; u++) mx = ok[u] ? fmaxf(mx, sc[u][g]) : mx;
+            const float alpha = exp2f(m[g] - mx);
+            m[g] = mx;
+            float sum = 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; q++) o[g][q] *= alpha;
+#pragma unroll
+            for (int u = 0; u < kGqaUnroll; u++) {
+                const float e = ok[u] ? exp2f(sc[u][g] - mx) : 0.f;
+                sum += e;
+#pragma unroll
+                for (int q = 0; q < 8; q++) o[g][q] = fmaf(e, vv[u][q], o[g][q]);
             }
+            l[g] = fmaf(l[g], alpha, sum);
         }
     }
 
@@ -480,24 +489,28 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
     // an f16 cache without grouping: 16 lanes x 16 bytes cover a row, where a full warp would issue
     // 8-byte loads
     const bool half_rows = sizeof(T) == 2 && group == 1 && p.head_dim % 8 == 0 && !gqa_off;
+    static const int unroll_env = getenv("AB_ATTN_UNROLL") ? atoi(getenv("AB_ATTN_UNROLL")) : 0;   // for measurements
+#define AB_GQA(GG, UU) attn_partition_gqa_kernel<T, GG, UU><<<grid, kAttnThreads, 0, l.stream>>>(p)
+    const bool deep = unroll_env ? unroll_env >= 4 : false;
     switch (G) {
     case 1:
-        if (half_rows) attn_partition_gqa_kernel<T, 1><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        if (half_rows) { if (deep) AB_GQA(1, 4); else AB_GQA(1, 2); }
         else attn_partition_kernel<T, 1><<<grid, kAttnThreads, 0, l.stream>>>(p);
         break;
     case 2:
-        if (gqa) attn_partition_gqa_kernel<T, 2><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        if (gqa) { if (deep) AB_GQA(2, 4); else AB_GQA(2, 2); }
         else attn_partition_kernel<T, 2><<<grid, kAttnThreads, 0, l.stream>>>(p);
         break;
     case 4:
-        if (gqa) attn_partition_gqa_kernel<T, 4><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        if (gqa) { if (deep) AB_GQA(4, 4); else AB_GQA(4, 2); }
         else attn_partition_kernel<T, 4><<<grid, kAttnThreads, 0, l.stream>>>(p);
         break;
     default:
-        if (gqa) attn_partition_gqa_kernel<T, 8><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        if (gqa) AB_GQA(8, 2);
         else attn_partition_kernel<T, 8><<<grid, kAttnThreads, 0, l.stream>>>(p);
         break;
     }
+#undef AB_GQA
     count_launch();
     if (p.parts > 1) {
         dim3 cgrid(p.q_heads, p.rows);

@@ -44,7 +44,8 @@ static constexpr uint32_t kGroup = 128;
 static constexpr int kBPhases = 4;                    // warps per group: warp p takes steps p, p+4, ...
 static constexpr int kBDepth = 4;                     // code steps in flight per warp
 static constexpr int kBActBatch = 8;                  // 16-byte activation loads in flight per thread
-static constexpr int kBMaxCluster = 8;
+static constexpr int kBMaxCluster = 16;          // above 8 needs the non-portable cluster size opt-in
+static constexpr int kBUsualCluster = 8;
 
 // a' row stride in bytes: kc f16 values, padded so that the eight rows a fragment load touches
 // start 32 bytes apart modulo 128 (no bank conflict for 8-byte loads)
@@ -362,6 +363,10 @@ Int4BatchPlan plan_int4_batch(uint32_t M, uint32_t N, uint32_t K)
     p.tiles = (gpr + G - 1) / G;
     const uint32_t slots = (4u / G) * sms;                         // CTAs resident at once
     uint32_t splits = slots / p.tiles;
+    // clusters of more than eight cost more than they save on a full-size product; a small product
+    // (a tensor-parallel shard: a few tiles) is a chain of latencies that only more CTAs shorten
+    const uint32_t most = p.tiles * kBUsualCluster <= sms ? kBMaxCluster : kBUsualCluster;
+    if (splits > most) splits = most;
     if (forced_s) splits = forced_s;
     if (splits < 1) splits = 1;
     if (splits > (uint32_t)kBMaxCluster) splits = kBMaxCluster;
@@ -384,6 +389,9 @@ static int launch_batch(const Launch &l, const Int4BatchPlan &p, float *out, uin
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         int rc = check_cuda(cudaFuncSetAttribute(int4_batch_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)batch_smem_cap(G)), "int4_batch_kernel attributes");
+        if (rc) return rc;
+        rc = check_cuda(cudaFuncSetAttribute(int4_batch_kernel<G>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1),
+                        "int4_batch_kernel attributes");
         if (rc) return rc;
         attr_set[dev] = true;
     }
