@@ -11,6 +11,8 @@
 //
 // Edge semantics kept: `last` is clamped to Tokens; an empty expert does nothing; GroupedMatMul
 // never writes a row past offsets[E]; GroupedMatVec writes zeros there.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ab {
@@ -170,6 +172,177 @@ __global__ void grouped_zero_tail_kernel(float *out, const uint32_t *offsets, ui
         out[i] = 0.f;
 }
 
+// ---- int4 experts on the tensor cores ------------------------------------------------------------
+// The same arithmetic as the decode-batch int4 kernel (int4_batch.cu), tiled for hundreds of rows
+// per expert: a CTA owns 128 rows of one expert x one 128-column quantisation group, so the scale
+// and zero of a weight depend on k only and
+//   out[m][n] = sum_k (x[m][k] s[k]) code[k][n] - sum_k (x[m][k] s[k]) z[k]
+// with x*s rounded to f16 once (the only rounded operand), the 4-bit code masked in place into an
+// f16 subnormal (exact; undone per column at the end) and the second sum one more MMA per k step
+// with z as its B operand.  A row whose group has scale 0 is the constant z
+// (internal/kernels/int4.go:85-87): its x*s is 0 and x*z is added from an f32 side sum.
+// Eight warps: warp (r, c) holds rows 32r .. 32r+31 x columns 64c .. 64c+63 (two m16 tiles x eight
+// n8 tiles, 64 accumulators per thread).  K advances in chunks of 64: the chunk's x*s goes through
+// shared memory (f16, row stride padded against bank conflicts), the codes go from global memory
+// straight to registers, one chunk ahead.
+static constexpr int kGmThreads = 256, kGmRows = 128, kGmChunk = 64;
+static constexpr int kGmStride = kGmChunk * 2 + 32;       // bytes per row of x*s in shared memory (32 mod 128: fragment loads spread over the banks)
+
+__device__ __forceinline__ void gm_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+                 "{%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// grid = (N / 128, row tiles upper bound); K % 64 == 0, N % 128 == 0
+__global__ void __launch_bounds__(kGmThreads, 2) grouped_int4_mma_kernel(const GroupedParams p)
+{
+    __shared__ __align__(16) unsigned char s_a[kGmRows * kGmStride];      // x*s, f16 [128][64]
+    __shared__ __align__(8) __half s_s[kGmChunk], s_z[kGmChunk];           // the chunk's scales and zeros
+    __shared__ float s_const[kGmRows][8];                                 // side sums over constant rows
+    uint32_t e, row0, last;
+    if (!find_tile(p, blockIdx.y, e, row0, last)) return;
+    const uint32_t g = blockIdx.x, gpr = p.N / kGroup;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, t = lane & 3;
+    const int wr = warp >> 1, wc = warp & 1;
+    const __half *bs = p.bs + e * p.groups_per_expert + g, *bz = p.bz + e * p.groups_per_expert + g;
+    // this lane's codes: rows 4t .. 4t+3 of every 16-row step, the 8 columns 64 wc + 8 gid .. +7
+    const uint32_t *code = p.bq + e * p.words_per_expert + (size_t)(4 * t) * (p.N / 8) + g * 16 + wc * 8 + gid;
+    const size_t row_words = p.N / 8;
+    // staging of x: row sm = tid / 2, k half sh = tid % 2 (32 of the chunk's 64 k)
+    const int sm = tid >> 1, shalf = tid & 1;
+    const bool srow_on = row0 + sm < last;
+    const float *xrow = p.x + (size_t)(row0 + (srow_on ? sm : 0)) * p.K + 32 * shalf;
+
+    float acc[2][8][4], accz[2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[mt][j][0] = acc[mt][j][1] = acc[mt][j][2] = acc[mt][j][3] = 0.f;
+        accz[mt][0] = accz[mt][1] = accz[mt][2] = accz[mt][3] = 0.f;
+    }
+    float csum = 0.f;
+    bool any_const = false;
+
+    uint32_t cw[4][4];                                     // [k16 step of the chunk][row 4t + i]
+    auto fetch_codes = [&](uint32_t k0) {
+#pragma unroll
+        for (int st = 0; st < 4; st++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                cw[st][i] = k0 < p.K ? __ldg(code + (size_t)(k0 + 16 * st + i) * row_words) : 0u;
+    };
+    fetch_codes(0);
+
+    for (uint32_t k0 = 0; k0 < p.K; k0 += kGmChunk) {
+        __syncthreads();                                   // the previous chunk's x*s is no longer read
+        if (tid < kGmChunk) {
+            s_s[tid] = __ldg(bs + (size_t)(k0 + tid) * gpr);
+            s_z[tid] = __ldg(bz + (size_t)(k0 + tid) * gpr);
+        }
+        float4 xv[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            xv[i] = srow_on ? __ldg(reinterpret_cast<const float4 *>(xrow + k0 + 4 * i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int k = 32 * shalf + 4 * i;
+            const uint2 s4 = *reinterpret_cast<const uint2 *>(s_s + k);
+            const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&s4.x));
+            const float2 s23 = __half22float2(*reinterpret_cast<const __half2 *>(&s4.y));
+            const __half2 p01 = __floats2half2_rn(xv[i].x * s01.x, xv[i].y * s01.y);
+            const __half2 p23 = __floats2half2_rn(xv[i].z * s23.x, xv[i].w * s23.y);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t *>(&p01);
+            pk.y = *reinterpret_cast<const uint32_t *>(&p23);
+            *reinterpret_cast<uint2 *>(s_a + sm * kGmStride + k * 2) = pk;
+            if (s01.x == 0.f || s01.y == 0.f || s23.x == 0.f || s23.y == 0.f) {
+                any_const = true;
+                if (s01.x == 0.f) csum = fmaf(xv[i].x, __half2float(s_z[k]), csum);
+                if (s01.y == 0.f) csum = fmaf(xv[i].y, __half2float(s_z[k + 1]), csum);
+                if (s23.x == 0.f) csum = fmaf(xv[i].z, __half2float(s_z[k + 2]), csum);
+                if (s23.y == 0.f) csum = fmaf(xv[i].w, __half2float(s_z[k + 3]), csum);
+            }
+        }
+        __syncthreads();
+        uint32_t cur[4][4];
+#pragma unroll
+        for (int st = 0; st < 4; st++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) cur[st][i] = cw[st][i];
+        fetch_codes(k0 + kGmChunk);                        // the next chunk's codes, while this one is used
+#pragma unroll
+        for (int st = 0; st < 4; st++) {
+            // a 16-row step: rows {4t, 4t+1} stand for the MMA's k slots {2t, 2t+1}, {4t+2, 4t+3} for
+            // {2t+8, 2t+9} (a free relabelling of k, applied to both operands)
+            uint32_t af[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                const unsigned char *a_lo = s_a + (32 * wr + 16 * mt + gid) * kGmStride + (16 * st + 4 * t) * 2;
+                const uint2 lo = *reinterpret_cast<const uint2 *>(a_lo);
+                const uint2 hi = *reinterpret_cast<const uint2 *>(a_lo + 8 * kGmStride);
+                af[mt][0] = lo.x; af[mt][1] = hi.x; af[mt][2] = lo.y; af[mt][3] = hi.y;
+            }
+            const uint2 z4 = *reinterpret_cast<const uint2 *>(s_z + 16 * st + 4 * t);
+            // a constant row's zero must not reach the MMA (its x*s is 0, but 0 * inf is NaN)
+            const uint2 sz4 = *reinterpret_cast<const uint2 *>(s_s + 16 * st + 4 * t);
+            uint32_t zb0 = z4.x, zb1 = z4.y;
+            if ((sz4.x & 0x7fffu) == 0) zb0 &= 0xffff0000u;
+            if ((sz4.x & 0x7fff0000u) == 0) zb0 &= 0x0000ffffu;
+            if ((sz4.y & 0x7fffu) == 0) zb1 &= 0xffff0000u;
+            if ((sz4.y & 0x7fff0000u) == 0) zb1 &= 0x0000ffffu;
+            gm_mma(accz[0], af[0], zb0, zb1);
+            gm_mma(accz[1], af[1], zb0, zb1);
+            const uint32_t w0 = cur[st][0], w1 = cur[st][1], w2 = cur[st][2], w3 = cur[st][3];
+            const uint32_t lo01 = __byte_perm(w0, w1, 0x5410), hi01 = __byte_perm(w0, w1, 0x7632);
+            const uint32_t lo23 = __byte_perm(w2, w3, 0x5410), hi23 = __byte_perm(w2, w3, 0x7632);
+            const uint32_t src01[4] = {lo01, lo01 >> 8, hi01, hi01 >> 8};
+            const uint32_t src23[4] = {lo23, lo23 >> 8, hi23, hi23 >> 8};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const uint32_t be0 = src01[q] & 0x000F000Fu, be1 = src23[q] & 0x000F000Fu;     // code 2q
+                const uint32_t bo0 = src01[q] & 0x00F000F0u, bo1 = src23[q] & 0x00F000F0u;     // code 2q + 1
+                gm_mma(acc[0][2 * q], af[0], be0, be1);
+                gm_mma(acc[1][2 * q], af[1], be0, be1);
+                gm_mma(acc[0][2 * q + 1], af[0], bo0, bo1);
+                gm_mma(acc[1][2 * q + 1], af[1], bo0, bo1);
+            }
+        }
+    }
+    // side sums over constant rows: two staging threads per row, added in a fixed order
+    const int has_const = __syncthreads_or(any_const);
+    if (has_const) {
+        s_const[sm][shalf] = csum;
+        __syncthreads();
+    }
+    // MMA j's n slot n is column 8 n + j of the warp's 64: the thread holds columns 16 t .. 16 t + 15
+    // (n = 2t: j = 0..7, n = 2t+1: j = 0..7) of rows gid and gid + 8 of each m tile
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t lr = 32 * wr + 16 * mt + gid + 8 * h, row = row0 + lr;
+            if (row >= last) continue;
+            float add = -accz[mt][2 * h];
+            if (has_const) add += s_const[lr][0] + s_const[lr][1];
+            float *o = p.out + (size_t)row * p.N + (size_t)g * kGroup + 64 * wc + 16 * t;
+#pragma unroll
+            for (int nn = 0; nn < 2; nn++)
+#pragma unroll
+                for (int j = 0; j < 8; j += 4) {
+                    float4 v;
+                    v.x = acc[mt][j][2 * h + nn] * 16777216.f + add;
+                    v.y = acc[mt][j + 1][2 * h + nn] * 1048576.f + add;
+                    v.z = acc[mt][j + 2][2 * h + nn] * 16777216.f + add;
+                    v.w = acc[mt][j + 3][2 * h + nn] * 1048576.f + add;
+                    *reinterpret_cast<float4 *>(o + 8 * nn + j) = v;
+                }
+        }
+}
+
 static int run_grouped(Launch &l, GroupedParams &p, bool int4, bool zero_tail, uint32_t out_rows,
                        const char *name)
 {
@@ -178,7 +351,12 @@ static int run_grouped(Launch &l, GroupedParams &p, bool int4, bool zero_tail, u
         return fail(AB_ERR_INVALID, "%s: Experts=%u K=%u N=%u", name, p.experts, p.K, p.N);
     if (p.tokens == 0) return AB_OK;
     bool fast = p.K % BK == 0 && (int4 ? p.N % kGroup == 0 : p.N % 4 == 0);
-    if (fast) {
+    static const bool simt_only = getenv("AB_GROUPED_SIMT") != nullptr;       // for measurements
+    const bool mma = int4 && fast && p.K % kGmChunk == 0 && !simt_only;
+    if (mma) {
+        dim3 grid(p.N / kGroup, (p.tokens + kGmRows - 1) / kGmRows + p.experts);
+        grouped_int4_mma_kernel<<<grid, kGmThreads, 0, l.stream>>>(p); count_launch();
+    } else if (fast) {
         dim3 grid((p.N + BN - 1) / BN, (p.tokens + BM - 1) / BM + p.experts);
         if (int4) { grouped_tile_kernel<true><<<grid, GT, 0, l.stream>>>(p); count_launch(); }
         else { grouped_tile_kernel<false><<<grid, GT, 0, l.stream>>>(p); count_launch(); }
@@ -191,7 +369,8 @@ static int run_grouped(Launch &l, GroupedParams &p, bool int4, bool zero_tail, u
     if (zero_tail)
         grouped_zero_tail_kernel<<<64, 256, 0, l.stream>>>(p.out, p.offsets, p.experts, out_rows, p.N); count_launch();
     note_selection("%s: %s, %u experts over %u rows", name,
-                   fast ? "128x128 register-tiled kernel" : "generic kernel", p.experts, p.tokens);
+                   mma ? "128x128 tensor-core kernel (m16n8k16, f16 operands, f32 accumulate)"
+                       : (fast ? "128x128 register-tiled kernel" : "generic kernel"), p.experts, p.tokens);
     return check_cuda(cudaGetLastError(), name);
 }
 

@@ -6,6 +6,7 @@ import pytest
 import torch
 
 import oracle as orc
+from accel_b200 import runtime
 from accel_b200 import tensor as T
 from util import GEMM_TOL, assert_close, normal
 
@@ -75,12 +76,13 @@ def test_moe_shape_reduced_against_the_oracle():
     assert_close(got, want, GEMM_TOL, "MoE slice")
 
 
-def test_int4_grouped_is_the_composition():
-    E, K, N, rows = 4, 256, 384, 200
-    rng = np.random.default_rng(8)
-    counts = np.array([70, 0, 129, 1], np.uint32)
+@pytest.mark.parametrize("K,kernel", [(256, "tensor-core kernel"), (80, "register-tiled kernel")])
+def test_int4_grouped_is_the_composition(K, kernel):
+    E, N, rows = 4, 384, 200
+    counts = np.array([70, 0, 129, 1], np.uint32)        # an empty expert, a two-tile expert, one row
     x = normal(9, (rows, K))
     w = normal(10, (E, K, N), 0.02)
+    w[2, 5, 128:256] = 0.125                              # a constant group: scale 0, weight = zero point
     planes = [orc.int4_quantize(w[e]) for e in range(E)]
     back = np.stack([orc.int4_dequantize(*planes[e], K * N).reshape(K, N) for e in range(E)])
     q = T.Int4(dev(np.concatenate([p[0] for p in planes])),
@@ -90,6 +92,7 @@ def test_int4_grouped_is_the_composition():
     off = orc.segment_offsets(counts)
     want = orc.grouped_matmul(x, back, off, rows, E, K, N)
     got = T.grouped_matmul_int4(dev(x), q, E, dev(counts)).cpu().numpy()
+    assert kernel in runtime.last_selection()
     assert_close(got, want, GEMM_TOL, "int4 grouped")
 
 
