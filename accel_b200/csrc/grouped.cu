@@ -197,11 +197,10 @@ __device__ __forceinline__ void gm_mma(float (&d)[4], const uint32_t (&a)[4], ui
 }
 
 // grid = (N / 128, row tiles upper bound); K % 64 == 0, N % 128 == 0
-__global__ void __launch_bounds__(kGmThreads, 2) grouped_int4_mma_kernel(const GroupedParams p)
+__global__ void __launch_bounds__(kGmThreads) grouped_int4_mma_kernel(const GroupedParams p)
 {
     __shared__ __align__(16) unsigned char s_a[kGmRows * kGmStride];      // x*s, f16 [128][64]
     __shared__ __align__(8) __half s_s[kGmChunk], s_z[kGmChunk];           // the chunk's scales and zeros
-    __shared__ float s_const[kGmRows][8];                                 // side sums over constant rows
     uint32_t e, row0, last;
     if (!find_tile(p, blockIdx.y, e, row0, last)) return;
     const uint32_t g = blockIdx.x, gpr = p.N / kGroup;
@@ -211,10 +210,10 @@ __global__ void __launch_bounds__(kGmThreads, 2) grouped_int4_mma_kernel(const G
     // this lane's codes: rows 4t .. 4t+3 of every 16-row step, the 8 columns 64 wc + 8 gid .. +7
     const uint32_t *code = p.bq + e * p.words_per_expert + (size_t)(4 * t) * (p.N / 8) + g * 16 + wc * 8 + gid;
     const size_t row_words = p.N / 8;
-    // staging of x: row sm = tid / 2, k half sh = tid % 2 (32 of the chunk's 64 k)
-    const int sm = tid >> 1, shalf = tid & 1;
-    const bool srow_on = row0 + sm < last;
-    const float *xrow = p.x + (size_t)(row0 + (srow_on ? sm : 0)) * p.K + 32 * shalf;
+    // staging of x: pass i covers rows 16 i .. 16 i + 15; thread = (row tid / 16 of the pass, the four
+    // k values 4 (tid % 16) ..): a half-warp reads 256 contiguous bytes of a row and its shared
+    // stores fall on distinct banks
+    const int srow = tid >> 4, skq = tid & 15;
 
     float acc[2][8][4], accz[2][4];
 #pragma unroll
@@ -223,20 +222,23 @@ __global__ void __launch_bounds__(kGmThreads, 2) grouped_int4_mma_kernel(const G
         for (int j = 0; j < 8; j++) acc[mt][j][0] = acc[mt][j][1] = acc[mt][j][2] = acc[mt][j][3] = 0.f;
         accz[mt][0] = accz[mt][1] = accz[mt][2] = accz[mt][3] = 0.f;
     }
-    float csum = 0.f;
+    float csum[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) csum[i] = 0.f;
     bool any_const = false;
 
-    uint32_t cw[4][4];                                     // [k16 step of the chunk][row 4t + i]
-    auto fetch_codes = [&](uint32_t k0) {
+    // codes of a chunk: [k16 step][row 4t + i]; two register sets used in turn, so that a chunk's
+    // loads are in flight while the other chunk is multiplied
+    const uint32_t *cp = code;
+    const size_t chunk_words = (size_t)kGmChunk * row_words;
+    auto fetch_codes = [&](uint32_t (&dst)[4][4], bool live) {
 #pragma unroll
         for (int st = 0; st < 4; st++)
 #pragma unroll
-            for (int i = 0; i < 4; i++)
-                cw[st][i] = k0 < p.K ? __ldg(code + (size_t)(k0 + 16 * st + i) * row_words) : 0u;
+            for (int i = 0; i < 4; i++) dst[st][i] = live ? __ldg(cp + (size_t)(16 * st + i) * row_words) : 0u;
+        cp += chunk_words;
     };
-    fetch_codes(0);
-
-    for (uint32_t k0 = 0; k0 < p.K; k0 += kGmChunk) {
+    auto stage = [&](uint32_t k0) {
         __syncthreads();                                   // the previous chunk's x*s is no longer read
         if (tid < kGmChunk) {
             s_s[tid] = __ldg(bs + (size_t)(k0 + tid) * gpr);
@@ -244,36 +246,41 @@ __global__ void __launch_bounds__(kGmThreads, 2) grouped_int4_mma_kernel(const G
         }
         float4 xv[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++)
-            xv[i] = srow_on ? __ldg(reinterpret_cast<const float4 *>(xrow + k0 + 4 * i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < 8; i++) {
+            const uint32_t row = row0 + 16 * i + srow;
+            xv[i] = row < last ? __ldg(reinterpret_cast<const float4 *>(p.x + (size_t)row * p.K + k0 + 4 * skq))
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
         __syncthreads();
+        const uint2 s4 = *reinterpret_cast<const uint2 *>(s_s + 4 * skq);
+        const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&s4.x));
+        const float2 s23 = __half22float2(*reinterpret_cast<const __half2 *>(&s4.y));
+        const bool cst = s01.x == 0.f || s01.y == 0.f || s23.x == 0.f || s23.y == 0.f;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const int k = 32 * shalf + 4 * i;
-            const uint2 s4 = *reinterpret_cast<const uint2 *>(s_s + k);
-            const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&s4.x));
-            const float2 s23 = __half22float2(*reinterpret_cast<const __half2 *>(&s4.y));
             const __half2 p01 = __floats2half2_rn(xv[i].x * s01.x, xv[i].y * s01.y);
             const __half2 p23 = __floats2half2_rn(xv[i].z * s23.x, xv[i].w * s23.y);
             uint2 pk;
             pk.x = *reinterpret_cast<const uint32_t *>(&p01);
             pk.y = *reinterpret_cast<const uint32_t *>(&p23);
-            *reinterpret_cast<uint2 *>(s_a + sm * kGmStride + k * 2) = pk;
-            if (s01.x == 0.f || s01.y == 0.f || s23.x == 0.f || s23.y == 0.f) {
-                any_const = true;
-                if (s01.x == 0.f) csum = fmaf(xv[i].x, __half2float(s_z[k]), csum);
-                if (s01.y == 0.f) csum = fmaf(xv[i].y, __half2float(s_z[k + 1]), csum);
-                if (s23.x == 0.f) csum = fmaf(xv[i].z, __half2float(s_z[k + 2]), csum);
-                if (s23.y == 0.f) csum = fmaf(xv[i].w, __half2float(s_z[k + 3]), csum);
+            *reinterpret_cast<uint2 *>(s_a + (16 * i + srow) * kGmStride + 8 * skq) = pk;
+        }
+        if (cst) {
+            any_const = true;
+            const float z0 = __half2float(s_z[4 * skq]), z1 = __half2float(s_z[4 * skq + 1]);
+            const float z2 = __half2float(s_z[4 * skq + 2]), z3 = __half2float(s_z[4 * skq + 3]);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                if (s01.x == 0.f) csum[i] = fmaf(xv[i].x, z0, csum[i]);
+                if (s01.y == 0.f) csum[i] = fmaf(xv[i].y, z1, csum[i]);
+                if (s23.x == 0.f) csum[i] = fmaf(xv[i].z, z2, csum[i]);
+                if (s23.y == 0.f) csum[i] = fmaf(xv[i].w, z3, csum[i]);
             }
         }
         __syncthreads();
-        uint32_t cur[4][4];
-#pragma unroll
-        for (int st = 0; st < 4; st++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) cur[st][i] = cw[st][i];
-        fetch_codes(k0 + kGmChunk);                        // the next chunk's codes, while this one is used
+    };
+    const unsigned char *a_base = s_a + (32 * wr + gid) * kGmStride + 8 * t;
+    auto multiply = [&](const uint32_t (&cur)[4][4]) {
 #pragma unroll
         for (int st = 0; st < 4; st++) {
             // a 16-row step: rows {4t, 4t+1} stand for the MMA's k slots {2t, 2t+1}, {4t+2, 4t+3} for
@@ -281,7 +288,7 @@ __global__ void __launch_bounds__(kGmThreads, 2) grouped_int4_mma_kernel(const G
             uint32_t af[2][4];
 #pragma unroll
             for (int mt = 0; mt < 2; mt++) {
-                const unsigned char *a_lo = s_a + (32 * wr + 16 * mt + gid) * kGmStride + (16 * st + 4 * t) * 2;
+                const unsigned char *a_lo = a_base + 16 * mt * kGmStride + 32 * st;
                 const uint2 lo = *reinterpret_cast<const uint2 *>(a_lo);
                 const uint2 hi = *reinterpret_cast<const uint2 *>(a_lo + 8 * kGmStride);
                 af[mt][0] = lo.x; af[mt][1] = hi.x; af[mt][2] = lo.y; af[mt][3] = hi.y;
@@ -311,11 +318,26 @@ __global__ void __launch_bounds__(kGmThreads, 2) grouped_int4_mma_kernel(const G
                 gm_mma(acc[1][2 * q + 1], af[1], bo0, bo1);
             }
         }
+    };
+
+    uint32_t cwa[4][4], cwb[4][4];
+    fetch_codes(cwa, true);
+    for (uint32_t k0 = 0; k0 < p.K; k0 += 2 * kGmChunk) {
+        fetch_codes(cwb, k0 + kGmChunk < p.K);
+        stage(k0);
+        multiply(cwa);
+        fetch_codes(cwa, k0 + 2 * kGmChunk < p.K);
+        if (k0 + kGmChunk < p.K) {                         // uniform over the CTA
+            stage(k0 + kGmChunk);
+            multiply(cwb);
+        }
     }
-    // side sums over constant rows: two staging threads per row, added in a fixed order
+    // side sums over constant rows: sixteen staging threads per row, added in a fixed order
     const int has_const = __syncthreads_or(any_const);
+    float *s_const = reinterpret_cast<float *>(s_a);       // [128][16], over x*s (no longer read)
     if (has_const) {
-        s_const[sm][shalf] = csum;
+#pragma unroll
+        for (int i = 0; i < 8; i++) s_const[(16 * i + srow) * 16 + skq] = csum[i];
         __syncthreads();
     }
     // MMA j's n slot n is column 8 n + j of the warp's 64: the thread holds columns 16 t .. 16 t + 15
@@ -327,7 +349,12 @@ __global__ void __launch_bounds__(kGmThreads, 2) grouped_int4_mma_kernel(const G
             const uint32_t lr = 32 * wr + 16 * mt + gid + 8 * h, row = row0 + lr;
             if (row >= last) continue;
             float add = -accz[mt][2 * h];
-            if (has_const) add += s_const[lr][0] + s_const[lr][1];
+            if (has_const) {
+                float cs = 0.f;
+#pragma unroll
+                for (int q = 0; q < 16; q++) cs += s_const[lr * 16 + q];
+                add += cs;
+            }
             float *o = p.out + (size_t)row * p.N + (size_t)g * kGroup + 64 * wc + 16 * t;
 #pragma unroll
             for (int nn = 0; nn < 2; nn++)
