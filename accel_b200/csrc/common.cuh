@@ -67,6 +67,10 @@ Int4DecodePlan plan_int4_decode(uint32_t M, uint32_t N, uint32_t K);
 int run_int4_decode(const Launch &l, const Int4DecodePlan &p, float *out, uint32_t M, uint32_t N, uint32_t K);
 int int4_decode_error_flag();
 
+// the 128 x 128 warp-MMA tile kernel of the grouped product, as a plain int4 product (grouped.cu)
+bool int4_tiles_ok(uint32_t N, uint32_t K);
+int run_int4_tiles(const Launch &l, float *out, uint32_t M, uint32_t N, uint32_t K);
+
 // the tcgen05 / TMEM int4 kernel (int4_tc.cu)
 struct Int4TcPlan { bool ok; uint32_t groups, splits, kc; int nmma; size_t ws; };
 Int4TcPlan plan_int4_tc(uint32_t M, uint32_t N, uint32_t K);

@@ -34,6 +34,12 @@ struct GroupedParams {
 __device__ __forceinline__ bool find_tile(const GroupedParams &p, uint32_t t, uint32_t &e,
                                           uint32_t &row0, uint32_t &last)
 {
+    if (!p.offsets) {                        // one matrix, no segments: rows 0 .. tokens
+        e = 0;
+        last = p.tokens;
+        row0 = t * BM;
+        return row0 < last;
+    }
     for (e = 0; e < p.experts; e++) {
         uint32_t first = p.offsets[e];
         last = min(p.offsets[e + 1], p.tokens);
@@ -368,6 +374,25 @@ __global__ void __launch_bounds__(kGmThreads) grouped_int4_mma_kernel(const Grou
                     *reinterpret_cast<float4 *>(o + 8 * nn + j) = v;
                 }
         }
+}
+
+// The same kernel as a plain int4 product for large batches of activation rows (one "expert", no
+// segment offsets): QuantMatMulInt4 from about a hundred rows, where 128-row tiles beat passes of
+// 16 rows.  K % 64 == 0 and N % 128 == 0.
+bool int4_tiles_ok(uint32_t N, uint32_t K) { return N % kGroup == 0 && K % kGmChunk == 0 && N > 0 && K > 0; }
+
+int run_int4_tiles(const Launch &l, float *out, uint32_t M, uint32_t N, uint32_t K)
+{
+    GroupedParams p{};
+    p.x = ptr<const float>(l, 0); p.bq = ptr<const uint32_t>(l, 1);
+    p.bs = ptr<const __half>(l, 2); p.bz = ptr<const __half>(l, 3);
+    p.offsets = nullptr; p.out = out;
+    p.experts = 1; p.tokens = M; p.K = K; p.N = N;
+    p.words_per_expert = ((uint64_t)K * N + 7) / 8;
+    p.groups_per_expert = ((uint64_t)K * N + kGroup - 1) / kGroup;
+    dim3 grid(N / kGroup, (M + kGmRows - 1) / kGmRows);
+    grouped_int4_mma_kernel<<<grid, kGmThreads, 0, l.stream>>>(p); count_launch();
+    return check_cuda(cudaGetLastError(), "QuantMatMulInt4 (tiles)");
 }
 
 static int run_grouped(Launch &l, GroupedParams &p, bool int4, bool zero_tail, uint32_t out_rows,

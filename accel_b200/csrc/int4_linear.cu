@@ -228,19 +228,31 @@ static int forced_path()
     if (v < 0) {
         const char *e = getenv("AB_INT4_PATH");
         v = !e ? 0 : (!strcmp(e, "tc") ? 1 : (!strcmp(e, "mma") ? 2 : (!strcmp(e, "simt") ? 3 :
-            (!strcmp(e, "batch") ? 4 : (!strcmp(e, "row") ? 5 : (!strcmp(e, "decode") ? 6 : 0))))));
+            (!strcmp(e, "batch") ? 4 : (!strcmp(e, "row") ? 5 : (!strcmp(e, "decode") ? 6 :
+            (!strcmp(e, "tiles") ? 7 : 0)))))));
     }
     return v;
 }
 
-static uint32_t tc_min_rows()
+// From how many activation rows the 128-row tile kernel is used instead of passes of 16 rows.
+// AB_INT4_TC_MIN_ROWS fixes it; otherwise a cost model fitted to measurements on a B200: a pass of
+// the batch kernel costs about 4 us + 0.53 bytes per weight at 1.65 TB/s, a wave of tiles about
+// 130 us per 4096 rows of K whatever the width of the matrix.
+static bool prefer_tiles(uint32_t M, uint32_t N, uint32_t K)
 {
-    static int v = -1;
-    if (v < 0) {
+    static int fixed = -2;
+    if (fixed == -2) {
         const char *e = getenv("AB_INT4_TC_MIN_ROWS");
-        v = e ? atoi(e) : 96;      // measured: the tcgen05 kernel wins from about a hundred rows
+        fixed = e ? atoi(e) : -1;
     }
-    return (uint32_t)v;
+    if (fixed >= 0) return M >= (uint32_t)fixed;
+    if (M < 64) return false;
+    const double pass_us = 4.0 + 0.53125 * (double)K * N / 1.65e6;
+    const double batch_us = (double)((M + 15) / 16) * pass_us;
+    const double ctas = (double)(N / kGroup) * ((M + 127) / 128);
+    const double waves = (double)(uint64_t)((ctas + sm_count() - 1) / sm_count());
+    const double tiles_us = waves * 130.0 * (double)K / 4096.0;
+    return tiles_us < batch_us;
 }
 
 static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint32_t K)
@@ -249,22 +261,25 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     Int4Plan p = plan_int4(M, N, K);
     // two or more rows of activations go to the tensor cores; one row stays on the CUDA cores
     Int4MmaPlan mp = plan_int4_mma(M, N, K);
-    // AB_INT4_PATH = tc | mma | simt overrides the choice (for measurements); tc_min_rows() is the
-    // batch size from which the tcgen05 kernel is used
+    // AB_INT4_PATH = tiles | tc | batch | decode | mma | simt | row overrides the choice (for
+    // measurements and tests)
     Int4TcPlan tp = plan_int4_tc(M, N, K);
     const int forced = forced_path();
-    const bool use_tc = tp.ok && (forced == 1 || (forced == 0 && M >= tc_min_rows()));
+    // from about a hundred rows: 128-row tiles on the warp-level MMAs (measured faster than the
+    // tcgen05 kernel as built, which stays behind AB_INT4_PATH=tc)
+    const bool use_tiles = int4_tiles_ok(N, K) && (forced == 7 || (forced == 0 && prefer_tiles(M, N, K)));
+    const bool use_tc = !use_tiles && tp.ok && forced == 1;
     Int4DecodePlan dp = plan_int4_decode(M, N, K);
-    const bool use_decode = !use_tc && dp.ok && forced == 6;
+    const bool use_decode = !use_tc && !use_tiles && dp.ok && forced == 6;
     Int4BatchPlan bp = plan_int4_batch(M, N, K);
-    const bool use_batch = !use_tc && !use_decode && bp.ok && (forced == 4 || (forced == 0 && M >= 2));
-    const bool use_mma = !use_tc && !use_batch && mp.ok && (forced == 2 || (forced == 0 && M >= 2));
+    const bool use_batch = !use_tc && !use_tiles && !use_decode && bp.ok && (forced == 4 || (forced == 0 && M >= 2));
+    const bool use_mma = !use_tc && !use_tiles && !use_batch && mp.ok && (forced == 2 || (forced == 0 && M >= 2));
     // one row: the streaming kernel that sums its own K splits (AB_INT4_PATH=simt keeps the older
     // two-kernel form, which is also the fallback when no counter slot is free)
     Int4RowPlan rp = plan_int4_row(N, K);
-    const bool use_row = !use_tc && !use_mma && !use_batch && !use_decode && rp.ok && M == 1 && forced != 3;
+    const bool use_row = !use_tc && !use_tiles && !use_mma && !use_batch && !use_decode && rp.ok && M == 1 && forced != 3;
     if (l.query_ws) {
-        l.ws_need = use_tc ? tp.ws : (use_batch || use_decode ? 0 : (use_mma ? mp.ws : (use_row ? 0 : p.ws)));
+        l.ws_need = use_tiles ? 0 : use_tc ? tp.ws : (use_batch || use_decode ? 0 : (use_mma ? mp.ws : (use_row ? 0 : p.ws)));
         return AB_OK;
     }
 
@@ -286,6 +301,13 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
             ptr<const __half>(l, 3), out, M, N, K); count_launch();
         note_selection("%s: generic kernel, N=%u is not a multiple of %u", name, N, kGroup);
         return check_cuda(cudaGetLastError(), name);
+    }
+    if (use_tiles) {
+        int rc = run_int4_tiles(l, out, M, N, K);
+        if (rc) return rc;
+        note_selection("%s: tensor-core tile kernel (128 rows x 128 columns per CTA, m16n8k16, f16 "
+                       "operands, f32 accumulate), %u x %u tiles", name, N / kGroup, (M + 127) / 128);
+        return AB_OK;
     }
     if (use_tc) {
         if (tp.ws > l.ws_bytes || (tp.ws && !l.ws))
