@@ -342,6 +342,9 @@ def run_b200(args):
         import faulthandler
         # a rank that never arrives must end the run with an error and a stack, not hang it
         faulthandler.dump_traceback_later(int(os.environ.get("AB_BENCH_WATCHDOG_S", "600")), exit=True)
+        # no NVLink multicast objects: a rank that dies while bound to one faults its peers' GPUs
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
         group = dist.group.WORLD
 
