@@ -172,6 +172,7 @@ struct ab_block {
     size_t size;
     void *dptr;     // device address (== host address mapping for pinned memory)
     void *hptr;     // host address for AB_MEMORY_HOST_VISIBLE
+    std::atomic<int> users{0};     // live executables that name this block (directly or by a slot)
 };
 
 struct ab_fence {
@@ -206,6 +207,7 @@ struct ab_exec {
     size_t ws_bytes = 0;
     bool timings = false;
     std::atomic<int> in_flight{0};
+    std::vector<ab_block *> held;          // blocks named directly by a node, counted in users
     cudaGraphExec_t graph = nullptr;
     bool graph_stale = true;
     cudaEvent_t ev_start = nullptr, ev_done = nullptr;
@@ -496,6 +498,11 @@ int ab_block_free(ab_block *b)
 {
     if (!b) return AB_OK;
     ab_device *d = b->dev;
+    // an executable that resolved pointers from this block would read freed memory on its next
+    // submission: children are freed before parents (the reference's pools refuse the same way)
+    if (b->users.load() > 0)
+        return ab::fail(AB_ERR_BUSY, "ab_block_free: %d live executable(s) still name this block; close "
+                        "them (or rebind their slots) first", b->users.load());
     if (!d->lost.load() && cudaSetDevice(d->ordinal) == cudaSuccess) {
         cudaStreamSynchronize(d->stream);
         if (b->hptr) cudaFreeHost(b->hptr); else cudaFree(b->dptr);
@@ -600,6 +607,9 @@ int ab_compile(ab_device *d, const ab_plan *plan, ab_exec **out)
     }
     cudaEventCreate(&e->ev_start);
     cudaEventCreate(&e->ev_done);
+    for (auto &nd : e->nodes)
+        for (auto &op : nd.bind)
+            if (op.block) { op.block->users.fetch_add(1); e->held.push_back(op.block); }
     d->live.fetch_add(1);
     *out = e;
     return AB_OK;
@@ -623,6 +633,13 @@ int ab_exec_rebind(ab_exec *e, const ab_slot_binding *b, int n)
     if (all) {
         int rc = resolve_all(e);
         if (rc) { e->slots = saved; e->slot_set = saved_set; return rc; }
+    }
+    for (int i = 0; i < n; i++) {
+        const size_t at = b[i].slot - 1;
+        b[i].block->users.fetch_add(1);
+        if (saved_set[at] && saved[at].block) saved[at].block->users.fetch_sub(1);
+        saved[at] = b[i];                    // a slot named twice in one call: count the last one
+        saved_set[at] = true;
     }
     e->graph_stale = true;
     return AB_OK;
@@ -711,18 +728,26 @@ int ab_exec_submit(ab_exec *e, ab_fence **out)
 int ab_fence_wait(ab_fence *f)
 {
     if (!f) return fail(AB_ERR_INVALID, "ab_fence_wait: fence is NULL");
-    if (f->injected) { if (f->exec) f->exec->in_flight.store(0); return fail(AB_ERR_DEVICE_LOST, "device lost (injected at this submission)"); }
+    if (f->injected) { if (f->exec) f->exec->in_flight.store(0); f->exec = nullptr; return fail(AB_ERR_DEVICE_LOST, "device lost (injected at this submission)"); }
     int rc = check_cuda(cudaEventSynchronize(f->done), "ab_fence_wait");   // needs no current context
     if (f->exec) f->exec->in_flight.store(0);
+    f->exec = nullptr;
+    // every outstanding fence reports a loss once the device is lost (internal/driver/plan.go:374-391)
+    if (rc == AB_OK && f->dev && f->dev->lost.load())
+        return fail(AB_ERR_DEVICE_LOST, "ab_fence_wait: the device was lost");
     return note_loss(f->dev, rc);
 }
 
 int ab_fence_done(ab_fence *f)
 {
     if (!f) return fail(AB_ERR_INVALID, "ab_fence_done: fence is NULL");
-    if (f->injected) return 1;
+    if (f->dev && f->dev->lost.load() && !f->injected)
+        return fail(AB_ERR_DEVICE_LOST, "ab_fence_done: the device was lost");
+    // a caller may learn of completion here and never wait: the executable is free again
+    auto finished = [&]() { if (f->exec) f->exec->in_flight.store(0); f->exec = nullptr; return 1; };
+    if (f->injected) return finished();
     cudaError_t e = cudaEventQuery(f->done);
-    if (e == cudaSuccess) return 1;
+    if (e == cudaSuccess) return finished();
     if (e == cudaErrorNotReady) return 0;
     return note_loss(f->dev, check_cuda(e, "ab_fence_done"));
 }
@@ -735,7 +760,15 @@ uint64_t ab_fence_elapsed_ns(ab_fence *f)
     return (uint64_t)((double)ms * 1e6);
 }
 
-void ab_fence_free(ab_fence *f) { delete f; }
+void ab_fence_free(ab_fence *f)
+{
+    if (!f) return;
+    if (f->exec) {                          // freed unwaited: wait here so the executable is not stuck busy
+        if (!f->injected) cudaEventSynchronize(f->done);
+        f->exec->in_flight.store(0);
+    }
+    delete f;
+}
 
 int ab_exec_close(ab_exec *e)
 {
@@ -749,6 +782,9 @@ int ab_exec_close(ab_exec *e)
         if (e->ev_start) cudaEventDestroy(e->ev_start);
         if (e->ev_done) cudaEventDestroy(e->ev_done);
     }
+    for (ab_block *blk : e->held) blk->users.fetch_sub(1);
+    for (size_t i = 0; i < e->slots.size(); i++)
+        if (e->slot_set[i] && e->slots[i].block) e->slots[i].block->users.fetch_sub(1);
     d->live.fetch_sub(1);
     delete e;
     return AB_OK;

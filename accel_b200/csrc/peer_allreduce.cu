@@ -22,6 +22,8 @@
 // the call can be captured in a CUDA graph and replayed.
 //
 // No reference counterpart: accel is single-device.  No multicast, no TMA: plain loads and stores.
+#include <cstddef>
+
 #include "common.cuh"
 
 namespace ab {
@@ -29,9 +31,16 @@ namespace ab {
 static constexpr int kArThreads = 256;
 static constexpr int kArMaxRanks = 8;
 static constexpr uint32_t kArFlagWords = 64;
-static constexpr uint32_t kArSpinLimit = 1u << 22;       // about a second of polling
+static constexpr uint32_t kArSpinLimit = 1u << 22;       // default: about a second of polling
 
-struct ArState { uint32_t epoch, arrived, done, error; };
+// spin_limit: polls a CTA spends waiting for its peers before it gives up; 0 means kArSpinLimit
+struct ArState { uint32_t epoch, arrived, done, error, spin_limit, reserved[3]; };
+
+__device__ __forceinline__ uint32_t spin_limit_of(const ArState *state)
+{
+    const uint32_t v = *reinterpret_cast<const volatile uint32_t *>(&state->spin_limit);
+    return v ? v : kArSpinLimit;
+}
 struct ArPeers { float *buf[kArMaxRanks]; };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
@@ -59,6 +68,7 @@ peer_allreduce_kernel(ArPeers peers, ArState *state, int rank, int world, const 
 {
     __shared__ int s_last, s_fail;
     const uint32_t e = *reinterpret_cast<volatile uint32_t *>(&state->epoch) + 1;
+    const uint32_t limit = spin_limit_of(state);
     const size_t half = kArFlagWords / 4 + (size_t)(e & 1) * capacity4;      // in float4 units
     float4 *mine = reinterpret_cast<float4 *>(peers.buf[rank]) + half;
     const uint32_t stride = gridDim.x * kArThreads;
@@ -79,7 +89,7 @@ peer_allreduce_kernel(ArPeers peers, ArState *state, int rank, int world, const 
         const uint32_t *flag = reinterpret_cast<const uint32_t *>(peers.buf[rank]) + threadIdx.x;
         uint32_t polls = 0;
         while ((int32_t)(ld_acquire_sys(flag) - e) < 0) {
-            if (++polls >= kArSpinLimit) { s_fail = 1; break; }
+            if (++polls >= limit) { s_fail = 1; break; }
         }
     }
     __syncthreads();
@@ -128,6 +138,7 @@ peer_allreduce_add_rmsnorm_kernel(ArPeers peers, ArState *state, int rank, int w
     __shared__ int s_last, s_fail;
     __shared__ float red[8];
     const uint32_t e = *reinterpret_cast<volatile uint32_t *>(&state->epoch) + 1;
+    const uint32_t limit = spin_limit_of(state);
     const size_t half = kArFlagWords + (size_t)(e & 1) * capacity;           // in floats
     const size_t base = (size_t)blockIdx.x * width;
     float *mine = peers.buf[rank] + half + base;
@@ -151,7 +162,7 @@ peer_allreduce_add_rmsnorm_kernel(ArPeers peers, ArState *state, int rank, int w
         const uint32_t *flag = reinterpret_cast<const uint32_t *>(peers.buf[rank]) + threadIdx.x;
         uint32_t polls = 0;
         while ((int32_t)(ld_acquire_sys(flag) - e) < 0) {
-            if (++polls >= kArSpinLimit) { s_fail = 1; break; }
+            if (++polls >= limit) { s_fail = 1; break; }
         }
     }
     __syncthreads();
@@ -226,8 +237,10 @@ peer_allreduce_add_rmsnorm_kernel(ArPeers peers, ArState *state, int rank, int w
 // The caller owns the regions and must not rewrite one until another all-reduce call has passed in
 // between (a peer may still be reading it until it has signalled its next call): two regions used
 // alternately are enough.
-__device__ __forceinline__ bool signal_and_wait(const ArPeers &peers, int rank, int world, uint32_t e, int *s_fail)
+__device__ __forceinline__ bool signal_and_wait(const ArPeers &peers, const ArState *state, int rank, int world,
+                                                uint32_t e, int *s_fail)
 {
+    const uint32_t limit = spin_limit_of(state);
     if (threadIdx.x == 0) *s_fail = 0;
     __syncthreads();
     if (blockIdx.x == 0 && threadIdx.x < (unsigned)world)      // the release is cumulative at system scope
@@ -236,7 +249,7 @@ __device__ __forceinline__ bool signal_and_wait(const ArPeers &peers, int rank, 
         const uint32_t *flag = reinterpret_cast<const uint32_t *>(peers.buf[rank]) + threadIdx.x;
         uint32_t polls = 0;
         while ((int32_t)(ld_acquire_sys(flag) - e) < 0) {
-            if (++polls >= kArSpinLimit) { *s_fail = 1; break; }
+            if (++polls >= limit) { *s_fail = 1; break; }
         }
     }
     __syncthreads();
@@ -263,7 +276,7 @@ peer_allreduce_inplace_kernel(ArPeers peers, ArState *state, int rank, int world
 {
     __shared__ int s_fail;
     const uint32_t e = *reinterpret_cast<volatile uint32_t *>(&state->epoch) + 1;
-    if (!signal_and_wait(peers, rank, world, e, &s_fail)) {
+    if (!signal_and_wait(peers, state, rank, world, e, &s_fail)) {
         if (threadIdx.x == 0) atomicExch(&state->error, e);
     } else {
         const uint32_t stride = gridDim.x * kArThreads;
@@ -294,7 +307,7 @@ peer_allreduce_inplace_add_rmsnorm_kernel(ArPeers peers, ArState *state, int ran
     __shared__ float red[8];
     const uint32_t e = *reinterpret_cast<volatile uint32_t *>(&state->epoch) + 1;
     const size_t base = (size_t)blockIdx.x * width;
-    if (!signal_and_wait(peers, rank, world, e, &s_fail)) {
+    if (!signal_and_wait(peers, state, rank, world, e, &s_fail)) {
         if (threadIdx.x == 0) atomicExch(&state->error, e);
     } else {
         // rank r + 1's row is in flight while rank r's is added: ranks in order, one NVLink round
@@ -403,6 +416,23 @@ extern "C" AB_API int ab_peer_allreduce_error(const void *state, uint32_t *faile
     if (failed_call) *failed_call = h.error;
     if (h.error) return fail(AB_ERR_TIMEOUT, "ab_peer_allreduce: call %u gave up waiting for its peers", h.error);
     return AB_OK;
+}
+
+extern "C" AB_API int ab_peer_allreduce_set_spin_limit(void *state, uint32_t polls)
+{
+    using namespace ab;
+    if (!state) return fail(AB_ERR_INVALID, "ab_peer_allreduce_set_spin_limit: NULL state");
+    return check_cuda(cudaMemcpy(static_cast<char *>(state) + offsetof(ArState, spin_limit), &polls, sizeof polls,
+                                 cudaMemcpyHostToDevice), "ab_peer_allreduce_set_spin_limit");
+}
+
+extern "C" AB_API int ab_peer_allreduce_clear_error(void *state)
+{
+    using namespace ab;
+    if (!state) return fail(AB_ERR_INVALID, "ab_peer_allreduce_clear_error: NULL state");
+    const uint32_t zero = 0;
+    return check_cuda(cudaMemcpy(static_cast<char *>(state) + offsetof(ArState, error), &zero, sizeof zero,
+                                 cudaMemcpyHostToDevice), "ab_peer_allreduce_clear_error");
 }
 
 extern "C" AB_API int ab_peer_allreduce_add_rmsnorm_f32(void *stream, void *const *peer_buffers, void *state,

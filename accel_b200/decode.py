@@ -152,6 +152,45 @@ class DecodeModel:
         self.embedding = torch.randn((cfg.vocab, d), generator=gen, device=self.device,
                                      dtype=torch.float32)
 
+    @classmethod
+    def from_host(cls, cfg: ModelConfig, device, layers, g_final, lm_head, embedding,
+                  shard: Optional[Shard] = None) -> "DecodeModel":
+        """A model from quantized planes held on the host (what a weight loader hands over).
+        `layers` is a list of dicts with the gains "g1", "g2" (f32 [d]) and the matrices "wq",
+        "wk", "wv", "wo", "wg", "wu", "wd", each a (codes u32, scales f16 bits, zeros f16 bits)
+        triple of the unsharded [K, N] matrix in quant.Int4Quantize's layout; `lm_head` is such a
+        triple, `embedding` f32 [vocab, d].  The shard's columns and rows are cut here."""
+        self = cls.__new__(cls)
+        dev = torch.device(device)
+        sh = shard if shard is not None else Shard.plan(cfg, 1, 0)
+        self.cfg, self.shard, self.device, self._quantize = cfg, sh, dev, None
+        d, D = cfg.d_model, cfg.head_dim
+        nq, nkv = cfg.n_heads * D, cfg.n_kv_heads * D
+
+        def planes(t):
+            c, s, z = (np.ascontiguousarray(a) for a in t)
+            return (torch.from_numpy(c.view(np.int32)).to(dev), torch.from_numpy(s.view(np.float16)).to(dev),
+                    torch.from_numpy(z.view(np.float16)).to(dev))
+
+        f32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(dev)
+        hq, hk, fr, vr = sh.heads, sh.kv_heads, sh.ffn, sh.vocab
+        self.layers = []
+        for src in layers:
+            L = Layer()
+            L.g1, L.g2 = f32(src["g1"]), f32(src["g2"])
+            L.wq = shard_columns(*planes(src["wq"]), d, nq, hq.start * D, hq.stop * D)
+            L.wk = shard_columns(*planes(src["wk"]), d, nkv, hk.start * D, hk.stop * D)
+            L.wv = shard_columns(*planes(src["wv"]), d, nkv, hk.start * D, hk.stop * D)
+            L.wo = shard_rows(*planes(src["wo"]), nq, d, hq.start * D, hq.stop * D)
+            L.wg = shard_columns(*planes(src["wg"]), d, cfg.ffn, fr.start, fr.stop)
+            L.wu = shard_columns(*planes(src["wu"]), d, cfg.ffn, fr.start, fr.stop)
+            L.wd = shard_rows(*planes(src["wd"]), cfg.ffn, d, fr.start, fr.stop)
+            self.layers.append(L)
+        self.g_final = f32(g_final)
+        self.lm_head = shard_columns(*planes(lm_head), d, cfg.vocab, vr.start, vr.stop)
+        self.embedding = f32(embedding)
+        return self
+
     def int4_bytes(self) -> int:
         n = self.lm_head.nbytes
         for L in self.layers:
@@ -474,11 +513,21 @@ class DecodeEngine:
         if self._pin is None:
             self._pin = torch.empty(packed.size, dtype=I32).pin_memory()
             self._out_pin = torch.empty(self.batch, dtype=I32).pin_memory()
+            self._err_pin = torch.zeros(1, dtype=I32).pin_memory()
         self._pin.numpy()[:] = packed
         self.inputs.copy_(self._pin, non_blocking=True)
         self.run_step()
         self._out_pin.copy_(self.next_tokens, non_blocking=True)
+        if self._peer is not None:
+            self._err_pin.copy_(self._peer.error_word, non_blocking=True)
         torch.cuda.current_stream(self.dev).synchronize()
+        if self._peer is not None and int(self._err_pin[0]) != 0:
+            # a bounded wait for a peer ran out: this step's sums are not the all-reduced ones.
+            # The rank stops here; its peers' next all-reduce runs out the same way and they stop too.
+            from . import _lib
+            raise _lib.AccelError(_lib.AB_ERR_TIMEOUT,
+                                  f"decode step: peer all-reduce call {int(self._err_pin[0])} gave up "
+                                  "waiting for its peers; the sampled tokens of this step are invalid")
         self.lengths_host += 1
         return self._out_pin.numpy().copy()
 

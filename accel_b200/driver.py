@@ -60,8 +60,9 @@ class Block:
         return dst
 
     def free(self):
+        """Refused (AB_ERR_BUSY) while a live executable still names the block."""
         if self._h:
-            _lib.lib().ab_block_free(self._h)
+            _lib.check(_lib.lib().ab_block_free(self._h))
             self._h = None
 
 

@@ -121,3 +121,17 @@ class PeerAllReduce:
     def check(self) -> None:
         """Synchronous: raises when a call of this rank gave up waiting for its peers."""
         _lib.check(_lib.lib().ab_peer_allreduce_error(C.c_void_p(self._state.data_ptr()), None))
+
+    def set_spin_limit(self, polls: int) -> None:
+        """How long a call waits for its peers before giving up, in polls of a flag (0: the
+        default, about a second)."""
+        _lib.check(_lib.lib().ab_peer_allreduce_set_spin_limit(C.c_void_p(self._state.data_ptr()), int(polls)))
+
+    def clear_error(self) -> None:
+        _lib.check(_lib.lib().ab_peer_allreduce_clear_error(C.c_void_p(self._state.data_ptr())))
+
+    @property
+    def error_word(self) -> torch.Tensor:
+        """The device word that holds the 1-based number of the call that gave up (0: none); a
+        caller that already reads results back every step can read this beside them."""
+        return self._state[3:4]

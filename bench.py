@@ -87,43 +87,79 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------
 # reference arm: the oracle's layer sample on the host cores
 # ----------------------------------------------------------------------------------------------
-def cpu_sample(steps: int, warmup: int, layers: int = 32):
-    """Times one layer of the step per 'step' (plus the lm_head once) and scales to the 32 layers
-    a token needs.  Returns (tok/s, seconds per layer, seconds for the head, cores)."""
+def cpu_sample(steps: int, warmup: int, layers: int = 32, budget_s: float = 20.0, sample=None):
+    """The CPU baseline beside the GPU number: times ONE of the step's layers per sample (plus the
+    lm_head and argmax once) on every host core and scales to the `layers` a token needs.
+    Returns (tok/s, seconds per layer, seconds for the head, threads used)."""
     import oracle
     from oracle.step import LayerSample
-    s = LayerSample()
+    cores = oracle.set_threads()             # not the launcher's OMP_NUM_THREADS
+    s = sample if sample is not None else LayerSample()
     x = None
     for _ in range(max(warmup, 0)):
         _, x = s.time_layer()
-    times = []
+    times, t_begin = [], time.perf_counter()
     for _ in range(max(steps, 1)):
         t, x = s.time_layer()
         times.append(t)
+        if time.perf_counter() - t_begin > budget_s:
+            break
     t_head = s.time_head(x)
     t_layer = statistics.median(times)
     step_s = layers * t_layer + t_head
-    return s.B / step_s, t_layer, t_head, oracle.threads()
+    return s.B / step_s, t_layer, t_head, cores
 
 
 def run_reference(args):
+    """The reference arm: accel's CPU kernels (their C restatement; the Go module cannot be built
+    without a Go toolchain) on every host core, the same decode step as the GPU arm.  A step runs
+    the layer `layers` times and the lm_head + argmax once, as a token does; when that would not
+    finish in a few minutes the step runs fewer layer passes and is scaled, and says so."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = min(args.steps, 20)
-    toks, t_layer, t_head, cores = cpu_sample(steps, min(args.warmup, 3))
+    import oracle
+    from oracle.step import LayerSample
+    cores = oracle.set_threads()             # torch.distributed.run exports OMP_NUM_THREADS=1
+    s = LayerSample(batch=args.batch, context=args.context)
+    layers, steps, warmup = args.layers, args.steps, args.warmup
+    t_probe, x = s.time_layer()              # untimed probe: sizes the sample
+    budget_s = float(os.environ.get("AB_REFERENCE_BUDGET_S", "240"))
+    passes = max(1, min(layers, int(budget_s / max(t_probe * (steps + warmup), 1e-9))))
+
+    def one_step():
+        nonlocal x
+        t0 = time.perf_counter()
+        for _ in range(passes):
+            x = s.layer()
+        t_layers = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        s.head_and_argmax(x)
+        return t_layers, time.perf_counter() - t0
+
+    for _ in range(warmup):
+        one_step()
+    w0 = time.perf_counter()
+    runs = [one_step() for _ in range(steps)]
+    wall = time.perf_counter() - w0
+    t_layers = sum(r[0] for r in runs) / steps
+    t_head = sum(r[1] for r in runs) / steps
+    step_s = t_layers * layers / passes + t_head
+    toks = s.B / step_s
+    sample = (f"every step runs the layer {passes} time(s) of the {layers} a token needs"
+              + ("" if passes == layers else f" (scaled x{layers}/{passes} to the full step)")
+              + f" and the lm_head + argmax once, batch {s.B}, context {s.context}; wall time of the "
+              f"{steps} timed steps {wall:.1f} s; C restatement of accel's CPU kernels, OpenMP over "
+              "workgroups; the Go backend itself cannot be built here (no Go toolchain)")
     line = {
         "impl": "reference", "metric": METRIC, "value": toks, "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": 1e3 * (32 * t_layer + t_head),
+        "steps": steps, "warmup": warmup, "ms_per_step": 1e3 * step_s,
+        "ms_per_step_as_run": 1e3 * wall / steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "kv_cache": "f32"},
-        "cpu_baseline": {"value": toks, "unit": "tok/s", "cores": cores, "kind": "port",
-                         "sample": "each step times 1 of the 32 layers of the same decode step "
-                                   "(batch 16, context 2048) and the lm_head + argmax once; "
-                                   "tok/s = 16 / (32 x median layer time + head time); C "
-                                   "restatement of accel's CPU kernels, OpenMP over workgroups; the "
-                                   "Go backend itself cannot be built here (no Go toolchain)"},
+        "config": {"workload": WORKLOAD, "batch": s.B, "context": s.context, "layers": layers,
+                   "kv_cache": "f32", "parallelism": "host cores", "layer_passes_per_step": passes},
+        "cpu_baseline": {"value": toks, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": toks, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -341,11 +377,11 @@ def run_b200(args):
         import datetime
         import faulthandler
         # a rank that never arrives must end the run with an error and a stack, not hang it
-        faulthandler.dump_traceback_later(int(os.environ.get("AB_BENCH_WATCHDOG_S", "600")), exit=True)
+        faulthandler.dump_traceback_later(int(os.environ.get("AB_BENCH_WATCHDOG_S", "900")), exit=True)
         # no NVLink multicast objects: a rank that dies while bound to one faults its peers' GPUs
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=600))
         group = dist.group.WORLD
 
     cache_dtype = torch.float16 if args.kv == "f16" else torch.float32
@@ -390,6 +426,44 @@ def run_b200(args):
     torch.cuda.synchronize()
     log("step captured")
     t_setup = time.perf_counter() - t_setup
+
+    # ---- parity of the sharded step, outside every timed region: the first step's logits and
+    # greedy ids on N ranks against the same step of the unsharded model, built once on rank 0
+    # from the same seeds (the ranks' shards are cut from bit-identical matrices)
+    tp_parity = None
+    if world > 1 and not args.no_tp_parity:
+        engine.set_inputs(first)
+        engine.run_step()
+        torch.cuda.synchronize()
+        tp_logits = engine.logits.clone()
+        tp_ids = engine.next_tokens.clone()
+        if rank == 0:
+            m1 = dec.DecodeModel(cfg, dec.Shard.plan(cfg, 1, 0), dev, seed=1234)
+            e1 = dec.DecodeEngine(m1, B, max_context=ctx + total_steps + 16)
+            e1.fill_context(ctx, seed=7)
+            for s_ in range(B):
+                e1.reserve(s_, ctx + total_steps + 8)
+            e1.upload_pages()
+            e1.set_inputs(first)
+            e1.prepare()
+            e1.record_step()
+            torch.cuda.synchronize()
+            ref = e1.logits
+            top2 = torch.topk(ref, 2, dim=1).values
+            clear = (top2[:, 0] - top2[:, 1]) > 2e-3 * ref.abs().max()
+            tp_parity = {
+                "tp_vs_tp1_rel_err": float((tp_logits - ref).abs().max() / ref.abs().max()),
+                "rows_with_clear_argmax": int(clear.sum()), "rows": B,
+                "ids_equal_on_clear_rows": bool(torch.equal(tp_ids[clear], e1.next_tokens[clear])),
+                "what": "first decode step, logits [batch, vocab] and greedy ids, N ranks against "
+                        "the unsharded model on rank 0 (same seeds, same cache contents)"}
+            del e1, m1, ref
+            torch.cuda.empty_cache()
+        # the other ranks wait here for rank 0: their next peer all-reduce would give up after its
+        # bounded wait if rank 0 were still building the unsharded model
+        torch.cuda.synchronize()
+        dist.barrier()
+        log("tp parity checked")
 
     stream = torch.cuda.current_stream(dev)
 
@@ -515,9 +589,17 @@ def run_b200(args):
                 "matrices_rotated": len(mats)}
 
     # ---- CPU baseline beside it (rank 0, N = 1 only): the oracle's layer sample
-    cpu = None
+    cpu, layer_par = None, None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        toks, t_layer, t_head, cores = cpu_sample(3, 1)
+        # parity at the benchmarked shape first (the GPU leg wants the sample's pristine cache):
+        # one full-size layer + lm_head + argmax, this library on the GPU against the oracle
+        from oracle.step import LayerSample, layer_parity
+        sample = LayerSample(batch=B, context=ctx)
+        layer_par = layer_parity(sample, dev)
+        layer_par["what"] = ("one full-size layer of the benchmarked step (batch %d, context %d, d 4096, "
+                             "32 heads x 128, ffn 11008, f32 cache) + lm_head + argmax, GPU against the "
+                             "CPU oracle on identical seeded inputs" % (B, ctx))
+        toks, t_layer, t_head, cores = cpu_sample(3, 1, sample=sample)
         cpu = {"value": toks, "unit": "tok/s", "cores": cores, "kind": "port",
                "sample": f"1 of 32 layers of the same step timed 3 times (median {t_layer:.3f} s) + "
                          f"lm_head and argmax once ({t_head:.3f} s), scaled to 32 layers; C "
@@ -557,6 +639,7 @@ def run_b200(args):
             "int4_gemv": gemv,
             "peer_allreduce_ranks_timed_out": peer_timeouts,
             "cpu_baseline": cpu,
+            "parity": {"layer_vs_oracle": layer_par, "tensor_parallel": tp_parity},
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -582,6 +665,8 @@ def main():
     ap.add_argument("--kv", default="f32", choices=["f32", "f16"],
                     help="KV cache dtype; f32 is what the reference's batched decode kernel reads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp-parity", action="store_true",
+                    help="skip the N-rank against one-rank comparison of the first step (N > 1)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="keep every operator on one stream")
     ap.add_argument("--force-overlap", action="store_true", help="side-stream overlap at N > 1 too")

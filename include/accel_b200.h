@@ -80,6 +80,8 @@ AB_API void *ab_block_device_ptr(ab_block *b);    /* the device address (no acce
 AB_API size_t ab_block_size(ab_block *b);
 AB_API int ab_block_write(ab_block *b, size_t off, const void *src, size_t n);  /* synchronous   */
 AB_API int ab_block_read(ab_block *b, size_t off, void *dst, size_t n);         /* synchronous   */
+/* Refused with AB_ERR_BUSY while a live executable names the block, directly or through a bound
+ * slot: children are closed before parents (docs/architecture.md:306-310). */
 AB_API int ab_block_free(ab_block *b);
 
 /* driver.KernelSupport.SupportsKernel (internal/driver/plan.go:424-428): AB_OK when this library
@@ -135,6 +137,9 @@ AB_API int ab_exec_set_uniform(ab_exec *e, int node, int index, const void *std1
 AB_API int ab_exec_set_payload(ab_exec *e, int node, const void *bytes, size_t n);
 AB_API int ab_exec_submit(ab_exec *e, ab_fence **out);     /* begins the work, does not wait */
 AB_API int ab_exec_close(ab_exec *e);
+/* driver.Fence (internal/driver/plan.go:374-391).  Once the device is lost every outstanding fence
+ * reports AB_ERR_DEVICE_LOST.  The executable accepts its next submission as soon as the fence
+ * has been waited for, has answered 1 to ab_fence_done, or has been freed (which waits). */
 AB_API int ab_fence_wait(ab_fence *f);                     /* AB_ERR_DEVICE_LOST on loss */
 AB_API int ab_fence_done(ab_fence *f);                     /* 1 done, 0 running, <0 error */
 AB_API uint64_t ab_fence_elapsed_ns(ab_fence *f);          /* driver.Timer.Elapsed; 0 if untimed */
@@ -317,6 +322,11 @@ AB_API int ab_peer_allreduce_inplace_add_rmsnorm_f32(void *stream, void *const *
                                                      uint32_t width, uint32_t eps_bits, size_t buffer_bytes);
 /* AB_OK, or AB_ERR_TIMEOUT with *failed_call = the 1-based call that gave up (synchronous). */
 AB_API int ab_peer_allreduce_error(const void *state, uint32_t *failed_call);
+/* How many polls of a peer's flag a CTA spends before it gives up (0 restores the default, about a
+ * second).  A call that gave up still advances the call counter, so the sequence stays aligned
+ * with the peers'; ab_peer_allreduce_clear_error forgets the recorded failure.  Both synchronous. */
+AB_API int ab_peer_allreduce_set_spin_limit(void *state, uint32_t polls);
+AB_API int ab_peer_allreduce_clear_error(void *state);
 
 #ifdef __cplusplus
 }

@@ -54,13 +54,29 @@ def lib() -> C.CDLL:
         L.orc_int4_error_bound.restype = C.c_double
         L.orc_int4_nibble.restype = C.c_uint32
         L.orc_blockpool_new.restype = C.c_void_p
+        L.orc_set_threads.argtypes = [C.c_int]
+        L.orc_max_threads.restype = C.c_int
     return _lib
 
 
 def threads() -> int:
-    """How many host threads the OpenMP loops use (OMP_NUM_THREADS, else every core)."""
-    env = os.environ.get("OMP_NUM_THREADS")
-    return int(env) if env else (os.cpu_count() or 1)
+    """How many host threads the OpenMP loops use right now."""
+    return int(lib().orc_max_threads())
+
+
+def host_cores() -> int:
+    """Cores this process may run on (its affinity mask, else every core)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        return os.cpu_count() or 1
+
+
+def set_threads(n: int | None = None) -> int:
+    """Sets the OpenMP thread count of the loops (default: every core this process may use),
+    whatever OMP_NUM_THREADS said when the library was loaded.  Returns the count in use."""
+    lib().orc_set_threads(int(n) if n else host_cores())
+    return threads()
 
 
 def _c(a, dt):

@@ -23,8 +23,32 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #define ORC_API __attribute__((visibility("default")))
+
+/* How many host threads the parallel loops below use.  A launcher may export OMP_NUM_THREADS=1 to
+ * its children (torch.distributed.run does); the timed CPU baseline overrides that here so that it
+ * always runs on the cores the host really has. */
+ORC_API void orc_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+ORC_API int orc_max_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
 
 /* ------------------------------------------------------------------------------------------ */
 /* f32 <-> f16, internal/kernel/narrow.go:67-140                                               */

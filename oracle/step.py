@@ -79,3 +79,56 @@ class LayerSample:
         t0 = time.perf_counter()
         self.head_and_argmax(x)
         return time.perf_counter() - t0
+
+
+def gpu_step_of(sample: "LayerSample", device="cuda:0"):
+    """The same layer + lm_head + argmax run by the product on a GPU, from this sample's weights,
+    cache contents, page table and activations: the thing the oracle checks.  Returns the hidden
+    state after the layer [B, d], the logits [B, V] and the sampled ids [B] as numpy arrays."""
+    import torch
+
+    from accel_b200 import decode as dec
+    s = sample
+    cfg = dec.ModelConfig(layers=1, d_model=s.d, n_heads=s.H, n_kv_heads=s.KH, head_dim=s.D, ffn=s.F,
+                          vocab=s.V, eps=1e-5, rope_base=10000.0, block=s.block,
+                          cache_dtype=torch.float32)
+    emb = np.zeros((s.V, s.d), np.float32)
+    emb[:s.B] = s.x                                  # token i of the batch embeds to row i of x
+    layer = {"g1": s.g1, "g2": s.g2, "wq": s.wq, "wk": s.wk, "wv": s.wv, "wo": s.wo, "wg": s.wg,
+             "wu": s.wu, "wd": s.wd}
+    model = dec.DecodeModel.from_host(cfg, device, [layer], s.g1, s.head, emb)
+    eng = dec.DecodeEngine(model, s.B, max_context=s.max_pages * s.block)
+    assert eng.max_pages == s.max_pages and eng.capacity == s.kc.shape[0]
+    eng.k_cache[0].copy_(torch.from_numpy(s.kc))
+    eng.v_cache[0].copy_(torch.from_numpy(s.vc))
+    eng.page_rows = [list(map(int, row)) for row in s.pages]
+    eng.upload_pages()
+    eng.lengths_host[:] = s.context
+    eng.set_inputs(np.arange(s.B))
+    eng.prepare()
+    eng.record_step()
+    torch.cuda.synchronize()
+    return (eng._final_x.cpu().numpy(), eng.logits.cpu().numpy(),
+            eng.next_tokens.cpu().numpy().astype(np.int64))
+
+
+def layer_parity(sample: "LayerSample", device="cuda:0") -> dict:
+    """Runs the sample's layer + head on the CPU oracle and on the GPU and compares them: the
+    hidden state's error relative to its largest magnitude, and whether the greedy ids agree on
+    every row whose two best oracle logits are clearly apart.  The oracle leg mutates the sample's
+    cache (it appends this step's K/V), so the GPU leg runs first on the pristine cache."""
+    hidden, logits, ids = gpu_step_of(sample, device)
+    want = sample.layer()
+    h = orc.rmsnorm(want, sample.g1, 1e-5)
+    want_logits = orc.quant_matmul_int4(h, *sample.head, sample.B, sample.V, sample.d)
+    want_ids = orc.sample_argmax(want_logits).astype(np.int64)
+    scale = float(np.max(np.abs(want)))
+    top2 = np.sort(want_logits, axis=1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 2e-3 * float(np.max(np.abs(want_logits)))
+    return {
+        "hidden_rel_err": float(np.max(np.abs(hidden.astype(np.float64) - want)) / scale),
+        "logits_rel_err": float(np.max(np.abs(logits.astype(np.float64) - want_logits))
+                                / float(np.max(np.abs(want_logits)))),
+        "rows_with_clear_argmax": int(clear.sum()), "rows": int(sample.B),
+        "ids_equal_on_clear_rows": bool(np.array_equal(ids[clear], want_ids[clear])),
+    }

@@ -20,7 +20,10 @@ def main():
     shapes = [tuple(int(v) for v in s.split("x")) for s in sys.argv[1:]]
     for M, K, N in shapes:
         w = normal(2, (K, N), 0.02)
-        w[3 * N:3 * N + 128] = 0.25                  # one constant group (scale 0)
+        # constant groups (scale 0, the value carried by the zero point): row 3's first group and,
+        # where the row has more than one group, the last group of the last row
+        w.reshape(-1)[3 * N:3 * N + 128] = 0.25
+        w.reshape(-1)[K * N - 128:] = -0.125
         p, s, z = orc.int4_quantize(w)
         a = normal(1, (M, K))
         want = orc.quant_matmul_int4(a, p, s, z, M, N, K) if M > 1 else \

@@ -154,3 +154,51 @@ def test_loss_is_injected_on_the_host_and_is_sticky():
     with pytest.raises(D.DeviceLost):
         dev.alloc(64)
     exe.close(); b.free(); dev.close()
+
+
+def test_a_block_cannot_be_freed_under_a_live_executable():
+    # children before parents: an executable holds device addresses resolved from its blocks
+    dev = D.Device(0)
+    a, b, spare = dev.alloc(4096), dev.alloc(4096), dev.alloc(4096)
+    a.write(0, np.ones(16, np.float32))
+    exe = dev.compile([D.Dispatch("ElemAdd", [op(a, 64), op(a, 64), D.Operand(slot=1, size=64)])], n_slots=1)
+    exe.rebind([(1, b, 0)])
+    for blk in (a, b):
+        with pytest.raises(D.AccelError, match="still name this block"):
+            blk.free()
+    exe.rebind([(1, spare, 0)])           # b is no longer named by the executable
+    b.free()
+    f = exe.submit(); f.wait()
+    assert np.array_equal(spare.read(0, np.zeros(16, np.float32)), np.full(16, 2.0, np.float32))
+    exe.close()
+    a.free(); spare.free()
+    dev.close()
+
+
+def test_a_fence_that_was_only_polled_or_freed_releases_its_executable():
+    dev = D.Device(0)
+    b = dev.alloc(4096)
+    b.write(0, np.ones(16, np.float32))
+    exe = dev.compile([D.Dispatch("ElemAdd", [op(b, 64), op(b, 64), op(b, 64, 256)])])
+    f = exe.submit()
+    while not f.done():                   # completion learnt by polling, never waited for
+        pass
+    f2 = exe.submit()                     # not refused as busy
+    f2.free()                             # freed unwaited: the executable is released all the same
+    f3 = exe.submit(); f3.wait()
+    exe.close(); b.free(); dev.close()
+
+
+def test_every_outstanding_fence_reports_an_injected_loss():
+    dev = D.Device(0, lose_at_submission=2)
+    b = dev.alloc(4096)
+    b.write(0, np.ones(16, np.float32))
+    e1 = dev.compile([D.Dispatch("ElemAdd", [op(b, 64), op(b, 64), op(b, 64, 256)])])
+    e2 = dev.compile([D.Dispatch("ElemAdd", [op(b, 64), op(b, 64), op(b, 64, 512)])])
+    f1 = e1.submit()                      # submission 1: runs
+    f2 = e2.submit()                      # submission 2: the loss is injected here, on the host
+    with pytest.raises(D.DeviceLost):
+        f1.wait()                         # the earlier fence reports the loss too
+    with pytest.raises(D.DeviceLost):
+        f2.wait()
+    e1.close(); e2.close(); b.free(); dev.close()

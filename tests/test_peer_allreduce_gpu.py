@@ -39,6 +39,50 @@ def test_single_rank_is_a_copy_and_replays_from_a_graph():
     ar.check()
 
 
+def test_a_wait_that_runs_out_reports_a_timeout_and_the_next_call_stays_aligned():
+    """Two "ranks" whose buffers both live on this GPU; rank 1 never calls.  Rank 0's wait is given
+    2^14 polls: the kernel must return, leave the output alone, record call 1 as timed out, and
+    still count the call, so that call 2 (for which rank 1's signal and data are put in place by
+    hand) sums correctly.  A wait that gives up is an ordinary return: nothing here can hang."""
+    import ctypes as C
+    dev = torch.device("cuda:0")
+    L = _lib.lib()
+    cap, n = 1024, 512
+    nbytes = int(L.ab_peer_allreduce_buffer_bytes(cap))
+    bufs = [torch.zeros(nbytes // 4, dtype=torch.float32, device=dev) for _ in range(2)]
+    state = torch.zeros(int(L.ab_peer_allreduce_state_bytes()) // 4, dtype=torch.int32, device=dev)
+    ptrs = (C.c_void_p * 2)(bufs[0].data_ptr(), bufs[1].data_ptr())
+    sp = C.c_void_p(state.data_ptr())
+    _lib.check(L.ab_peer_allreduce_set_spin_limit(sp, 1 << 14))
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    x = torch.randn(n, device=dev)
+    out = torch.full((n,), -7.0, device=dev)
+    _lib.check(L.ab_peer_allreduce_f32(stream, ptrs, sp, 0, 2, C.c_void_p(x.data_ptr()),
+                                       C.c_void_p(out.data_ptr()), n, cap))
+    torch.cuda.synchronize()
+    assert torch.all(out == -7.0), "a call that gave up must not write its output"
+    failed = C.c_uint32(0)
+    rc = L.ab_peer_allreduce_error(sp, C.byref(failed))
+    assert rc == _lib.AB_ERR_TIMEOUT and failed.value == 1
+    with pytest.raises(_lib.AccelError, match="gave up waiting"):
+        _lib.check(rc)
+    assert int(state[0]) == 1, "the call counter advances even when the call gave up"
+
+    # call 2 uses data half 0 (epoch & 1): rank 1's part and its flag for call 2, placed by hand
+    _lib.check(L.ab_peer_allreduce_clear_error(sp))
+    other = torch.randn(n, device=dev)
+    bufs[1][64:64 + n] = other                                   # behind the 64 flag words
+    bufs[0].view(torch.int32)[1] = 2                             # flag[rank 1] in rank 0's buffer
+    torch.cuda.synchronize()
+    _lib.check(L.ab_peer_allreduce_f32(stream, ptrs, sp, 0, 2, C.c_void_p(x.data_ptr()),
+                                       C.c_void_p(out.data_ptr()), n, cap))
+    torch.cuda.synchronize()
+    assert L.ab_peer_allreduce_error(sp, None) == 0
+    assert torch.equal(out, x + other)
+    assert int(state[0]) == 2
+
+
 def test_refusals():
     dev = torch.device("cuda:0")
     ar = PeerAllReduce(1024, dev)
