@@ -134,6 +134,9 @@ SYMBOLS = [
     ("ab_blockpool_grow", C.c_int, [_P, _P, C.c_int, C.c_int]),
     ("ab_blockpool_free", C.c_int, [_P, _P, C.c_int]),
     ("ab_blockpool_positions", C.c_int, [_P, C.c_int]),
+    ("ab_int4_prepack_bytes", C.c_size_t, [C.c_uint32, C.c_uint32]),
+    ("ab_int4_prepack", C.c_int, [_P, _P, _P, _P, C.c_uint32, C.c_uint32, _P]),
+    ("ab_int4_stream_error", C.c_int, []),
     ("ab_int4_column_split", C.c_int, [C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_uint32),
                                        C.POINTER(C.c_uint32)]),
 ]

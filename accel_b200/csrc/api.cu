@@ -87,6 +87,10 @@ int sm_count()
 static const KernelEntry kKernels[] = {
     {"QuantMatVecInt4", 5, 16, launch_quant_matvec_int4},
     {"QuantMatMulInt4", 5, 16, launch_quant_matmul_int4},
+    {"QuantMatVecInt4Packed", 3, 16, launch_quant_matvec_int4_packed},
+    {"QuantMatMulInt4Packed", 3, 16, launch_quant_matmul_int4_packed},
+    {"QuantMatMulInt4PackedSplit3", 5, 32, launch_quant_matmul_int4_packed_split3},
+    {"QuantMatMulInt4PackedSwiGLU", 3, 16, launch_quant_matmul_int4_packed_swiglu},
     {"AttentionDecode", 5, 16, launch_attention_decode},
     {"AttentionDecodeF16", 5, 16, launch_attention_decode_f16},
     {"AttentionDecodePaged", 6, 32, launch_attention_decode_paged},

@@ -77,6 +77,20 @@ Int4TcPlan plan_int4_tc(uint32_t M, uint32_t N, uint32_t K);
 int run_int4_tc(const Launch &l, const Int4TcPlan &p, float *dst, uint32_t M, uint32_t N, uint32_t K);
 int int4_tc_error_flag();       // nonzero once a bounded device-side wait has run out
 
+// the decode-batch int4 kernel over prepacked weights: bulk copies, tensor memory, tcgen05 (int4_stream.cu)
+bool int4_stream_ok(uint32_t M, uint32_t N, uint32_t K);
+size_t int4_stream_packed_bytes(uint32_t N, uint32_t K);
+int run_int4_prepack(cudaStream_t stream, const uint32_t *codes, const uint16_t *scales, const uint16_t *zeros,
+                     unsigned char *packed, uint32_t N, uint32_t K);
+size_t int4_stream_workspace(uint32_t M);
+int run_int4_stream(cudaStream_t stream, const float *a, const float *amax, const unsigned char *packed, float *out,
+                    uint32_t M, uint32_t N, uint32_t K, uint32_t ldo, void *scratch, bool dependent);
+int int4_stream_error_flag();
+int launch_quant_matvec_int4_packed(Launch &);
+int launch_quant_matmul_int4_packed(Launch &);
+int launch_quant_matmul_int4_packed_split3(Launch &);
+int launch_quant_matmul_int4_packed_swiglu(Launch &);
+
 // launchers, one per reference kernel name (defined beside their kernels)
 int launch_quant_matvec_int4(Launch &);
 int launch_quant_matmul_int4(Launch &);

@@ -88,6 +88,42 @@ class Int4Matrix:
         return self.codes.numel() * 4 + self.scales.numel() * 2 + self.zeros.numel() * 2
 
 
+@dataclass
+class PackedMatrix:
+    """An int4 matrix in the decode kernels' stream layout (quant.int4_prepack)."""
+    packed: torch.Tensor     # int32 words
+    K: int
+    N: int
+
+    @property
+    def nbytes(self) -> int:
+        return self.packed.numel() * 4
+
+
+def pack(m: Int4Matrix) -> PackedMatrix:
+    from .quant import int4_prepack
+    return PackedMatrix(int4_prepack(m.codes, m.scales, m.zeros, m.K, m.N), m.K, m.N)
+
+
+def concat_columns(mats) -> Int4Matrix:
+    """[K, N1 | N2 | ...]: matrices of equal K side by side (whole 128-column groups each)."""
+    K = mats[0].K
+    c = torch.cat([m.codes.view(K, m.N // 8) for m in mats], dim=1).contiguous().view(-1)
+    s = torch.cat([m.scales.view(K, m.N // 128) for m in mats], dim=1).contiguous().view(-1)
+    z = torch.cat([m.zeros.view(K, m.N // 128) for m in mats], dim=1).contiguous().view(-1)
+    return Int4Matrix(c, s, z, K, sum(m.N for m in mats))
+
+
+def interleave_groups(a: Int4Matrix, b: Int4Matrix) -> Int4Matrix:
+    """[K, 2N] whose 128-column groups alternate a's and b's: group 2j is a's group j, 2j + 1 is b's."""
+    K, G = a.K, a.N // 128
+    assert (b.K, b.N) == (a.K, a.N)
+    c = torch.stack([a.codes.view(K, G, 16), b.codes.view(K, G, 16)], dim=2).contiguous().view(-1)
+    s = torch.stack([a.scales.view(K, G), b.scales.view(K, G)], dim=2).contiguous().view(-1)
+    z = torch.stack([a.zeros.view(K, G), b.zeros.view(K, G)], dim=2).contiguous().view(-1)
+    return Int4Matrix(c, s, z, K, 2 * a.N)
+
+
 def shard_columns(codes, scales, zeros, K, N, b, e) -> Int4Matrix:
     """Columns [b, e) of a packed [K, N] matrix; b and e are multiples of 128."""
     c = codes.view(K, N // 8)[:, b // 8:e // 8].contiguous().view(-1)
@@ -105,7 +141,9 @@ def shard_rows(codes, scales, zeros, K, N, b, e) -> Int4Matrix:
 
 
 class Layer:
-    __slots__ = ("g1", "g2", "wq", "wk", "wv", "wo", "wg", "wu", "wd")
+    # wqkv, wo_p, wgu, wd_p: the same matrices prepacked for the decode kernels (GPU models): q | k | v
+    # side by side, gate and up interleaved by 128-column group
+    __slots__ = ("g1", "g2", "wq", "wk", "wv", "wo", "wg", "wu", "wd", "wqkv", "wo_p", "wgu", "wd_p")
 
 
 class DecodeModel:
@@ -114,7 +152,7 @@ class DecodeModel:
     ranks together are bit-for-bit the unsharded model."""
 
     def __init__(self, cfg: ModelConfig, shard: Shard, device, seed: int = 1234, ops=rt,
-                 quantize=None, std: float = 0.02):
+                 quantize=None, std: float = 0.02, prepack: bool = True):
         self.cfg, self.shard, self.device = cfg, shard, torch.device(device)
         d, D = cfg.d_model, cfg.head_dim
         gen = torch.Generator(device=self.device)
@@ -151,6 +189,25 @@ class DecodeModel:
         gen.manual_seed(seed * 1000003 + 999003)
         self.embedding = torch.randn((cfg.vocab, d), generator=gen, device=self.device,
                                      dtype=torch.float32)
+        self.packed = False
+        if prepack and self.device.type == "cuda":
+            self.prepack()
+
+    def prepack(self, keep_planes: bool = True):
+        """The load-time permutation of every matrix into the decode kernels' stream layout; q, k and
+        v become one matrix (one product, three outputs), gate and up one matrix whose groups
+        alternate (one product with SwiGLU in its epilogue).  keep_planes=False drops the
+        reference-layout planes of the layers afterwards (the oracle-side step and the unfused
+        path need them; a serving process does not)."""
+        for L in self.layers:
+            L.wqkv = pack(concat_columns([L.wq, L.wk, L.wv]))
+            L.wo_p = pack(L.wo)
+            L.wgu = pack(interleave_groups(L.wg, L.wu))
+            L.wd_p = pack(L.wd)
+            if not keep_planes:
+                L.wq = L.wk = L.wv = L.wo = L.wg = L.wu = L.wd = None
+        self.lm_head_p = pack(self.lm_head)
+        self.packed = True
 
     @classmethod
     def from_host(cls, cfg: ModelConfig, device, layers, g_final, lm_head, embedding,
@@ -189,9 +246,15 @@ class DecodeModel:
         self.g_final = f32(g_final)
         self.lm_head = shard_columns(*planes(lm_head), d, cfg.vocab, vr.start, vr.stop)
         self.embedding = f32(embedding)
+        self.packed = False
+        if dev.type == "cuda":
+            self.prepack()
         return self
 
     def int4_bytes(self) -> int:
+        """Bytes of int4 weights one step streams (either layout: the prepack is a permutation)."""
+        if self.packed:
+            return self.lm_head_p.nbytes + sum(m.nbytes for L in self.layers for m in (L.wqkv, L.wo_p, L.wgu, L.wd_p))
         n = self.lm_head.nbytes
         for L in self.layers:
             n += sum(m.nbytes for m in (L.wq, L.wk, L.wv, L.wo, L.wg, L.wu, L.wd))
@@ -208,7 +271,7 @@ class DecodeEngine:
     captured once as a CUDA graph and replayed."""
 
     def __init__(self, model: DecodeModel, batch: int, max_context: int, ops=rt, group=None,
-                 collective: str = "nccl"):
+                 collective: str = "nccl", use_packed: Optional[bool] = None):
         """collective: how the row-parallel products are summed over the ranks: "nccl" (the
         process group's all-reduce) or "peer" (this library's one-shot kernel over NVLink peer
         memory, peer.PeerAllReduce; GPUs only)."""
@@ -220,6 +283,8 @@ class DecodeEngine:
         # bit-identical to the chain of reference operators it replaces); an operator table that
         # only knows the reference names, like the oracle's, gets the chain
         self.fuse = ops is rt
+        # prepacked weights and the kernels that read them (q | k | v and gate | up as one product each)
+        self.use_packed = ops is rt and getattr(model, "packed", False) and use_packed is not False
         self.batch = batch
         dev = model.device
         self.dev = dev
@@ -341,8 +406,11 @@ class DecodeEngine:
         self.ops.launch(name, bindings, uniform)
         self._count += 1
 
-    def _linear(self, a, w: Int4Matrix, out):
+    def _linear(self, a, w, out):
         M = a.shape[0]
+        if isinstance(w, PackedMatrix):
+            self._launch("QuantMatMulInt4Packed", [a, w.packed, out], _u("<IIII", M, w.N, w.K, 0))
+            return
         self._launch("QuantMatMulInt4", [a, w.codes, w.scales, w.zeros, out],
                      _u("<IIII", M, w.N, w.K, 0))
 
@@ -442,8 +510,14 @@ class DecodeEngine:
                     L("CastF32ToF16", [self.v, vrows])
                 L(scatter, [vrows, self.slots, self.v_cache[li]], rp)
 
-            # q, k and v depend only on h: three branches that may run side by side
-            self._parallel([q_branch, k_branch, v_branch])
+            if self.use_packed and self.fuse:
+                # one product over q | k | v, each written to its own buffer
+                w = lay.wqkv
+                L("QuantMatMulInt4PackedSplit3", [self.h, w.packed, self.q, self.k, self.v],
+                  _u("<IIIIIIII", B, w.N, w.K, self.hq * D, self.hk * D, 0, 0, 0))
+            else:
+                # q, k and v depend only on h: three branches that may run side by side
+                self._parallel([q_branch, k_branch, v_branch])
             if self.fuse:
                 L("RopeScatterQKVF16" if f16 else "RopeScatterQKV",
                   [self.pos_q, self.pos_k, self.slots, self.q, self.k, self.v, self.k_cache[li], self.v_cache[li]],
@@ -451,14 +525,19 @@ class DecodeEngine:
             L("AttentionDecodeBatchedF16" if f16 else "AttentionDecodeBatched",
               [self.q, self.k_cache[li], self.v_cache[li], self.pages, self.lengths, self.attn],
               _u("<IIIIIIfI", B, self.hq, self.hk, D, cfg.block, self.max_pages, scale, 0))
-            self._linear(self.attn, lay.wo, self._proj[0])
+            self._linear(self.attn, lay.wo_p if self.use_packed else lay.wo, self._proj[0])
             add_norm(lay.g2, 0)
-            self._parallel([lambda: self._linear(self.h, lay.wg, self.gate),
-                            lambda: self._linear(self.h, lay.wu, self.up)])
-            L("SwiGLU", [self.gate, self.up, self.act])
-            self._linear(self.act, lay.wd, self._proj[1])
+            if self.use_packed and self.fuse:
+                # gate and up as one product whose epilogue applies SwiGLU
+                w = lay.wgu
+                L("QuantMatMulInt4PackedSwiGLU", [self.h, w.packed, self.act], _u("<IIII", B, w.N, w.K, 0))
+            else:
+                self._parallel([lambda: self._linear(self.h, lay.wg, self.gate),
+                                lambda: self._linear(self.h, lay.wu, self.up)])
+                L("SwiGLU", [self.gate, self.up, self.act])
+            self._linear(self.act, lay.wd_p if self.use_packed else lay.wd, self._proj[1])
         add_norm(self.model.g_final, 1)
-        self._linear(self.h, self.model.lm_head, self.logits_local)
+        self._linear(self.h, self.model.lm_head_p if self.use_packed else self.model.lm_head, self.logits_local)
         if self.shard.tp > 1:
             # each rank owns a column range of the vocabulary: place it in a zeroed full-width
             # buffer and sum across ranks (x + 0 = x exactly), then every rank takes the argmax

@@ -60,3 +60,25 @@ def int4_column_split(n_cols: int, parts: int, rank: int) -> tuple:
     b, e = C.c_uint32(0), C.c_uint32(0)
     _lib.check(_lib.lib().ab_int4_column_split(n_cols, parts, rank, C.byref(b), C.byref(e)))
     return b.value, e.value
+
+
+def int4_prepack(codes: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, K: int, N: int) -> torch.Tensor:
+    """The load-time permutation of a device-resident int4 matrix [K, N] (N a multiple of 128) into
+    the stream layout the decode-batch kernels read (QuantMatVecInt4Packed / QuantMatMulInt4Packed).
+    Returns an int32 tensor holding the packed bytes."""
+    import ctypes as C
+    L = _lib.lib()
+    nbytes = int(L.ab_int4_prepack_bytes(K, N))
+    if nbytes == 0:
+        raise _lib.AccelError(_lib.AB_ERR_INVALID, f"int4_prepack: K={K} N={N}; N must be a multiple of 128")
+    out = torch.empty(nbytes // 4, dtype=torch.int32, device=codes.device)
+    with torch.cuda.device(codes.device):
+        stream = torch.cuda.current_stream(codes.device).cuda_stream
+        _lib.check(L.ab_int4_prepack(C.c_void_p(stream), C.c_void_p(codes.data_ptr()), C.c_void_p(scales.data_ptr()),
+                                     C.c_void_p(zeros.data_ptr()), K, N, C.c_void_p(out.data_ptr())))
+    return out
+
+
+def int4_stream_check() -> None:
+    """Raises AB_ERR_TIMEOUT when a bounded device-side wait of the prepacked kernels has run out."""
+    _lib.check(_lib.lib().ab_int4_stream_error())

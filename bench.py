@@ -199,10 +199,14 @@ def run_linear(args):
     u = rt.gemm_dims(M if M > 1 else 0, N, K)
     name = "QuantMatMulInt4" if M > 1 else "QuantMatVecInt4"
     x = a if M > 1 else a[0]
+    if not args.planes:
+        # the load-time prepack (a permutation of the three planes) and the kernels that read it
+        mats = [(quant.int4_prepack(c, sc, z, K, N),) for c, sc, z in mats]
+        name += "Packed"
 
     def body():
-        for c, sc, z in mats:
-            rt.launch(name, [x, c, sc, z, out], u)
+        for m in mats:
+            rt.launch(name, [x, *m, out], u)
 
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
@@ -678,6 +682,9 @@ def main():
                     help="time the paged decode attention of config 3 on its own, f32 and f16 caches")
     ap.add_argument("--moe", action="store_true",
                     help="time the expert-parallel grouped int4 FFN (config 5) instead of the decode step")
+    ap.add_argument("--planes", action="store_true",
+                    help="with --linear: read quant.Int4Quantize's three planes as they are (the reference's "
+                         "layout) instead of the load-time prepack")
     ap.add_argument("--linear", default=None, metavar="M,K,N",
                     help="time one int4 product on its own instead of the decode step")
     args = ap.parse_args()

@@ -272,6 +272,23 @@ AB_API int ab_blockpool_positions(ab_blockpool *p, int n_pages);
 AB_API int ab_int4_column_split(uint32_t n_cols, int parts, int rank, uint32_t *begin,
                                 uint32_t *end);
 
+/* ---- Load-time prepack of an int4 matrix for the decode-batch kernels ----------------------
+ * No reference counterpart: accel's kernels read quant.Int4Quantize's three planes as they are
+ * (internal/kernels/int4.go:60-101).  The prepack is a pure permutation of those planes (N a
+ * multiple of 128): per 128-column group and per 64 weight rows, the codes of a column contiguous
+ * along k with the group's scale / zero pairs behind them, so that one CTA's K range of a group is
+ * one contiguous run for a bulk copy; a header keeps one float per group (a power of two from the
+ * group's largest scale).  ab_int4_prepack_bytes gives the size of `packed` (device memory,
+ * 256-byte aligned); ab_int4_prepack fills it on `stream` from device-resident planes.  The
+ * kernels QuantMatVecInt4Packed / QuantMatMulInt4Packed (ab_launch; bindings a, packed, out;
+ * GEMMDims) compute what QuantMatVecInt4 / QuantMatMulInt4 compute from the three planes. */
+AB_API size_t ab_int4_prepack_bytes(uint32_t K, uint32_t N);
+AB_API int ab_int4_prepack(void *stream, const uint32_t *codes, const uint16_t *scales,
+                           const uint16_t *zeros, uint32_t K, uint32_t N, void *packed);
+/* AB_OK, or AB_ERR_TIMEOUT once a bounded device-side wait of the prepacked kernels has run out
+ * (synchronous; sticky for the process). */
+AB_API int ab_int4_stream_error(void);
+
 /* ---- One-shot all-reduce over NVLink peer memory (tensor-parallel decode) -----------------
  * No reference counterpart: accel is single-device (the tensor-parallel layer sits above the
  * per-device plan).  Sums `n` f32 values (a multiple of 4) over `world` <= 8 ranks, one process per

@@ -108,8 +108,9 @@ def test_fused_support_kernels_equal_the_chain_of_reference_operators(cache):
     shard = dec.Shard.plan(cfg, 1, 0)
     model = dec.DecodeModel(cfg, shard, DEV, seed=9, std=0.08)
     batch, steps = 3, 6
-    fused = dec.DecodeEngine(model, batch, max_context=64)
-    chain = dec.DecodeEngine(model, batch, max_context=64)
+    # both on the reference-layout planes, so that the products are the same kernels in both
+    fused = dec.DecodeEngine(model, batch, max_context=64, use_packed=False)
+    chain = dec.DecodeEngine(model, batch, max_context=64, use_packed=False)
     assert fused.fuse
     chain.fuse = False
     for e in (fused, chain):
@@ -127,6 +128,36 @@ def test_fused_support_kernels_equal_the_chain_of_reference_operators(cache):
     for li in range(cfg.layers):
         assert torch.equal(fused.k_cache[li], chain.k_cache[li])
         assert torch.equal(fused.v_cache[li], chain.v_cache[li])
+
+
+def test_prepacked_products_give_the_step_of_the_reference_planes():
+    """The same model stepped twice: on quant.Int4Quantize's planes (one product per matrix, SwiGLU as
+    its own kernel) and on the load-time prepack (q | k | v as one product, gate | up as one product
+    with SwiGLU in its epilogue).  Different kernels, same mathematics: logits within the int4
+    tolerance compounded over the layers, greedy ids equal where the top two are clearly apart."""
+    cfg = small_cfg()
+    model = dec.DecodeModel(cfg, dec.Shard.plan(cfg, 1, 0), DEV, seed=21, std=0.08)
+    assert model.packed
+    batch, steps = 5, 8
+    planes = dec.DecodeEngine(model, batch, max_context=64, use_packed=False)
+    packed = dec.DecodeEngine(model, batch, max_context=64)
+    assert packed.use_packed and not planes.use_packed
+    for e in (planes, packed):
+        e.fill_context(9, seed=4)
+        for s in range(batch):
+            e.reserve(s, 9 + steps + 1)
+        e.upload_pages()
+    tok = np.arange(batch) + 3
+    for t in range(steps):
+        a = planes.step(tok)
+        b = packed.step(tok)
+        la, lb = planes.logits.cpu().numpy(), packed.logits.cpu().numpy()
+        assert_close(lb, la, 3e-3, f"logits at step {t}")
+        top2 = np.sort(la, axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 1e-2 * np.abs(la).max()
+        assert np.array_equal(a[clear], b[clear]), t
+        tok = a
+    assert packed.launches_per_step < planes.launches_per_step
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
