@@ -99,6 +99,10 @@ static const KernelEntry kKernels[] = {
     {"AttentionDecodeBatchedF16", 6, 32, launch_attention_decode_batched_f16},
     {"AttentionRagged", 7, 32, launch_attention_ragged},
     {"AttentionRaggedF16", 7, 32, launch_attention_ragged_f16},
+    {"AttentionPrefill", 5, 32, launch_attention_prefill},
+    {"AttentionPrefillF16", 5, 32, launch_attention_prefill_f16},
+    {"AttentionPrefillPaged", 6, 32, launch_attention_prefill_paged},
+    {"AttentionPrefillPagedF16", 6, 32, launch_attention_prefill_paged_f16},
     {"GroupedMatVec", 4, 16, launch_grouped_matvec},
     {"GroupedMatMul", 4, 16, launch_grouped_matmul},
     {"GroupedMatMulInt4", 6, 16, launch_grouped_matmul_int4},
@@ -112,6 +116,21 @@ static const KernelEntry kKernels[] = {
     {"SwiGLU", 3, 0, launch_swiglu},
     {"ElemAdd", 3, 0, launch_elem_add},
     {"SampleArgmax", 2, 16, launch_sample_argmax},
+    {"Softmax", 2, 16, launch_softmax},
+    {"ScaleRows", 3, 16, launch_scale_rows},
+    {"LogitBias", 4, 16, launch_logit_bias},
+    {"TopKMaskRows", 3, 16, launch_topk_mask_rows},
+    {"TopPMaskRows", 3, 16, launch_topp_mask_rows},
+    {"TopKMask", 2, 16, launch_topk_mask},
+    {"TopPMask", 2, 16, launch_topp_mask},
+    {"SampleRows", 4, 16, launch_sample_rows},
+    {"SampleCategorical", 3, 16, launch_sample_categorical},
+    {"PenaltyClearRows", 1, 16, launch_penalty_clear_rows},
+    {"PenaltyCountRows", 3, 16, launch_penalty_count_rows},
+    {"PenaltyApplyRows", 6, 16, launch_penalty_apply_rows},
+    {"PenaltyClear", 1, 32, launch_penalty_clear},
+    {"PenaltyCount", 2, 32, launch_penalty_count},
+    {"PenaltyApply", 3, 32, launch_penalty_apply},
     {"CastF32ToF16", 2, 0, launch_cast_f32_to_f16},
     {"CastF16ToF32", 2, 0, launch_cast_f16_to_f32},
     {"Int4Quantize", 4, 0, launch_int4_quantize},
@@ -238,6 +257,7 @@ static size_t elem_bytes_of(const char *k, int i)
     auto is = [&](const char *n) { return strcmp(k, n) == 0; };
     if (is("QuantMatVecInt4") || is("QuantMatMulInt4")) return (i == 2 || i == 3) ? 2 : 4;
     if (is("GroupedMatMulInt4")) return (i == 2 || i == 3) ? 2 : 4;
+    if (is("AttentionPrefillF16") || is("AttentionPrefillPagedF16")) return (i == 1 || i == 2) ? 2 : 4;
     if (is("AttentionDecodeF16") || is("AttentionDecodePagedF16") || is("AttentionDecodeBatchedF16") ||
         is("AttentionRaggedF16"))
         return (i == 1 || i == 2) ? 2 : 4;

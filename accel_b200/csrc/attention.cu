@@ -32,7 +32,7 @@ static constexpr int kPosUnroll = 4;
 static constexpr float kLog2e = 1.4426950408889634f;
 static constexpr float kNegBig = -3.0e38f;
 
-enum Mode { kContiguous = 0, kPaged = 1, kBatched = 2, kRagged = 3 };
+enum Mode { kContiguous = 0, kPaged = 1, kBatched = 2, kRagged = 3, kPrefill = 4 };
 
 struct AttnParams {
     const float *q;
@@ -46,6 +46,7 @@ struct AttnParams {
     uint32_t capacity;  // positions the page table (or the contiguous cache) can address
     float scale_log2;   // Scale * log2(e)
     int mode;
+    uint32_t base;      // prefill: query row s sees positions <= base + s
 };
 
 // What one query row may see.
@@ -68,6 +69,10 @@ __device__ __forceinline__ RowView row_view(const AttnParams &p, uint32_t row)
     } else if (p.mode == kBatched) {
         rv.len = min(p.lengths[row], p.capacity);
         rv.pages = p.pages + (size_t)row * p.max_pages;
+    } else if (p.mode == kPrefill) {
+        // one sequence, query row `row` of it: the causal limit and the cache length both bound it
+        // (internal/kernels/prefill.go:436-470); base + row + 1 cannot wrap for any cache that exists
+        rv.len = min(min(p.base + row + 1, p.lengths[0]), p.capacity);
     } else {
         rv.len = min(p.lengths[0], p.capacity);
     }
@@ -153,7 +158,7 @@ attn_partition_kernel(const AttnParams p)
             kv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
             vv[u] = kv[u];
             if (ok[u] && lane_on) {
-                size_t phys = p.mode == kContiguous
+                size_t phys = rv.pages == nullptr           // a contiguous cache has no page table
                                   ? (size_t)j
                                   : (size_t)__ldg(rv.pages + j / p.block) * p.block + j % p.block;
                 const size_t off = phys * row_stride + head_off;
@@ -325,7 +330,7 @@ attn_partition_gqa_kernel(const AttnParams p)
 #pragma unroll
             for (int e = 0; e < 8; e++) kv[u][e] = vv[u][e] = 0.f;
             if (ok[u] && lane_on) {
-                const size_t phys = p.mode == kContiguous
+                const size_t phys = rv.pages == nullptr
                                         ? (size_t)j
                                         : (size_t)__ldg(rv.pages + j / p.block) * p.block + j % p.block;
                 const size_t off = phys * row_stride + head_off;
@@ -464,7 +469,7 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
     if (p.head_dim == 0 || p.head_dim % 8 != 0 || p.head_dim > 128)
         return fail(AB_ERR_INVALID, "%s: head dimension %u; it is a multiple of eight and at most "
                     "128", name, p.head_dim);
-    if (p.mode != kContiguous && p.block == 0)
+    if (p.block == 0)
         return fail(AB_ERR_INVALID, "%s: a page table addresses blocks, and Block is 0", name);
     p.parts = (p.capacity + kPartition - 1) / kPartition;
     if (p.parts == 0) p.parts = 1;
@@ -581,6 +586,45 @@ static int batched(Launch &l, bool f16, bool ragged, const char *name)
     }
     return f16 ? run_attention<__half>(l, p, name) : run_attention<float>(l, p, name);
 }
+
+// AttentionPrefill(F16) and AttentionPrefillPaged(F16) (internal/kernels/prefill.go:197,409;
+// pagedprefillf16.go:31): QSeq query rows of one sequence against its cache, row s seeing the
+// positions <= Base + s.  Every row is a decode over its own visible prefix: the split-K decode
+// kernels run with one row per query position.
+static int prefill(Launch &l, bool f16, bool is_paged, const char *name)
+{   // q, k, v, [pages,] lengths, out; PrefillDims{QHeads,KVHeads,HeadDim,QSeq,Base,Scale} or
+    // PagedPrefillDims{QHeads,KVHeads,HeadDim,QSeq,Base,Block,Scale}
+    AttnParams p{};
+    p.mode = kPrefill;
+    p.q_heads = u32_at(l.u, 0); p.kv_heads = u32_at(l.u, 4); p.head_dim = u32_at(l.u, 8);
+    p.rows = u32_at(l.u, 12); p.base = u32_at(l.u, 16);
+    p.block = is_paged ? u32_at(l.u, 20) : 1;
+    p.scale_log2 = f32_at(l.u, is_paged ? 24 : 20) * kLog2e;
+    p.batch = 1;
+    const int len_i = is_paged ? 4 : 3, out_i = is_paged ? 5 : 4;
+    const uint64_t per = (uint64_t)p.q_heads * p.head_dim, kvper = (uint64_t)p.kv_heads * p.head_dim;
+    if (is_paged) {
+        p.max_pages = l.len[3];
+        p.capacity = l.len[3] * p.block;                    // len(pages) * Block
+    } else {
+        p.capacity = kvper ? (uint32_t)(l.len[1] / kvper) : 0;
+    }
+    if (l.len[0] < (uint64_t)p.rows * per || l.len[out_i] < (uint64_t)p.rows * per || l.len[len_i] < 1)
+        return fail(AB_ERR_INVALID, "%s: QSeq=%u QHeads=%u HeadDim=%u and the lengths block says q[%u] lengths[%u] "
+                    "out[%u]", name, p.rows, p.q_heads, p.head_dim, l.len[0], l.len[len_i], l.len[out_i]);
+    if (!l.query_ws) {
+        p.q = ptr<const float>(l, 0); p.k = l.b[1]; p.v = l.b[2];
+        p.pages = is_paged ? ptr<const uint32_t>(l, 3) : nullptr;
+        p.lengths = ptr<const uint32_t>(l, len_i);
+        p.out = ptr<float>(l, out_i);
+    }
+    return f16 ? run_attention<__half>(l, p, name) : run_attention<float>(l, p, name);
+}
+
+int launch_attention_prefill(Launch &l) { return prefill(l, false, false, "AttentionPrefill"); }
+int launch_attention_prefill_f16(Launch &l) { return prefill(l, true, false, "AttentionPrefillF16"); }
+int launch_attention_prefill_paged(Launch &l) { return prefill(l, false, true, "AttentionPrefillPaged"); }
+int launch_attention_prefill_paged_f16(Launch &l) { return prefill(l, true, true, "AttentionPrefillPagedF16"); }
 
 int launch_attention_decode(Launch &l) { return contiguous(l, false, "AttentionDecode"); }
 int launch_attention_decode_f16(Launch &l) { return contiguous(l, true, "AttentionDecodeF16"); }

@@ -102,6 +102,10 @@ int launch_attention_decode_batched(Launch &);
 int launch_attention_decode_batched_f16(Launch &);
 int launch_attention_ragged(Launch &);
 int launch_attention_ragged_f16(Launch &);
+int launch_attention_prefill(Launch &);
+int launch_attention_prefill_f16(Launch &);
+int launch_attention_prefill_paged(Launch &);
+int launch_attention_prefill_paged_f16(Launch &);
 int launch_grouped_matvec(Launch &);
 int launch_grouped_matmul(Launch &);
 int launch_grouped_matmul_int4(Launch &);
@@ -117,6 +121,21 @@ int launch_elem_add(Launch &);
 int launch_sample_argmax(Launch &);
 int launch_cast_f32_to_f16(Launch &);
 int launch_cast_f16_to_f32(Launch &);
+int launch_softmax(Launch &);
+int launch_scale_rows(Launch &);
+int launch_logit_bias(Launch &);
+int launch_topk_mask_rows(Launch &);
+int launch_topp_mask_rows(Launch &);
+int launch_topk_mask(Launch &);
+int launch_topp_mask(Launch &);
+int launch_sample_rows(Launch &);
+int launch_sample_categorical(Launch &);
+int launch_penalty_clear_rows(Launch &);
+int launch_penalty_count_rows(Launch &);
+int launch_penalty_apply_rows(Launch &);
+int launch_penalty_clear(Launch &);
+int launch_penalty_count(Launch &);
+int launch_penalty_apply(Launch &);
 int launch_int4_quantize(Launch &);
 int launch_decode_step_inputs(Launch &);
 int launch_add_rmsnorm(Launch &);

@@ -63,7 +63,7 @@ static constexpr uint32_t kSxCodeBytes = 4096;
 static constexpr uint32_t kSxChunkBytes = 4352;   // codes + 64 scales + 64 zeros
 static constexpr int kSxNC = 6;                   // ring stages in flight from global memory
 static constexpr int kSxNA = 3;                   // A (TMEM) and B (shared) stages
-static constexpr uint32_t kSxTmemCols = 256;      // per group: D, D_z and three stages of codes
+__host__ __device__ constexpr uint32_t sx_tmem_cols(int G) { return G == 1 ? 128u : 256u; }   // per group: D (32) + 3 x 32
 static constexpr long long kSxWaitCycles = 1ll << 31;      // about a second
 
 __device__ int g_stream_error;                    // nonzero: a bounded wait ran out
@@ -183,7 +183,7 @@ static constexpr uint32_t kSxLbo = kSxNB * 16u + 16u;              // B: k-block
 static constexpr uint32_t kSxBStage = 8u * kSxLbo;                 // B: 64 k x 16 rows of one group
 __host__ __device__ constexpr size_t sx_smem_bytes(int G)
 {
-    return (size_t)kSxNC * G * kSxChunkBytes + (size_t)kSxNA * G * kSxBStage + (size_t)G * kSxRecvRows * 128 * 4 +
+    return (size_t)kSxNC * G * kSxChunkBytes + (size_t)kSxNA * G * kSxBStage + (size_t)G * (kSxRecvRows + kSxNB) * 128 * 4 +
            (size_t)(G + 1) * kSxNB * 4 + (2 * kSxNC + 2 * kSxNA + 2) * 8 + 16 + 128 + 256;
 }
 
@@ -228,12 +228,14 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
     constexpr int NB = kSxNB;
     constexpr uint32_t kStage = G * kSxChunkBytes;                   // one ring stage: G groups' chunk
     constexpr uint32_t kA0 = G * 32;                                  // TMEM: D per group (32 columns apart), then A stages
+    constexpr uint32_t kSxTmemCols = sx_tmem_cols(G);
     static_assert(kA0 + G * kSxNA * 32 <= kSxTmemCols, "TMEM budget");
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(sx_raw) + 127) & ~(uintptr_t)127);
     unsigned char *ring = smem;
     unsigned char *bring = ring + kSxNC * kStage;
     float *recv = reinterpret_cast<float *>(bring + kSxNA * G * kSxBStage);   // [rows][G][128] partial rows of the K splits
-    float *unscale = recv + kSxRecvRows * G * 128;                             // [NB] 2^(E_a - 12)
+    float *tile = recv + kSxRecvRows * G * 128;                                // [NB][G][128] this CTA's partial rows
+    float *unscale = tile + NB * G * 128;                                      // [NB] 2^(E_a - 12)
     float *zsum = unscale + NB;                                                // [G][NB] zero-point term
     uint64_t *w_full = reinterpret_cast<uint64_t *>(zsum + G * NB);
     uint64_t *w_empty = w_full + kSxNC;
@@ -255,24 +257,39 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
     const unsigned char *stream = packed + header_bytes + ((size_t)g0 * nchunks_total + c_beg) * kSxChunkBytes;
     const size_t group_stride = (size_t)nchunks_total * kSxChunkBytes;
 
-    if (tid == 0) {
-        for (int i = 0; i < kSxNC; i++) { sx_bar_init(&w_full[i], 1); sx_bar_init(&w_empty[i], kSxExpanders / 32); }
-        for (int i = 0; i < kSxNA; i++) { sx_bar_init(&ab_ready[i], kSxExpanders / 32); sx_bar_init(&ab_free[i], 1); }
-        sx_bar_init(done, 1);
-        sx_bar_init(red_bar, 1);                     // completes when every K split's rows have arrived
-        *s_abort = 0;
-        if (splits > 1) {
-            // this CTA owns rows split, split + splits, ... of the tile: their partial sums arrive
-            // from every CTA of the cluster as asynchronous stores that count bytes on red_bar
-            const uint32_t owned = M > split ? (M - split + splits - 1) / splits : 0u;
-            sx_bar_expect_tx(red_bar, owned * splits * gcount * 128u * 4u);
+    if (warp == 9) {
+        // the copy warp initialises the barriers and starts the first stages at once, one lane per
+        // stage (issuing a copy takes a few hundred cycles): the weights depend on nothing that
+        // runs before this kernel
+        if (lane == 0) {
+            for (int i = 0; i < kSxNC; i++) { sx_bar_init(&w_full[i], 1); sx_bar_init(&w_empty[i], kSxExpanders / 32); }
+            for (int i = 0; i < kSxNA; i++) { sx_bar_init(&ab_ready[i], kSxExpanders / 32); sx_bar_init(&ab_free[i], 1); }
+            sx_bar_init(done, 1);
+            sx_bar_init(red_bar, 1);                 // completes when every K split's rows have arrived
+            *s_abort = 0;
+            if (splits > 1) {
+                // this CTA owns rows split, split + splits, ... of the tile: their partial sums arrive
+                // from every CTA of the cluster as bulk copies that count bytes on red_bar
+                const uint32_t owned = M > split ? (M - split + splits - 1) / splits : 0u;
+                sx_bar_expect_tx(red_bar, owned * splits * (uint32_t)G * 128u * 4u);
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            SX_STAMP(40);
         }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        __syncwarp();
+        if ((uint32_t)lane < (uint32_t)kSxNC && (uint32_t)lane < nch) {
+            sx_bar_expect_tx(&w_full[lane], gcount * kSxChunkBytes);
+            for (uint32_t gi = 0; gi < gcount; gi++)
+                sx_bulk_load(ring + lane * kStage + gi * kSxChunkBytes,
+                             stream + gi * group_stride + (size_t)lane * kSxChunkBytes, kSxChunkBytes, &w_full[lane]);
+        }
+        if (lane == 0) SX_STAMP(41);
     }
     if (warp == 8) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(sx_smem(tmem_slot)), "r"(kSxTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (lane == 0) SX_STAMP(42);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -280,21 +297,16 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
     const uint32_t tmem = *tmem_slot;
     // every CTA of the cluster has initialised its barriers before anyone's partial rows arrive
     // (waited for at the end of the loop, long after)
-    if (splits > 1) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    if (tid == 0) SX_STAMP(43);
+    // (relaxed: the barrier initialisations were published by fence.mbarrier_init above)
+    if (splits > 1) asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
     if (tid == 0) SX_STAMP(1);
     // a dependent launch may begin now: it only prefetches its own weights until this grid is done
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 9) {
-        // ---- the copy warp: the groups' runs of chunks, kSxNC stages ahead of the expanders.  The
-        //      first stages are issued by one lane each (issuing a copy takes a few hundred cycles),
-        //      the rest by lane 0 as stages are handed back
-        if ((uint32_t)lane < (uint32_t)kSxNC && (uint32_t)lane < nch) {
-            sx_bar_expect_tx(&w_full[lane], gcount * kSxChunkBytes);
-            for (uint32_t gi = 0; gi < gcount; gi++)
-                sx_bulk_load(ring + lane * kStage + gi * kSxChunkBytes,
-                             stream + gi * group_stride + (size_t)lane * kSxChunkBytes, kSxChunkBytes, &w_full[lane]);
-        }
+        // ---- the copy lane: the groups' runs of chunks, kSxNC stages ahead of the expanders (the
+        //      first stages were issued before the CTA-wide barrier)
         if (lane == 0) {
             SX_DECL();
             for (uint32_t c = kSxNC; c < nch; c++) {     // the first kSxNC stages are already on their way
@@ -529,6 +541,12 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (splits > 1) asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
             if (tid == 0) SX_STAMP(9);
+            {   // the four warps decide together (they meet at a barrier below)
+                uint32_t all;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 2, 128, q;\n\t"
+                             "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(all) : "r"((uint32_t)ok) : "memory");
+                ok = all != 0;
+            }
             if (ok) {
                 const uint32_t rank = split;         // cluster = the K splits of this tile, in order
                 // one finished row of the tile: both groups' sums of column tcol
@@ -568,26 +586,23 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
                         }
                     }
                 } else {
-                    // row i belongs to CTA i % splits of the cluster: slot (i / splits) * splits + rank.
-                    // Asynchronous stores into the owner's shared memory count bytes on its barrier.
-                    uint32_t owner = 0, slot = rank;
+                    // this CTA's partial rows go through a local tile, from where row i leaves as one
+                    // bulk copy into the shared memory of CTA i % splits of the cluster, slot
+                    // (i / splits) * splits + rank, counting bytes on that CTA's barrier
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        if ((uint32_t)i < M) {
-                            uint32_t rbar;
-                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(sx_smem(red_bar)), "r"(owner));
+                    for (int i = 0; i < 16; i++)
 #pragma unroll
-                            for (int gi = 0; gi < G; gi++) {
-                                if ((uint32_t)gi < gcount) {
-                                    uint32_t raddr;
-                                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
-                                                 : "=r"(raddr) : "r"(sx_smem(&recv[(slot * G + gi) * 128 + tcol])), "r"(owner));
-                                    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
-                                                 ::"r"(raddr), "r"(__float_as_uint(vals[gi][i])), "r"(rbar) : "memory");
-                                }
-                            }
-                            if (++owner == splits) { owner = 0; slot += splits; }
-                        }
+                        for (int gi = 0; gi < G; gi++) tile[(i * G + gi) * 128 + tcol] = vals[gi][i];
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    if ((uint32_t)tid < M) {
+                        const uint32_t i = (uint32_t)tid, owner = i % splits, slot = (i / splits) * splits + rank;
+                        uint32_t raddr, rbar;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                                     : "=r"(raddr) : "r"(sx_smem(&recv[slot * G * 128])), "r"(owner));
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(sx_smem(red_bar)), "r"(owner));
+                        asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(raddr), "r"(sx_smem(&tile[i * G * 128])), "r"((uint32_t)(G * 128 * 4)), "r"(rbar) : "memory");
                     }
                     if (tid == 0) SX_STAMP(7);
                     // the rows this CTA owns, from every K split in split order
@@ -626,6 +641,13 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
     }
     if (warp >= 8 && splits > 1) {
         __syncwarp();                                // the working lane rejoins its warp
+        asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    }
+    if (splits > 1) {
+        // the bulk copies that carry this CTA's partial rows read its shared memory until they are
+        // done, which is when every CTA of the cluster has received its rows: nobody leaves before
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     }
     if (tid == 0) SX_STAMP(6);
@@ -793,13 +815,21 @@ template <int G> static int sx_prepare()
         int rc = check_cuda(cudaFuncSetAttribute(int4_stream_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)sx_smem_bytes(G)), "int4_stream_kernel shared memory");
         if (rc) return rc;
+        // the kernel touches global memory through bulk copies and a few broadcast loads: all of the
+        // SM's memory as shared memory, so that several CTAs fit
+        rc = check_cuda(cudaFuncSetAttribute(int4_stream_kernel<G>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                             (int)cudaSharedmemCarveoutMaxShared), "int4_stream_kernel carve-out");
+        if (rc) return rc;
         attr_set[dev] = true;
     }
     return AB_OK;
 }
 
-// How many clusters of `splits` CTAs the device holds at once (clusters do not straddle GPCs, so
-// this is less than the CTA slots divided by the cluster size); asked of the runtime once.
+// How many clusters of `splits` CTAs the device holds at once.  Clusters do not straddle GPCs, so
+// this is less than the CTA slots divided by the cluster size; the runtime's answer is for ONE CTA
+// per SM (its occupancy calculation gives a kernel that allocates tensor memory one CTA per SM,
+// although several run side by side when their columns fit), so it is scaled by the CTAs per SM
+// this kernel's registers, shared memory and tensor-memory columns allow: a lower bound.
 template <int G> static uint32_t sx_resident_clusters(uint32_t splits)
 {
     static int cached[64][kSxMaxSplits + 1] = {};
@@ -811,11 +841,20 @@ template <int G> static uint32_t sx_resident_clusters(uint32_t splits)
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr[1];
         sx_config<G>(cfg, attr, splits, splits);
-        if (sx_prepare<G>() != AB_OK || cudaOccupancyMaxActiveClusters(&n, int4_stream_kernel<G>, &cfg) != cudaSuccess || n <= 0) {
+        cudaFuncAttributes fa{};
+        if (sx_prepare<G>() != AB_OK || cudaOccupancyMaxActiveClusters(&n, int4_stream_kernel<G>, &cfg) != cudaSuccess ||
+            n <= 0 || cudaFuncGetAttributes(&fa, int4_stream_kernel<G>) != cudaSuccess) {
             cudaGetLastError();
-            n = (int)(2u * (uint32_t)sm_count() / splits * 3 / 4);      // a cautious guess
+            n = (int)((uint32_t)sm_count() / splits * 3 / 4);           // a cautious guess
+            fa.numRegs = 96;
         }
-        cached[dev][splits] = n;
+        const uint32_t by_regs = 65536u / ((uint32_t)((fa.numRegs + 7) / 8 * 8) * kSxThreads);
+        const uint32_t by_smem = (uint32_t)(233472 / (sx_smem_bytes(G) + 1024));
+        const uint32_t by_tmem = 512u / sx_tmem_cols(G);
+        uint32_t per_sm = by_regs < by_smem ? by_regs : by_smem;
+        if (by_tmem < per_sm) per_sm = by_tmem;
+        if (per_sm < 1) per_sm = 1;
+        cached[dev][splits] = n * (int)per_sm;
     }
     return (uint32_t)cached[dev][splits];
 }
@@ -944,9 +983,12 @@ int int4_stream_error_flag()
 }
 
 // ---- dispatch by name: bindings a, packed, out; GEMMDims{M,N,K} ------------------------------------
+// Programmatic dependent launch: the product starts while its predecessor in the stream is still
+// running, prefetches its weights (which depend on nothing) and waits for the predecessor only
+// before it reads the activations.  AB_INT4_PDL=0 launches it the ordinary way (for measurements).
 static bool sx_pdl()
 {
-    static const bool pdl = getenv("AB_INT4_PDL") && atoi(getenv("AB_INT4_PDL")) != 0;
+    static const bool pdl = !(getenv("AB_INT4_PDL") && atoi(getenv("AB_INT4_PDL")) == 0);
     return pdl;
 }
 

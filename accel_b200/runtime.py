@@ -33,6 +33,15 @@ def batched_dims(batch, q_heads, kv_heads, head_dim, block, max_pages, scale) ->
     return struct.pack("<IIIIIIfI", batch, q_heads, kv_heads, head_dim, block, max_pages, scale, 0)
 
 
+def prefill_dims(q_heads, kv_heads, head_dim, q_seq, base, scale) -> bytes:         # PrefillDims, prefill.go:18
+    return struct.pack("<IIIIIfII", q_heads, kv_heads, head_dim, q_seq, base, scale, 0, 0)
+
+
+def paged_prefill_dims(q_heads, kv_heads, head_dim, q_seq, base, block, scale) -> bytes:
+    # PagedPrefillDims, prefill.go:368
+    return struct.pack("<IIIIIIfI", q_heads, kv_heads, head_dim, q_seq, base, block, scale, 0)
+
+
 def grouped_dims(experts, K, N) -> bytes:                       # GroupedDims, grouped.go:10
     return struct.pack("<IIII", experts, K, N, 0)
 
@@ -59,6 +68,18 @@ def rope_params(rows, width, rotary_dim, base) -> bytes:        # RoPEParams, el
 
 def sample_dims(vocab, rows) -> bytes:                          # SampleDims, sample.go
     return struct.pack("<IIII", vocab, rows, 0, 0)
+
+
+def row_sample_dims(vocab, rows, history=0, slots=0) -> bytes:  # RowSampleDims, rowsample.go:25
+    return struct.pack("<IIII", vocab, rows, history, slots)
+
+
+def top_dims(vocab, k=0, p=0.0) -> bytes:                        # TopDims, topk.go:10
+    return struct.pack("<IIfI", vocab, k, p, 0)
+
+
+def penalty_dims(vocab, history, count, repetition, presence, frequency) -> bytes:   # PenaltyDims, penalty.go:15
+    return struct.pack("<IIIfffII", vocab, history, count, repetition, presence, frequency, 0, 0)
 
 
 # ---------------------------------------------------------------- launch

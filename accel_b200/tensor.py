@@ -128,12 +128,14 @@ class AttentionOptions:
     block: int = 0
     scale: float = 1.0
     query_extents: Optional[torch.Tensor] = None
+    base: Optional[int] = None     # stands for BaseName: the cache position of a prefill's first query token
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, opts: AttentionOptions) -> torch.Tensor:
-    """tensor.Attention (tensor/attention.go:124), decode forms.  q's rank selects the kernel:
-    [qHeads, D] one token; [batch, 1, qHeads, D] with Pages the batched decode (f32 cache; an f16
-    cache runs the batched-f16 extension); [tokens, qHeads, D] with QueryExtents the ragged step.
+    """tensor.Attention (tensor/attention.go:124).  q's rank selects the kernel: [qHeads, D] one
+    token; [batch, 1, qHeads, D] with Pages the batched decode (f32 cache; an f16 cache runs the
+    batched-f16 extension); [tokens, qHeads, D] with QueryExtents the ragged step; [qSeq, qHeads, D]
+    without it a causal prefill of one sequence (Base required; paged when Pages is set).
     k and v are the caches, [capacity, kvHeads, D], f32 or f16."""
     op = "Attention"
     if q.dtype != torch.float32:
@@ -153,7 +155,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, opts: Attention
                       "for several sequences stepping together")
     batch, q_seq = 1, 1
     batched = rank == 4
-    ragged = False
+    ragged = prefill = False
     if rank == 4:
         batch, q_seq = q.shape[0], q.shape[1]
     if opts.query_extents is not None:
@@ -169,8 +171,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, opts: Attention
             raise Refused(op, "QueryExtents is empty; it is one count per sequence and a step has "
                           "at least one sequence")
     elif rank == 3:
-        raise Refused(op, "a prefill is outside this backend's path; the decode, batched and "
-                      "ragged forms are built")
+        prefill, q_seq = True, q.shape[0]
     if k.dim() != 3 or tuple(k.shape) != tuple(v.shape):
         raise Refused(op, f"the key cache is {tuple(k.shape)} and the value cache is "
                       f"{tuple(v.shape)}; both are [capacity, kvHeads, headDim] and equal")
@@ -198,6 +199,24 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, opts: Attention
     k, v = k.contiguous(), v.contiguous()
     scale = float(opts.scale)
 
+    if prefill:
+        if opts.base is None:
+            raise Refused(op, "a prefill needs BaseName: the position of its first query token within "
+                          "the cache, which is what the causal mask is measured from")
+        out = torch.empty((q_seq, q_heads, head_dim), dtype=torch.float32, device=q.device)
+        if q_seq == 0:
+            return out
+        if opts.pages is not None:
+            if opts.pages.dim() != 1:
+                raise Refused(op, f"Pages is {tuple(opts.pages.shape)}; a prefill is one sequence, whose "
+                              "page table is one row of block ids")
+            rt.launch("AttentionPrefillPagedF16" if f16 else "AttentionPrefillPaged",
+                      [q, k, v, opts.pages.contiguous(), opts.lengths, out],
+                      rt.paged_prefill_dims(q_heads, kv_heads, head_dim, q_seq, int(opts.base), opts.block, scale))
+        else:
+            rt.launch("AttentionPrefillF16" if f16 else "AttentionPrefill", [q, k, v, opts.lengths, out],
+                      rt.prefill_dims(q_heads, kv_heads, head_dim, q_seq, int(opts.base), scale))
+        return out
     if ragged:
         if opts.pages is None:
             raise Refused(op, f"a ragged step of {batch} sequences needs Pages: they have "
@@ -451,4 +470,108 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
         raise Refused("Cast", f"{x.dtype} to {dtype}; f32 and f16 are built")
     if x.numel():
         rt.launch(name, [x.contiguous(), out])
+    return out
+
+
+# ------------------------------------------------------------------------------- sampling policy
+@dataclass
+class RowPenalties:
+    """tensor.RowPenalties (tensor/rowsample.go): per-row history rings [rows, capacity] of token ids
+    (u32), how much of each is filled, the counts scratch [rows, vocab] (u32, rebuilt every step)
+    and the three strengths per row."""
+    history: torch.Tensor
+    counts: torch.Tensor
+    filled: torch.Tensor
+    repetition: torch.Tensor
+    presence: torch.Tensor
+    frequency: torch.Tensor
+
+
+@dataclass
+class RowSampling:
+    """tensor.RowSampling: every parameter is one value per row.  factor is the inverse temperature,
+    0 for a greedy row; top_k / top_p None leaves the node out; bias is (ids u32 [rows, slots],
+    values f32 [rows, slots])."""
+    factor: Optional[torch.Tensor] = None
+    top_k: Optional[torch.Tensor] = None
+    top_p: Optional[torch.Tensor] = None
+    bias: Optional[tuple] = None
+    penalties: Optional[RowPenalties] = None
+
+
+def softmax(x: torch.Tensor) -> torch.Tensor:
+    """tensor.Softmax over the last axis (internal/kernels/norm.go:94)."""
+    if x.dtype != torch.float32 or x.dim() < 1 or x.shape[-1] == 0:
+        raise Refused("Softmax", f"x is {x.dtype} {tuple(x.shape)}; the kernel reads f32 rows")
+    rows, width = x.numel() // x.shape[-1], x.shape[-1]
+    out = torch.empty_like(x)
+    if rows:
+        rt.launch("Softmax", [x.contiguous(), out], rt.row_dims(rows, width, 0.0))
+    return out
+
+
+def sample_rows(logits: torch.Tensor, draws: torch.Tensor, o: RowSampling) -> torch.Tensor:
+    """tensor.SampleRows (tensor/rowsample.go): logits [rows, vocab] f32 -> one token id per row.
+    bias -> penalties -> x factor -> softmax -> top-k -> top-p -> draw (or the argmax of a row whose
+    factor is 0), each a kernel of its own as the reference records them."""
+    op = "SampleRows"
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.shape[1] == 0:
+        raise Refused(op, f"logits are {logits.dtype} {tuple(logits.shape)}; they are f32 [rows, vocab]")
+    rows, vocab = logits.shape
+    if o.factor is None:
+        raise Refused(op, "Factor is nil; every row needs its inverse temperature, and zero is how a "
+                      "row asks for the argmax")
+    if draws is None:
+        raise Refused(op, "draws is nil; every stochastic row draws against its own uniform, and the "
+                      "greedy rows ignore theirs")
+    for name, t, u32 in (("Factor", o.factor, False), ("TopK", o.top_k, True), ("TopP", o.top_p, False),
+                         ("draws", draws, False)):
+        if t is None:
+            continue
+        if (u32 and not _is_u32(t)) or (not u32 and t.dtype != torch.float32):
+            raise Refused(op, f"{name} is {t.dtype} and the kernels read {'u32' if u32 else 'f32'}")
+        if t.numel() != rows:
+            raise Refused(op, f"{name} holds {t.numel()} entries and the logits hold {rows} rows; there "
+                          "is exactly one per row")
+    dims = rt.row_sample_dims(vocab, rows)
+    x = logits.contiguous()
+    dev = x.device
+    new = lambda: torch.empty((rows, vocab), dtype=torch.float32, device=dev)
+    if rows == 0:
+        return torch.empty(0, dtype=torch.int32, device=dev)
+    if o.bias is not None:
+        ids, values = o.bias
+        if not _is_u32(ids) or values.dtype != torch.float32 or ids.numel() != values.numel() or ids.numel() % rows:
+            raise Refused(op, "Bias.IDs (u32) and Bias.Values (f32) are both [rows, slots]")
+        y = new()
+        rt.launch("LogitBias", [x, ids.contiguous(), values.contiguous(), y],
+                  rt.row_sample_dims(vocab, rows, 0, ids.numel() // rows))
+        x = y
+    if o.penalties is not None:
+        p = o.penalties
+        if not _is_u32(p.history) or not _is_u32(p.counts) or not _is_u32(p.filled):
+            raise Refused(op, "the history, the counts and the filled lengths are u32")
+        if p.counts.numel() != rows * vocab or p.history.numel() % rows or p.history.numel() == 0:
+            raise Refused(op, f"the counts hold {p.counts.numel()} entries for {rows} rows of {vocab}, the "
+                          f"history {p.history.numel()}; they are [rows, vocab] and [rows, capacity]")
+        cap = p.history.numel() // rows
+        pd = rt.row_sample_dims(vocab, rows, cap)
+        rt.launch("PenaltyClearRows", [p.counts], pd)
+        rt.launch("PenaltyCountRows", [p.history.contiguous(), p.filled, p.counts], pd)
+        y = new()
+        rt.launch("PenaltyApplyRows", [x, p.counts, p.repetition, p.presence, p.frequency, y], pd)
+        x = y
+    y = new()
+    rt.launch("ScaleRows", [x, o.factor, y], dims)
+    x = softmax(y)
+    if o.top_k is not None:
+        y = new()
+        rt.launch("TopKMaskRows", [x, o.top_k, y], dims)
+        x = y
+    if o.top_p is not None:
+        y = new()
+        rt.launch("TopPMaskRows", [x, o.top_p, y], dims)
+        x = y
+    out = torch.empty(rows, dtype=torch.int32, device=dev)
+    rt.launch("SampleRows", [x, draws, o.factor, out], dims)
     return out

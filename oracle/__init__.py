@@ -216,6 +216,29 @@ def attention_ragged(q, k, v, pages, lengths, offsets, tokens, batch, q_heads, k
     return out
 
 
+def attention_prefill(q, k, v, lengths, q_heads, kv_heads, head_dim, q_seq, base, scale):
+    """AttentionPrefill(F16), internal/kernels/prefill.go:197: contiguous cache, one sequence."""
+    q, lengths = _c(q, np.float32), _c(lengths, np.uint32)
+    k, v, f16 = _cache(k, v)
+    out = np.zeros(q_seq * q_heads * head_dim, np.float32)
+    lib().orc_attention_prefill(C.c_uint32(q_heads), C.c_uint32(kv_heads), C.c_uint32(head_dim),
+                                C.c_uint32(q_seq), C.c_uint32(base), C.c_float(scale), _vp(q), _vp(k), _vp(v),
+                                C.c_int(f16), C.c_uint64(k.size), _vp(lengths), _vp(out))
+    return out
+
+
+def attention_prefill_paged(q, k, v, pages, lengths, q_heads, kv_heads, head_dim, q_seq, base, block, scale):
+    """AttentionPrefillPaged(F16), internal/kernels/prefill.go:409, pagedprefillf16.go:31."""
+    q, lengths, pages = _c(q, np.float32), _c(lengths, np.uint32), _c(pages, np.uint32)
+    k, v, f16 = _cache(k, v)
+    out = np.zeros(q_seq * q_heads * head_dim, np.float32)
+    lib().orc_attention_prefill_paged(C.c_uint32(q_heads), C.c_uint32(kv_heads), C.c_uint32(head_dim),
+                                      C.c_uint32(q_seq), C.c_uint32(base), C.c_uint32(block), C.c_float(scale),
+                                      _vp(q), _vp(k), _vp(v), C.c_int(f16), _vp(pages), C.c_uint32(pages.size),
+                                      _vp(lengths), _vp(out))
+    return out
+
+
 def attention_definition_f64(q, k, v, rows, q_heads, kv_heads, head_dim, scale):
     q, rows = _c(q, np.float32), _c(rows, np.uint32)
     k, v, f16 = _cache(k, v)
@@ -312,6 +335,79 @@ def sample_argmax(logits) -> np.ndarray:
     out = np.zeros(rows, np.uint32)
     lib().orc_sample_argmax(C.c_uint32(rows), C.c_uint32(vocab), _vp(logits), _vp(out))
     return out
+
+
+# ---------------------------------------------------------------- sampling policy
+def softmax(x) -> np.ndarray:
+    x = _c(x, np.float32)
+    rows, width = x.shape
+    out = np.empty_like(x)
+    lib().orc_softmax(C.c_uint32(rows), C.c_uint32(width), _vp(x), _vp(out))
+    return out
+
+
+def scale_rows(x, factors) -> np.ndarray:
+    x, factors = _c(x, np.float32), _c(factors, np.float32)
+    out = np.empty_like(x)
+    lib().orc_scale_rows(C.c_uint32(x.shape[0]), C.c_uint32(x.shape[1]), _vp(x), _vp(factors), _vp(out))
+    return out
+
+
+def topk_mask(weights, k) -> np.ndarray:
+    """TopKMaskRows when k is an array (one per row), TopKMask when it is a number."""
+    w = _c(np.atleast_2d(weights), np.float32)
+    out = np.empty_like(w)
+    if np.ndim(k) == 0:
+        lib().orc_topk_mask(C.c_uint32(w.shape[0]), C.c_uint32(w.shape[1]), _vp(w), None, C.c_uint32(int(k)), _vp(out))
+    else:
+        ks = _c(k, np.uint32)
+        lib().orc_topk_mask(C.c_uint32(w.shape[0]), C.c_uint32(w.shape[1]), _vp(w), _vp(ks), C.c_uint32(0), _vp(out))
+    return out.reshape(np.shape(weights))
+
+
+def topp_mask(weights, p) -> np.ndarray:
+    """TopPMaskRows when p is an array (one per row), TopPMask when it is a number."""
+    w = _c(np.atleast_2d(weights), np.float32)
+    out = np.empty_like(w)
+    if np.ndim(p) == 0:
+        lib().orc_topp_mask(C.c_uint32(w.shape[0]), C.c_uint32(w.shape[1]), _vp(w), None, C.c_float(float(p)), _vp(out))
+    else:
+        ps = _c(p, np.float32)
+        lib().orc_topp_mask(C.c_uint32(w.shape[0]), C.c_uint32(w.shape[1]), _vp(w), _vp(ps), C.c_float(0), _vp(out))
+    return out.reshape(np.shape(weights))
+
+
+def sample_rows(probs, draws, factors=None) -> np.ndarray:
+    """SampleRows (factors given: a zero factor takes the row's argmax) or SampleCategorical."""
+    p = _c(np.atleast_2d(probs), np.float32)
+    d = _c(np.atleast_1d(draws), np.float32)
+    out = np.zeros(p.shape[0], np.uint32)
+    f = _c(factors, np.float32) if factors is not None else None
+    lib().orc_sample_rows(C.c_uint32(p.shape[0]), C.c_uint32(p.shape[1]), _vp(p), _vp(d),
+                          _vp(f) if f is not None else None, _vp(out))
+    return out
+
+
+def logit_bias(logits, ids, values) -> np.ndarray:
+    x, ids, values = _c(logits, np.float32), _c(ids, np.uint32), _c(values, np.float32)
+    out = np.empty_like(x)
+    lib().orc_logit_bias(C.c_uint32(x.shape[0]), C.c_uint32(x.shape[1]), C.c_uint32(ids.shape[1]), _vp(x),
+                         _vp(ids), _vp(values), _vp(out))
+    return out
+
+
+def penalty_rows(logits, history, filled, repetition, presence, frequency):
+    """PenaltyClearRows -> PenaltyCountRows -> PenaltyApplyRows.  Returns (penalised logits, counts)."""
+    x = _c(np.atleast_2d(logits), np.float32)
+    h = _c(np.atleast_2d(history), np.uint32)
+    rows, vocab = x.shape
+    f = _c(np.atleast_1d(filled), np.uint32)
+    rep, pres, freq = (_c(np.atleast_1d(a), np.float32) for a in (repetition, presence, frequency))
+    counts = np.zeros((rows, vocab), np.uint32)
+    out = np.empty_like(x)
+    lib().orc_penalty_rows(C.c_uint32(rows), C.c_uint32(vocab), C.c_uint32(h.shape[1]), _vp(x), _vp(h), _vp(f),
+                           _vp(rep), _vp(pres), _vp(freq), _vp(counts), _vp(out))
+    return out, counts
 
 
 # ---------------------------------------------------------------- block pool

@@ -488,6 +488,65 @@ ORC_API void orc_attention_decode_batched(uint32_t batch, uint32_t q_heads, uint
     }
 }
 
+/* One query row of a causal attention over a paged (or contiguous) cache: the body shared by
+ * AttentionRagged (internal/kernels/ragged.go:61-241) and AttentionPrefill / AttentionPrefillPaged
+ * (internal/kernels/prefill.go:409-560).  Positions pos <= limit and pos < kv_len are visible; the
+ * loop walks blocks of 128 up to `bound`.  Lane-per-position sequential dot products, binary-tree
+ * block maximum and sum over 128 lanes, sequential weighted sum of V per output element. */
+static void attn_causal_unit(const attn_unit *up, uint32_t limit, uint32_t bound, float *o_out)
+{
+    const attn_unit u = *up;
+    const float *qr = u.q;
+    const void *k = u.k, *v = u.v;
+    const uint32_t D = u.head_dim, kv_len = u.kv_len;
+    const float scale = u.scale;
+    float m = -3.4e38f, l = 0;
+    float o[ATTN_BLOCK], scores[ATTN_BLOCK], red[ATTN_BLOCK];
+    for (uint32_t t = 0; t < ATTN_BLOCK; t++) o[t] = 0;
+
+    for (uint32_t base = 0; base < bound; base += ATTN_BLOCK) {
+        for (uint32_t lane = 0; lane < ATTN_BLOCK; lane++) {
+            uint32_t pos = base + lane;
+            float score = -3.4e38f;
+            if (pos <= limit && pos < kv_len) {
+                uint64_t row = attn_row(&u, pos);
+                float dot = 0;
+                for (uint32_t j = 0; j < D; j++) dot = dot + qr[j] * cache_at(&u, k, row + j);
+                score = dot * scale;
+            }
+            scores[lane] = score;
+            red[lane] = score;
+        }
+        for (uint32_t stride = ATTN_BLOCK / 2; stride > 0; stride /= 2)
+            for (uint32_t lane = 0; lane < stride; lane++)
+                red[lane] = k_max(red[lane], red[lane + stride]);
+        float block_max = red[0];
+        float next = k_max(m, block_max);
+        float alpha = k_exp(m - next);
+        for (uint32_t lane = 0; lane < ATTN_BLOCK; lane++) {
+            uint32_t pos = base + lane;
+            float e = 0;
+            if (pos <= limit && pos < kv_len) e = k_exp(scores[lane] - next);
+            scores[lane] = e;
+            red[lane] = e;
+        }
+        for (uint32_t stride = ATTN_BLOCK / 2; stride > 0; stride /= 2)
+            for (uint32_t lane = 0; lane < stride; lane++)
+                red[lane] = red[lane] + red[lane + stride];
+        l = alpha * l + red[0];
+        m = next;
+        for (uint32_t lane = 0; lane < D && lane < ATTN_BLOCK; lane++) {
+            float ol = alpha * o[lane];
+            for (uint32_t j = 0; j < ATTN_BLOCK; j++) {
+                if (base + j <= limit && base + j < kv_len)
+                    ol = ol + scores[j] * cache_at(&u, v, attn_row(&u, base + j) + lane);
+            }
+            o[lane] = ol;
+        }
+    }
+    for (uint32_t lane = 0; lane < D && lane < ATTN_BLOCK; lane++) o_out[lane] = o[lane] / l;
+}
+
 /* AttentionRagged / AttentionRaggedF16, internal/kernels/ragged.go:61-241, raggedf16.go:43. */
 ORC_API void orc_attention_ragged(uint32_t tokens, uint32_t batch, uint32_t q_heads,
                                   uint32_t kv_heads, uint32_t head_dim, uint32_t block,
@@ -528,51 +587,52 @@ ORC_API void orc_attention_ragged(uint32_t tokens, uint32_t batch, uint32_t q_he
 
         attn_unit u = { qr, k, v, cache_f16, prow, block, kv_heads, head_dim, kv_head, kv_len,
                         scale, 1 };
-        float m = -3.4e38f, l = 0;
-        float o[ATTN_BLOCK], scores[ATTN_BLOCK], red[ATTN_BLOCK];
-        for (uint32_t t = 0; t < ATTN_BLOCK; t++) o[t] = 0;
+        attn_causal_unit(&u, limit, bound, o_out);
+    }
+}
 
-        for (uint32_t base = 0; base < bound; base += ATTN_BLOCK) {
-            for (uint32_t lane = 0; lane < ATTN_BLOCK; lane++) {
-                uint32_t pos = base + lane;
-                float score = -3.4e38f;
-                if (pos <= limit && pos < kv_len) {
-                    uint64_t row = attn_row(&u, pos);
-                    float dot = 0;
-                    for (uint32_t j = 0; j < D; j++) dot = dot + qr[j] * cache_at(&u, k, row + j);
-                    score = dot * scale;
-                }
-                scores[lane] = score;
-                red[lane] = score;
-            }
-            for (uint32_t stride = ATTN_BLOCK / 2; stride > 0; stride /= 2)
-                for (uint32_t lane = 0; lane < stride; lane++)
-                    red[lane] = k_max(red[lane], red[lane + stride]);
-            float block_max = red[0];
-            float next = k_max(m, block_max);
-            float alpha = k_exp(m - next);
-            for (uint32_t lane = 0; lane < ATTN_BLOCK; lane++) {
-                uint32_t pos = base + lane;
-                float e = 0;
-                if (pos <= limit && pos < kv_len) e = k_exp(scores[lane] - next);
-                scores[lane] = e;
-                red[lane] = e;
-            }
-            for (uint32_t stride = ATTN_BLOCK / 2; stride > 0; stride /= 2)
-                for (uint32_t lane = 0; lane < stride; lane++)
-                    red[lane] = red[lane] + red[lane + stride];
-            l = alpha * l + red[0];
-            m = next;
-            for (uint32_t lane = 0; lane < D && lane < ATTN_BLOCK; lane++) {
-                float ol = alpha * o[lane];
-                for (uint32_t j = 0; j < ATTN_BLOCK; j++) {
-                    if (base + j <= limit && base + j < kv_len)
-                        ol = ol + scores[j] * cache_at(&u, v, attn_row(&u, base + j) + lane);
-                }
-                o[lane] = ol;
-            }
-        }
-        for (uint32_t lane = 0; lane < D && lane < ATTN_BLOCK; lane++) o_out[lane] = o[lane] / l;
+/* AttentionPrefill / AttentionPrefillF16 (contiguous cache), internal/kernels/prefill.go:197-360:
+ * q_seq query rows of ONE sequence, row s seeing positions <= base + s.  cache_elems = len(k). */
+ORC_API void orc_attention_prefill(uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t q_seq,
+                                   uint32_t base, float scale, const float *q, const void *k,
+                                   const void *v, int cache_f16, uint64_t cache_elems,
+                                   const uint32_t *lengths, float *out)
+{
+    int64_t groups = (int64_t)q_seq * q_heads;
+    uint32_t capacity = (uint32_t)(cache_elems / ((uint64_t)kv_heads * head_dim));
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t gidx = 0; gidx < groups; gidx++) {
+        uint32_t s = (uint32_t)(gidx / q_heads), h = (uint32_t)(gidx % q_heads);
+        size_t qbase = ((size_t)s * q_heads + h) * head_dim;
+        uint32_t kv_len = lengths[0], limit = base + s, bound = limit + 1;
+        if (bound > capacity) bound = capacity;
+        if (kv_len > capacity) kv_len = capacity;
+        attn_unit u = { q + qbase, k, v, cache_f16, NULL, 1, kv_heads, head_dim,
+                        h / (q_heads / kv_heads), kv_len, scale, 1 };
+        attn_causal_unit(&u, limit, bound, out + qbase);
+    }
+}
+
+/* AttentionPrefillPaged / AttentionPrefillPagedF16, internal/kernels/prefill.go:409-560,
+ * pagedprefillf16.go:31: the same over a page table; n_pages = len(pages). */
+ORC_API void orc_attention_prefill_paged(uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
+                                         uint32_t q_seq, uint32_t base, uint32_t block, float scale,
+                                         const float *q, const void *k, const void *v, int cache_f16,
+                                         const uint32_t *pages, uint32_t n_pages,
+                                         const uint32_t *lengths, float *out)
+{
+    int64_t groups = (int64_t)q_seq * q_heads;
+    uint32_t capacity = n_pages * block;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t gidx = 0; gidx < groups; gidx++) {
+        uint32_t s = (uint32_t)(gidx / q_heads), h = (uint32_t)(gidx % q_heads);
+        size_t qbase = ((size_t)s * q_heads + h) * head_dim;
+        uint32_t kv_len = lengths[0], limit = base + s, bound = limit + 1;
+        if (bound > capacity) bound = capacity;
+        if (kv_len > capacity) kv_len = capacity;
+        attn_unit u = { q + qbase, k, v, cache_f16, pages, block, kv_heads, head_dim,
+                        h / (q_heads / kv_heads), kv_len, scale, 1 };
+        attn_causal_unit(&u, limit, bound, out + qbase);
     }
 }
 
@@ -613,6 +673,220 @@ ORC_API void orc_attention_definition_f64(uint32_t q_heads, uint32_t kv_heads, u
             out[(size_t)h * head_dim + i] = acc / total;
         }
         free(sc);
+    }
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* Sampling policy on the device: internal/kernels/norm.go:80-137 (Softmax), rowsample.go:42-379 */
+/* (the per-row forms), topk.go:59-256, penalty.go:60-141, sample.go:133-171 (the uniform forms). */
+/* Workgroups of 128 lanes: lane l walks i = l, l + 128, ...; reductions are binary trees.         */
+/* ------------------------------------------------------------------------------------------ */
+#define ROW_WIDTH 128u
+#define TOP_MAX_ROUNDS 128u   /* internal/kernels/topk.go:30 */
+
+/* Softmax, internal/kernels/norm.go:94-137. */
+ORC_API void orc_softmax(uint32_t rows, uint32_t width, const float *x, float *out)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t row = 0; row < (int64_t)rows; row++) {
+        const float *xr = x + (size_t)row * width;
+        float sh[ROW_WIDTH];
+        for (uint32_t lid = 0; lid < ROW_WIDTH; lid++) {
+            float m = xr[lid % width];
+            for (uint32_t i = lid; i < width; i += ROW_WIDTH) m = k_max(m, xr[i]);
+            sh[lid] = m;
+        }
+        for (uint32_t stride = ROW_WIDTH / 2; stride > 0; stride /= 2)
+            for (uint32_t lid = 0; lid < stride; lid++) sh[lid] = k_max(sh[lid], sh[lid + stride]);
+        float row_max = sh[0];
+        for (uint32_t lid = 0; lid < ROW_WIDTH; lid++) {
+            float acc = 0;
+            for (uint32_t i = lid; i < width; i += ROW_WIDTH) acc = acc + k_exp(xr[i] - row_max);
+            sh[lid] = acc;
+        }
+        for (uint32_t stride = ROW_WIDTH / 2; stride > 0; stride /= 2)
+            for (uint32_t lid = 0; lid < stride; lid++) sh[lid] = sh[lid] + sh[lid + stride];
+        float total = sh[0];
+        for (uint32_t i = 0; i < width; i++) out[(size_t)row * width + i] = k_exp(xr[i] - row_max) / total;
+    }
+}
+
+/* ScaleRows, rowsample.go:226-236: a factor of zero marks a greedy row and scales by one. */
+ORC_API void orc_scale_rows(uint32_t rows, uint32_t vocab, const float *x, const float *factors, float *out)
+{
+    for (size_t i = 0; i < (size_t)rows * vocab; i++) {
+        float f = factors[i / vocab];
+        if (f == 0) f = 1;
+        out[i] = x[i] * f;
+    }
+}
+
+/* One extraction round of TopKMask / TopPMask: the largest entry strictly below the frontier in the
+ * order (value descending, index ascending), by 128 strided lanes and a binary tree that breaks
+ * value ties towards the lower index (topk.go:71-112). */
+static void top_round(const float *w, uint32_t vocab, float front_v, uint32_t front_i, float *best_v,
+                      uint32_t *best_i)
+{
+    float best[ROW_WIDTH];
+    uint32_t at[ROW_WIDTH];
+    for (uint32_t lane = 0; lane < ROW_WIDTH; lane++) {
+        float v = -3.4e38f;
+        uint32_t idx = vocab;
+        for (uint32_t i = lane; i < vocab; i += ROW_WIDTH) {
+            float x = w[i];
+            int below = x < front_v;
+            if (x == front_v && i > front_i) below = 1;
+            if (below) {
+                int better = x > v;
+                if (x == v && i < idx) better = 1;
+                if (better) { v = x; idx = i; }
+            }
+        }
+        best[lane] = v;
+        at[lane] = idx;
+    }
+    for (uint32_t stride = 64; stride > 0; stride /= 2)
+        for (uint32_t lane = 0; lane < stride; lane++) {
+            float a = best[lane], b = best[lane + stride];
+            if (b > a) { best[lane] = b; at[lane] = at[lane + stride]; }
+            else if (b == a && at[lane + stride] < at[lane]) at[lane] = at[lane + stride];
+        }
+    *best_v = best[0];
+    *best_i = at[0];
+}
+
+static void top_keep(const float *w, uint32_t vocab, float front_v, uint32_t front_i, int keep_all, float *out)
+{
+    for (uint32_t i = 0; i < vocab; i++) {
+        float x = w[i];
+        int keep = x > front_v;
+        if (x == front_v && i <= front_i) keep = 1;
+        if (keep_all) keep = 1;
+        out[i] = keep ? x : 0.0f;
+    }
+}
+
+/* TopKMaskRows (rowsample.go:42-120) when ks != NULL: k per row, 0 or >= vocab passes the row
+ * through; TopKMask (topk.go:59-130) when ks == NULL: the uniform k, no pass-through. */
+ORC_API void orc_topk_mask(uint32_t rows, uint32_t vocab, const float *weights, const uint32_t *ks,
+                           uint32_t uniform_k, float *out)
+{
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t row = 0; row < (int64_t)rows; row++) {
+        const float *w = weights + (size_t)row * vocab;
+        uint32_t rounds = ks ? ks[row] : uniform_k;
+        if (rounds > TOP_MAX_ROUNDS) rounds = TOP_MAX_ROUNDS;
+        if (ks && rounds >= vocab) rounds = 0;
+        float front_v = 3.4e38f;
+        uint32_t front_i = 0;
+        for (uint32_t r = 0; r < rounds; r++) top_round(w, vocab, front_v, front_i, &front_v, &front_i);
+        top_keep(w, vocab, front_v, front_i, ks && rounds == 0, out + (size_t)row * vocab);
+    }
+}
+
+/* TopPMaskRows (rowsample.go:126-220) when ps != NULL: p per row, outside (0, 1) passes the row
+ * through; TopPMask (topk.go:153-256) when ps == NULL: the uniform p, always active. */
+ORC_API void orc_topp_mask(uint32_t rows, uint32_t vocab, const float *weights, const float *ps,
+                           float uniform_p, float *out)
+{
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t row = 0; row < (int64_t)rows; row++) {
+        const float *w = weights + (size_t)row * vocab;
+        float p = ps ? ps[row] : uniform_p;
+        int active = ps ? (p > 0 && p < 1) : 1;
+        float part[ROW_WIDTH];
+        for (uint32_t lane = 0; lane < ROW_WIDTH; lane++) {
+            float sum = 0;
+            for (uint32_t i = lane; i < vocab; i += ROW_WIDTH) sum = sum + w[i];
+            part[lane] = sum;
+        }
+        for (uint32_t stride = 64; stride > 0; stride /= 2)
+            for (uint32_t lane = 0; lane < stride; lane++) part[lane] = part[lane] + part[lane + stride];
+        float target = part[0] * p;
+        float front_v = 3.4e38f, kept = 0;
+        uint32_t front_i = 0;
+        for (uint32_t r = 0; r < TOP_MAX_ROUNDS; r++) {
+            float bv;
+            uint32_t bi;
+            if (!(active && kept < target)) break;          /* later rounds change nothing */
+            top_round(w, vocab, front_v, front_i, &bv, &bi);
+            front_v = bv;
+            front_i = bi;
+            kept = kept + front_v;
+        }
+        top_keep(w, vocab, front_v, front_i, !active, out + (size_t)row * vocab);
+    }
+}
+
+/* SampleRows (rowsample.go:246-300) when factors != NULL: the argmax of a row whose factor is zero,
+ * a categorical walk otherwise; SampleCategorical (sample.go:133-171) when factors == NULL. */
+ORC_API void orc_sample_rows(uint32_t rows, uint32_t vocab, const float *probs, const float *draws,
+                             const float *factors, uint32_t *out)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < (int64_t)rows; r++) {
+        const float *p = probs + (size_t)r * vocab;
+        if (factors && factors[r] == 0) {
+            float v = -3.4e38f;
+            uint32_t idx = 0;
+            for (uint32_t i = 0; i < vocab; i++) if (p[i] > v) { v = p[i]; idx = i; }
+            out[r] = idx;
+            continue;
+        }
+        float draw = draws[r];
+        if (draw < 0.0f) draw = 0.0f;
+        if (draw > 0.99999994f) draw = 0.99999994f;
+        float total = 0;
+        for (uint32_t i = 0; i < vocab; i++) total = total + p[i];
+        float target = draw * total;
+        float acc = 0;
+        uint32_t chosen = vocab - 1;
+        int found = 0;
+        for (uint32_t i = 0; i < vocab; i++) {
+            acc = acc + p[i];
+            if (!found && acc > target) { chosen = i; found = 1; }
+        }
+        out[r] = chosen;
+    }
+}
+
+/* LogitBias, rowsample.go:304-320. */
+ORC_API void orc_logit_bias(uint32_t rows, uint32_t vocab, uint32_t slots, const float *logits,
+                            const uint32_t *ids, const float *values, float *out)
+{
+    for (size_t i = 0; i < (size_t)rows * vocab; i++) {
+        uint32_t row = (uint32_t)(i / vocab), id = (uint32_t)(i - (size_t)row * vocab);
+        float x = logits[i];
+        for (uint32_t s = 0; s < slots; s++)
+            if (ids[(size_t)row * slots + s] == id) x = x + values[(size_t)row * slots + s];
+        out[i] = x;
+    }
+}
+
+/* PenaltyClearRows, PenaltyCountRows, PenaltyApplyRows (rowsample.go:325-379), which are
+ * PenaltyClear / PenaltyCount / PenaltyApply (penalty.go:60-141) with a row axis: the counts are
+ * rebuilt from the filled part of each row's history ring, then each counted token is penalised
+ * once.  counts [rows][vocab] is written. */
+ORC_API void orc_penalty_rows(uint32_t rows, uint32_t vocab, uint32_t history_cap, const float *logits,
+                              const uint32_t *history, const uint32_t *filled, const float *repetition,
+                              const float *presence, const float *frequency, uint32_t *counts, float *out)
+{
+    memset(counts, 0, (size_t)rows * vocab * sizeof(uint32_t));
+    for (uint32_t row = 0; row < rows; row++)
+        for (uint32_t j = 0; j < history_cap && j < filled[row]; j++) {
+            uint32_t id = history[(size_t)row * history_cap + j];
+            if (id < vocab) counts[(size_t)row * vocab + id] += 1;
+        }
+    for (size_t i = 0; i < (size_t)rows * vocab; i++) {
+        uint32_t row = (uint32_t)(i / vocab);
+        float l = logits[i];
+        uint32_t c = counts[i];
+        if (c == 0) { out[i] = l; continue; }
+        float rep = repetition[row];
+        if (rep != 0 && rep != 1) {
+            if (l > 0) l = l / rep; else l = l * rep;
+        }
+        out[i] = l - presence[row] - frequency[row] * (float)c;
     }
 }
 

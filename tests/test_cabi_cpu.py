@@ -44,7 +44,7 @@ def test_an_unknown_kernel_is_a_refusal_not_a_fallback():
     assert rc == _lib.AB_ERR_UNSUPPORTED
     assert b"no CPU fallback" in L.ab_last_error()
     assert L.ab_supports_kernel(None, b"QuantMatVecInt4", None) == _lib.AB_OK
-    assert L.ab_supports_kernel(None, b"Softmax", None) == _lib.AB_ERR_UNSUPPORTED
+    assert L.ab_supports_kernel(None, b"LinearAttention", None) == _lib.AB_ERR_UNSUPPORTED
 
 
 def test_workspace_query_and_argument_checks_need_no_gpu():

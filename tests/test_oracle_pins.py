@@ -411,3 +411,127 @@ def test_support_operators_against_numpy(rng):
     orc.scatter_rows(table[:3].copy(), [9, 10, 2], state)
     assert np.array_equal(state[9], table[0]) and np.array_equal(state[2], table[2])
     assert np.count_nonzero(state) == 12          # the row with id 10 was dropped
+
+
+# ----------------------------------------------------------------------------- prefill attention
+def test_prefill_equals_incremental_decode():
+    # internal/kernels/prefill_test.go:185-250: cos/sin fixtures, n = 6 tokens prefilled at once
+    # against one decode step per token over a growing cache, within 1e-5 (1 + |x|)
+    qH, kvH, D, n = 4, 2, 8, 6
+    scale = _scale(D)
+    i = np.arange(n * kvH * D)
+    k = np.cos(i * 0.23).astype(np.float32)
+    v = (np.sin(i * 0.19).astype(np.float32) * np.float32(2)).astype(np.float32)
+    q = np.sin(np.arange(n * qH * D) * 0.41).astype(np.float32)
+    kc, vc = k.reshape(n, kvH, D), v.reshape(n, kvH, D)
+    pre = orc.attention_prefill(q, kc, vc, np.array([n], np.uint32), qH, kvH, D, n, 0, scale)
+    for step in range(n):
+        one = orc.attention_decode(q[step * qH * D:(step + 1) * qH * D], kc[:step + 1], vc[:step + 1],
+                                   np.array([step + 1], np.uint32), qH, kvH, D, scale)
+        got = pre[step * qH * D:(step + 1) * qH * D]
+        assert np.all(np.abs(got - one) <= 1e-5 * (1 + np.abs(one))), step
+
+
+def test_paged_prefill_matches_the_contiguous_one_bit_for_bit(rng):
+    # internal/kernels/prefill_test.go:1120-1190: a page table is an addressing, so the two answers
+    # are the same answer (qHeads 4, kvHeads 2, headDim 16, block 8, 300 tokens from position 0)
+    qH, kvH, D, block, q_seq, base = 4, 2, 16, 8, 300, 0
+    kv_len = base + q_seq
+    n_pages = (kv_len + block - 1) // block
+    pool = 4 * n_pages
+    q = rng.standard_normal(q_seq * qH * D).astype(np.float32)
+    pk = rng.standard_normal((pool * block, kvH, D)).astype(np.float32)
+    pv = rng.standard_normal((pool * block, kvH, D)).astype(np.float32)
+    pages = rng.permutation(pool)[:n_pages].astype(np.uint32)
+    lengths = np.array([kv_len], np.uint32)
+    scale = _scale(D)
+    paged = orc.attention_prefill_paged(q, pk, pv, pages, lengths, qH, kvH, D, q_seq, base, block, scale)
+    rows = np.array([pages[j // block] * block + j % block for j in range(kv_len)])
+    contiguous = orc.attention_prefill(q, pk[rows], pv[rows], lengths, qH, kvH, D, q_seq, base, scale)
+    assert np.array_equal(paged, contiguous)
+    # and against the definition in binary64, row by row of the causal mask
+    for s_ in (0, 1, 127, 128, 299):
+        want = orc.attention_definition_f64(q[s_ * qH * D:(s_ + 1) * qH * D], pk, pv, rows[:base + s_ + 1],
+                                            qH, kvH, D, scale)
+        assert np.max(np.abs(paged[s_ * qH * D:(s_ + 1) * qH * D] - want)) <= 1e-5
+
+
+# ----------------------------------------------------------------------------- sampling policy
+def _kept(out):
+    return [i for i, v in enumerate(np.ravel(out)) if v != 0]
+
+
+def test_categorical_walks_the_distribution():
+    # internal/kernels/sample_test.go:105-150
+    probs = np.array([0.1, 0.2, 0.3, 0.4], np.float32)
+    for draw, want in [(0, 0), (0.05, 0), (0.1, 1), (0.15, 1), (0.3, 2), (0.45, 2), (0.6, 3), (0.99, 3),
+                       (0.999999, 3), (-0.5, 0), (1.5, 3), (1.0, 3)]:
+        assert orc.sample_rows(probs, [draw])[0] == want, draw
+    short = np.array([0.25, 0.25, 0.25, 0.2499], np.float32)
+    assert orc.sample_rows(short, [0.9999])[0] == 3
+
+
+def test_top_k_keeps_exactly_k_and_the_largest():
+    # internal/kernels/topk_test.go:67-105, ties to the lowest indices
+    for w, k, want in [([0.1, 0.5, 0.2, 0.4, 0.3], 2, [1, 3]), ([0.1, 0.5, 0.2], 1, [1]),
+                       ([0.3, 0.1, 0.2], 3, [0, 1, 2]), ([5, 5, 5, 5, 1], 2, [0, 1]),
+                       ([2, 2, 2, 2], 3, [0, 1, 2]), ([0, 3, 0, 1, 0], 2, [1, 3])]:
+        out = orc.topk_mask(np.array(w, np.float32), k)
+        assert _kept(out) == want, (w, k)
+        assert all(out[i] == np.float32(w[i]) for i in want)
+
+
+def test_top_p_keeps_the_nucleus_and_is_relative_to_its_input():
+    # internal/kernels/topk_test.go:152-225
+    w = np.array([0.1, 0.2, 0.3, 0.4], np.float32)
+    for p, want in [(0.3, [3]), (0.4, [3]), (0.5, [2, 3]), (0.7, [2, 3]), (0.9, [1, 2, 3]), (1.0, [0, 1, 2, 3])]:
+        assert _kept(orc.topp_mask(w, p)) == want, p
+    assert _kept(orc.topp_mask(w * np.float32(37), 0.5)) == _kept(orc.topp_mask(w, 0.5))
+    ramp = np.arange(1, 65, dtype=np.float32)
+    after_k = orc.topk_mask(ramp, 8)
+    after_p = _kept(orc.topp_mask(after_k, 0.5))
+    assert 0 < len(after_p) <= 8 and set(after_p) <= set(_kept(after_k))
+
+
+def test_truncation_respects_its_bound_and_matches_a_sort(rng):
+    # internal/kernels/topk_test.go:110-150, 229-260: at most TopMaxRounds = 128 entries are kept
+    w = rng.random(400).astype(np.float32)
+    assert len(_kept(orc.topk_mask(w, 300))) == 128
+    for k in (1, 7, 50):
+        want = sorted(sorted(range(400), key=lambda i: (-w[i], i))[:k])
+        assert _kept(orc.topk_mask(w, k)) == want
+    # per-row parameters: k = 0 passes the row through; so does k >= vocab, but the bound of 128
+    # rounds is applied FIRST (rowsample.go:51-57), so with 400 entries k = 400 keeps 128 of them
+    rows = np.stack([w, w, w])
+    out = orc.topk_mask(rows, np.array([0, 5, 400], np.uint32))
+    assert np.array_equal(out[0], w) and len(_kept(out[1])) == 5 and len(_kept(out[2])) == 128
+    small = orc.topk_mask(np.stack([w[:100]]), np.array([100], np.uint32))
+    assert np.array_equal(small[0], w[:100])
+    outp = orc.topp_mask(rows, np.array([0.0, 0.5, 1.0], np.float32))
+    assert np.array_equal(outp[0], w) and 0 < len(_kept(outp[1])) < 400 and np.array_equal(outp[2], w)
+
+
+def test_penalties():
+    # internal/kernels/penalty_test.go:40-135
+    logits = np.array([0.1, -0.3, 2.7, -1.9, 0.30000001, 1e-30, -1e-30, 3.3], np.float32)
+    got, _ = orc.penalty_rows(logits, [2, 5, 0, 0], 2, 1.3, 0.5, 0.25)
+    for i in range(8):
+        if i not in (2, 5):
+            assert got[0, i] == logits[i]
+    got, _ = orc.penalty_rows(np.array([2.0, -2.0], np.float32), [0, 1], 2, 2.0, 0.0, 0.0)
+    assert got[0, 0] < 2.0 and got[0, 1] == np.float32(-4)
+    got, _ = orc.penalty_rows(np.zeros(3, np.float32), [0, 1, 1, 2, 2, 2, 0, 0], 6, 0.0, 1.0, 0.5)
+    assert np.array_equal(got[0], np.array([-1.5, -2, -2.5], np.float32))
+    got, _ = orc.penalty_rows(np.zeros(4, np.float32), [1, 2, 3, 0, 0, 0, 0, 0], 3, 0.0, 1.0, 0.0)
+    assert np.array_equal(got[0], np.array([0, -1, -1, -1], np.float32))
+    got, counts = orc.penalty_rows(np.zeros(4, np.float32), [9, 4, 1, 4], 4, 0.0, 1.0, 0.0)
+    assert got[0, 3] == 0 and np.array_equal(counts[0], np.array([0, 1, 0, 0], np.uint32))
+
+
+def test_softmax_is_a_distribution_and_matches_binary64(rng):
+    x = (rng.standard_normal((3, 1000)) * 5).astype(np.float32)
+    x[1] += 100                                       # a logit of 100 is ordinary
+    y = orc.softmax(x)
+    e = np.exp(x.astype(np.float64) - x.max(axis=1, keepdims=True))
+    assert np.max(np.abs(y - e / e.sum(axis=1, keepdims=True))) < 1e-6
+    assert np.all(np.abs(y.sum(axis=1) - 1) < 1e-5)
