@@ -63,6 +63,17 @@ int check_cuda(cudaError_t e, const char *what)
     return fail(AB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
+// Whether the support kernels (norms, RoPE, attention, sampling) are launched as programmatic
+// dependents too.  Off unless AB_PDL=1: measured on the 7B-shape decode step, dependents that start
+// early and wait hold SM resources the running kernel's later waves need (8.97 ms per step against
+// 8.01 ms with only the int4 products launched that way).  The kernels still TRIGGER their
+// dependents early, which is what lets the product that follows a norm prefetch its weights.
+bool pdl_enabled()
+{
+    static const bool on = getenv("AB_PDL") && atoi(getenv("AB_PDL")) != 0;
+    return on;
+}
+
 static std::atomic<unsigned long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 

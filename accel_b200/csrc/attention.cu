@@ -108,6 +108,7 @@ attn_partition_kernel(const AttnParams p)
 {
     // With G > 1 blockIdx.y is a KV head and the CTA serves its G query heads; with G == 1 it is
     // a query head, which also covers group widths that have no instantiation.
+    pdl_wait();          // the kernel runs in several waves: its dependent starts as the last one drains
     const uint32_t part = blockIdx.x, row = blockIdx.z;
     const uint32_t hq0 = blockIdx.y * G;
     const uint32_t kvh = G == 1 ? blockIdx.y / (p.q_heads / p.kv_heads) : blockIdx.y;
@@ -281,6 +282,7 @@ template <typename T, int G, int kGqaUnroll>
 __global__ void __launch_bounds__(kAttnThreads)
 attn_partition_gqa_kernel(const AttnParams p)
 {
+    pdl_wait();
     const uint32_t part = blockIdx.x, row = blockIdx.z, kvh = blockIdx.y;
     const uint32_t hq0 = kvh * G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sl = lane & 15, half = lane >> 4;
@@ -442,6 +444,7 @@ attn_partition_gqa_kernel(const AttnParams p)
 // grid = (q_heads, rows); one thread per output element.
 __global__ void attn_combine_kernel(const AttnParams p)
 {
+    pdl_enter();
     const uint32_t h = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
     const RowView rv = row_view(p, row);
     if (rv.zero || d >= p.head_dim) return;
@@ -495,31 +498,37 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
     // 8-byte loads
     const bool half_rows = sizeof(T) == 2 && group == 1 && p.head_dim % 8 == 0 && !gqa_off;
     static const int unroll_env = getenv("AB_ATTN_UNROLL") ? atoi(getenv("AB_ATTN_UNROLL")) : 0;   // for measurements
-#define AB_GQA(GG, UU) attn_partition_gqa_kernel<T, GG, UU><<<grid, kAttnThreads, 0, l.stream>>>(p)
+#define AB_GQA(GG, UU) lerr = launch_dependent(attn_partition_gqa_kernel<T, GG, UU>, grid, dim3(kAttnThreads), 0, l.stream, p)
+#define AB_MHA(GG) lerr = launch_dependent(attn_partition_kernel<T, GG>, grid, dim3(kAttnThreads), 0, l.stream, p)
+    cudaError_t lerr = cudaSuccess;
     const bool deep = unroll_env ? unroll_env >= 4 : false;
     switch (G) {
     case 1:
         if (half_rows) { if (deep) AB_GQA(1, 4); else AB_GQA(1, 2); }
-        else attn_partition_kernel<T, 1><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        else AB_MHA(1);
         break;
     case 2:
         if (gqa) { if (deep) AB_GQA(2, 4); else AB_GQA(2, 2); }
-        else attn_partition_kernel<T, 2><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        else AB_MHA(2);
         break;
     case 4:
         if (gqa) { if (deep) AB_GQA(4, 4); else AB_GQA(4, 2); }
-        else attn_partition_kernel<T, 4><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        else AB_MHA(4);
         break;
     default:
         if (gqa) AB_GQA(8, 2);
-        else attn_partition_kernel<T, 8><<<grid, kAttnThreads, 0, l.stream>>>(p);
+        else AB_MHA(8);
         break;
     }
 #undef AB_GQA
+#undef AB_MHA
     count_launch();
+    if (lerr != cudaSuccess) return check_cuda(lerr, name);
     if (p.parts > 1) {
         dim3 cgrid(p.q_heads, p.rows);
-        attn_combine_kernel<<<cgrid, 128, 0, l.stream>>>(p); count_launch();
+        lerr = launch_dependent(attn_combine_kernel, cgrid, dim3(128), 0, l.stream, p);
+        count_launch();
+        if (lerr != cudaSuccess) return check_cuda(lerr, name);
     }
     note_selection("%s: split-K decode, %u partition(s) of %d positions, %u query head(s) sharing "
                    "each K/V read, %u row(s), %s per position", name, p.parts, kPartition, group, p.rows,

@@ -39,6 +39,36 @@ int check_cuda(cudaError_t e, const char *what);   // maps a CUDA error to an ab
 int sm_count();                                    // SMs of the current device (cached)
 void count_launch();                               // one more kernel launch issued by this library
 
+// Programmatic dependent launch.  A kernel launched through launch_dependent may begin while the
+// kernel before it in the stream is still running; it must call pdl_enter() (or pdl_wait()) before
+// it reads or writes anything that kernel touches.  pdl_trigger() lets the kernel AFTER this one
+// begin: at the top of a kernel that fits the device at once, at the end of one that runs in
+// several waves (an early dependent would only hold resources the remaining waves need).
+// Both instructions do nothing in a kernel launched the ordinary way.  launch_dependent sets the
+// attribute only when pdl_enabled() (AB_PDL=1); the int4 products decide for themselves.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() { pdl_trigger(); pdl_wait(); }
+#endif
+bool pdl_enabled();
+
+template <typename... P, typename... A>
+inline cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A &&...args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
 inline uint32_t u32_at(const uint8_t *u, size_t off) { uint32_t v; memcpy(&v, u + off, 4); return v; }
 inline float f32_at(const uint8_t *u, size_t off) { float v; memcpy(&v, u + off, 4); return v; }
 

@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const float *__restric
                                                           float *__restrict__ norm_out, uint32_t width, float eps)
 {
     __shared__ float red[8];
+    pdl_enter();
     const size_t base = (size_t)blockIdx.x * width;
     float v[PER];
     float acc = 0.f;
@@ -62,11 +63,12 @@ int launch_add_rmsnorm(Launch &l)
     if (rows == 0) return AB_OK;
     auto a = ptr<const float>(l, 0), d = ptr<const float>(l, 1), w = ptr<const float>(l, 2);
     auto s = ptr<float>(l, 3), o = ptr<float>(l, 4);
-    if (width <= 256 * 4) add_rmsnorm_kernel<4><<<rows, 256, 0, l.stream>>>(a, d, w, s, o, width, eps);
-    else if (width <= 256 * 16) add_rmsnorm_kernel<16><<<rows, 256, 0, l.stream>>>(a, d, w, s, o, width, eps);
-    else add_rmsnorm_kernel<32><<<rows, 256, 0, l.stream>>>(a, d, w, s, o, width, eps);
+    cudaError_t e;
+    if (width <= 256 * 4) e = launch_dependent(add_rmsnorm_kernel<4>, dim3(rows), dim3(256), 0, l.stream, a, d, w, s, o, width, eps);
+    else if (width <= 256 * 16) e = launch_dependent(add_rmsnorm_kernel<16>, dim3(rows), dim3(256), 0, l.stream, a, d, w, s, o, width, eps);
+    else e = launch_dependent(add_rmsnorm_kernel<32>, dim3(rows), dim3(256), 0, l.stream, a, d, w, s, o, width, eps);
     count_launch();
-    return check_cuda(cudaGetLastError(), "AddRMSNorm");
+    return check_cuda(e, "AddRMSNorm");
 }
 
 // ---------------------------------------------------------------- RoPE(q), RoPE(k), ScatterRows(k), ScatterRows(v)
@@ -100,6 +102,7 @@ __global__ void rope_scatter_kernel(const uint32_t *__restrict__ pos_q, const ui
                                     float *__restrict__ k, const float *__restrict__ v,
                                     T *__restrict__ k_cache, T *__restrict__ v_cache, RopeScatterDims d)
 {
+    pdl_enter();
     const uint32_t half = d.head_dim / 2, rot_pairs = d.rotary / 2;
     const size_t nq = (size_t)d.batch * d.q_heads * half, nk = (size_t)d.batch * d.kv_heads * half;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -154,11 +157,12 @@ template <typename T> static int rope_scatter(Launch &l, const char *name)
                     l.len[3], l.len[4], l.len[5], l.len[6], l.len[7]);
     const size_t items = (size_t)(nq + 2 * nk) / 2;
     if (items == 0) return AB_OK;
-    rope_scatter_kernel<T><<<blocks_for(items, 128), 128, 0, l.stream>>>(
-        ptr<const uint32_t>(l, 0), ptr<const uint32_t>(l, 1), ptr<const uint32_t>(l, 2), ptr<float>(l, 3),
-        ptr<float>(l, 4), ptr<const float>(l, 5), ptr<T>(l, 6), ptr<T>(l, 7), d);
+    cudaError_t e = launch_dependent(rope_scatter_kernel<T>, dim3(blocks_for(items, 128)), dim3(128), 0, l.stream,
+                                     ptr<const uint32_t>(l, 0), ptr<const uint32_t>(l, 1), ptr<const uint32_t>(l, 2),
+                                     ptr<float>(l, 3), ptr<float>(l, 4), ptr<const float>(l, 5), ptr<T>(l, 6),
+                                     ptr<T>(l, 7), d);
     count_launch();
-    return check_cuda(cudaGetLastError(), name);
+    return check_cuda(e, name);
 }
 int launch_rope_scatter_qkv(Launch &l) { return rope_scatter<float>(l, "RopeScatterQKV"); }
 int launch_rope_scatter_qkv_f16(Launch &l) { return rope_scatter<uint16_t>(l, "RopeScatterQKVF16"); }

@@ -16,6 +16,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float *__restrict__ 
                                                       float eps)
 {
     __shared__ float red[8];
+    pdl_enter();
     const size_t base = (size_t)blockIdx.x * width;
     float acc = 0.f;
     for (uint32_t i = threadIdx.x; i < width; i += 256) { float v = x[base + i]; acc = fmaf(v, v, acc); }
@@ -39,9 +40,10 @@ int launch_rmsnorm(Launch &l)
         return fail(AB_ERR_INVALID, "RMSNorm: Rows=%u Width=%u; x[%u] w[%u] out[%u]", rows, width,
                     l.len[0], l.len[1], l.len[2]);
     if (rows == 0) return AB_OK;
-    rmsnorm_kernel<<<rows, 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<const float>(l, 1),
-                                               ptr<float>(l, 2), width, eps); count_launch();
-    return check_cuda(cudaGetLastError(), "RMSNorm");
+    cudaError_t e = launch_dependent(rmsnorm_kernel, dim3(rows), dim3(256), 0, l.stream, ptr<const float>(l, 0),
+                                     ptr<const float>(l, 1), ptr<float>(l, 2), width, eps);
+    count_launch();
+    return check_cuda(e, "RMSNorm");
 }
 
 // ---------------------------------------------------------------- RoPE
@@ -118,6 +120,7 @@ __global__ void gather_rows_kernel(const T *__restrict__ table, const uint32_t *
                                    float *__restrict__ out, uint32_t rows, uint32_t width,
                                    uint32_t capacity)
 {
+    pdl_enter();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)rows * width) return;
     uint32_t r = (uint32_t)(i / width), c = (uint32_t)(i % width), id = ids[r];
@@ -149,7 +152,10 @@ template <typename T> static int gather(Launch &l, const char *name)
                     name, rows, width, cap, l.len[0], l.len[1], l.len[2]);
     size_t n = (size_t)rows * width;
     if (n == 0) return AB_OK;
-    gather_rows_kernel<T><<<blocks_for(n, 256), 256, 0, l.stream>>>(ptr<const T>(l, 0), ptr<const uint32_t>(l, 1), ptr<float>(l, 2), rows, width, cap); count_launch();
+    cudaError_t e = launch_dependent(gather_rows_kernel<T>, dim3(blocks_for(n, 256)), dim3(256), 0, l.stream,
+                                     ptr<const T>(l, 0), ptr<const uint32_t>(l, 1), ptr<float>(l, 2), rows, width, cap);
+    count_launch();
+    if (e != cudaSuccess) return check_cuda(e, "GatherRows");
     return check_cuda(cudaGetLastError(), name);
 }
 template <typename T> static int scatter(Launch &l, const char *name)
@@ -176,6 +182,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
 {
     __shared__ float bv[8];
     __shared__ uint32_t bi[8];
+    pdl_enter();
     const size_t base = (size_t)blockIdx.x * vocab;
     float v = -3.4e38f;
     uint32_t idx = 0;
@@ -205,8 +212,10 @@ int launch_sample_argmax(Launch &l)
     if (l.len[0] < (uint64_t)rows * vocab)
         return fail(AB_ERR_INVALID, "SampleArgmax: Vocab=%u rows=%u; logits[%u]", vocab, rows, l.len[0]);
     if (rows == 0) return AB_OK;
-    argmax_kernel<<<rows, 256, 0, l.stream>>>(ptr<const float>(l, 0), ptr<uint32_t>(l, 1), vocab); count_launch();
-    return check_cuda(cudaGetLastError(), "SampleArgmax");
+    cudaError_t e = launch_dependent(argmax_kernel, dim3(rows), dim3(256), 0, l.stream, ptr<const float>(l, 0),
+                                     ptr<uint32_t>(l, 1), vocab);
+    count_launch();
+    return check_cuda(e, "SampleArgmax");
 }
 
 // ---------------------------------------------------------------- casts
@@ -250,6 +259,7 @@ __global__ void decode_step_inputs_kernel(const uint32_t *__restrict__ sampled,
                                           uint32_t *__restrict__ lengths, uint32_t batch, uint32_t hq,
                                           uint32_t hk, uint32_t block, uint32_t max_pages)
 {
+    pdl_enter();
     const uint32_t s = blockIdx.x;
     if (s >= batch) return;
     const uint32_t pos = lengths[s];
@@ -276,10 +286,12 @@ int launch_decode_step_inputs(Launch &l)
         return fail(AB_ERR_INVALID, "DecodeStepInputs: Batch=%u QHeads=%u KVHeads=%u Block=%u "
                     "MaxPages=%u does not match the lengths block", batch, hq, hk, block, mp);
     if (batch == 0) return AB_OK;
-    decode_step_inputs_kernel<<<batch, 64, 0, l.stream>>>(
-        ptr<const uint32_t>(l, 0), ptr<const uint32_t>(l, 1), ptr<uint32_t>(l, 2), ptr<uint32_t>(l, 3),
-        ptr<uint32_t>(l, 4), ptr<uint32_t>(l, 5), ptr<uint32_t>(l, 6), batch, hq, hk, block, mp); count_launch();
-    return check_cuda(cudaGetLastError(), "DecodeStepInputs");
+    cudaError_t e = launch_dependent(decode_step_inputs_kernel, dim3(batch), dim3(64), 0, l.stream,
+                                     ptr<const uint32_t>(l, 0), ptr<const uint32_t>(l, 1), ptr<uint32_t>(l, 2),
+                                     ptr<uint32_t>(l, 3), ptr<uint32_t>(l, 4), ptr<uint32_t>(l, 5), ptr<uint32_t>(l, 6),
+                                     batch, hq, hk, block, mp);
+    count_launch();
+    return check_cuda(e, "DecodeStepInputs");
 }
 
 // ---------------------------------------------------------------- quant.Int4Quantize on the device
