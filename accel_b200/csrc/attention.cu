@@ -492,16 +492,14 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
     const int G = (group == 2 || group == 4 || group == 8) ? (int)group : 1;
     dim3 grid(p.parts, G == 1 ? p.q_heads : p.kv_heads, p.rows);
     // grouped heads: half a warp per position when the head dimension allows 8 elements per lane
-    static const bool gqa_off = getenv("AB_ATTN_WARP_PER_POSITION") != nullptr;      // for measurements
-    const bool gqa = G > 1 && p.head_dim % 8 == 0 && !gqa_off;
+    const bool gqa = G > 1 && p.head_dim % 8 == 0;
     // an f16 cache without grouping: 16 lanes x 16 bytes cover a row, where a full warp would issue
     // 8-byte loads
-    const bool half_rows = sizeof(T) == 2 && group == 1 && p.head_dim % 8 == 0 && !gqa_off;
-    static const int unroll_env = getenv("AB_ATTN_UNROLL") ? atoi(getenv("AB_ATTN_UNROLL")) : 0;   // for measurements
+    const bool half_rows = sizeof(T) == 2 && group == 1 && p.head_dim % 8 == 0;
 #define AB_GQA(GG, UU) lerr = launch_dependent(attn_partition_gqa_kernel<T, GG, UU>, grid, dim3(kAttnThreads), 0, l.stream, p)
 #define AB_MHA(GG) lerr = launch_dependent(attn_partition_kernel<T, GG>, grid, dim3(kAttnThreads), 0, l.stream, p)
     cudaError_t lerr = cudaSuccess;
-    const bool deep = unroll_env ? unroll_env >= 4 : false;
+    const bool deep = false;      // four positions in flight per half warp measured no faster than two
     switch (G) {
     case 1:
         if (half_rows) { if (deep) AB_GQA(1, 4); else AB_GQA(1, 2); }

@@ -91,11 +91,6 @@ struct Int4BatchPlan { bool ok; int G; uint32_t tiles, splits, kc; };    // G gr
 Int4BatchPlan plan_int4_batch(uint32_t M, uint32_t N, uint32_t K);
 int run_int4_batch(const Launch &l, const Int4BatchPlan &p, float *out, uint32_t M, uint32_t N, uint32_t K);
 
-// the decode-batch int4 kernel on tcgen05 / TMEM (int4_decode_tc.cu)
-struct Int4DecodePlan { bool ok; int G; uint32_t tiles, splits, kc; };
-Int4DecodePlan plan_int4_decode(uint32_t M, uint32_t N, uint32_t K);
-int run_int4_decode(const Launch &l, const Int4DecodePlan &p, float *out, uint32_t M, uint32_t N, uint32_t K);
-int int4_decode_error_flag();
 
 // the 128 x 128 warp-MMA tile kernel of the grouped product, as a plain int4 product (grouped.cu)
 bool int4_tiles_ok(uint32_t N, uint32_t K);

@@ -342,23 +342,15 @@ int4_batch_kernel(const float *__restrict__ a, const uint2 *__restrict__ bq,
     cluster.sync();                              // nobody leaves while its sums are being read
 }
 
-static uint32_t env_u32(const char *name)
-{
-    const char *e = getenv(name);
-    return e ? (uint32_t)atoi(e) : 0u;
-}
-
 Int4BatchPlan plan_int4_batch(uint32_t M, uint32_t N, uint32_t K)
 {
     Int4BatchPlan p{};
     p.ok = N % kGroup == 0 && K % 16 == 0 && N > 0 && K > 0 && M > 0;
     if (!p.ok) return p;
     const uint32_t gpr = N / kGroup, sms = (uint32_t)sm_count();
-    static const uint32_t forced_g = env_u32("AB_INT4_TILE_GROUPS"), forced_s = env_u32("AB_INT4_SPLITS");
     // wide matrices: four groups per tile (one scale sector serves four groups, a quarter of the
     // activation traffic); narrow ones: one group per tile, or the SMs run short of CTAs
     uint32_t G = gpr >= 64 ? 4 : 1;
-    if (forced_g == 1 || forced_g == 2 || forced_g == 4) G = forced_g;
     p.G = (int)G;
     p.tiles = (gpr + G - 1) / G;
     const uint32_t slots = (4u / G) * sms;                         // CTAs resident at once
@@ -367,7 +359,6 @@ Int4BatchPlan plan_int4_batch(uint32_t M, uint32_t N, uint32_t K)
     // (a tensor-parallel shard: a few tiles) is a chain of latencies that only more CTAs shorten
     const uint32_t most = p.tiles * kBUsualCluster <= sms ? kBMaxCluster : kBUsualCluster;
     if (splits > most) splits = most;
-    if (forced_s) splits = forced_s;
     if (splits < 1) splits = 1;
     if (splits > (uint32_t)kBMaxCluster) splits = kBMaxCluster;
     uint32_t kc = ((K + splits - 1) / splits + 15) / 16 * 16;

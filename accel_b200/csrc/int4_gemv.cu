@@ -235,19 +235,12 @@ int4_row_kernel(const float *__restrict__ a, const uint4 *__restrict__ bq, const
     cluster.sync();                              // nobody leaves while its row is being read
 }
 
-static uint32_t env_u32(const char *name)
-{
-    const char *e = getenv(name);
-    return e ? (uint32_t)atoi(e) : 0u;
-}
-
 Int4RowPlan plan_int4_row(uint32_t N, uint32_t K)
 {
     Int4RowPlan p{};
     p.ok = N % kGroup == 0 && N > 0 && K > 0;
     if (!p.ok) return p;
     const uint32_t gpr = N / kGroup, sms = (uint32_t)sm_count();
-    static const uint32_t forced_w = env_u32("AB_INT4_ROW_GROUPS"), forced_s = env_u32("AB_INT4_SPLITS");
     // measured: about two CTAs per SM and clusters of at most eight do best; two groups per tile
     // for wide matrices (one scale sector serves both), one for narrow ones, unless the K ranges
     // (at most 768 rows) then make more CTAs than fit at once (three per SM at 168 registers)
@@ -256,7 +249,6 @@ Int4RowPlan plan_int4_row(uint32_t N, uint32_t K)
         p.tiles = (gpr + W - 1) / W;
         uint32_t splits = 2u * sms / p.tiles;
         if (splits > 8) splits = 8;
-        if (forced_s) splits = forced_s;
         if (splits < 1) splits = 1;
         if (splits > (uint32_t)kRowMaxCluster) splits = kRowMaxCluster;
         uint32_t kc = ((K + splits - 1) / splits + 15) / 16 * 16;
@@ -266,7 +258,6 @@ Int4RowPlan plan_int4_row(uint32_t N, uint32_t K)
     };
     lay(gpr >= 64 ? 2 : 1);
     if (p.W == 1 && p.tiles * p.splits > 3 * sms) lay(2);
-    if (forced_w == 1 || forced_w == 2) lay((int)forced_w);
     p.ok = p.splits <= (uint32_t)kRowMaxCluster;          // deeper K: another kernel takes it
     p.ws = 0;
     return p;

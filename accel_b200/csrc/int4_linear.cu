@@ -228,8 +228,7 @@ static int forced_path()
     if (v < 0) {
         const char *e = getenv("AB_INT4_PATH");
         v = !e ? 0 : (!strcmp(e, "tc") ? 1 : (!strcmp(e, "mma") ? 2 : (!strcmp(e, "simt") ? 3 :
-            (!strcmp(e, "batch") ? 4 : (!strcmp(e, "row") ? 5 : (!strcmp(e, "decode") ? 6 :
-            (!strcmp(e, "tiles") ? 7 : 0)))))));
+            (!strcmp(e, "batch") ? 4 : (!strcmp(e, "row") ? 5 : (!strcmp(e, "tiles") ? 7 : 0))))));
     }
     return v;
 }
@@ -261,7 +260,7 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     Int4Plan p = plan_int4(M, N, K);
     // two or more rows of activations go to the tensor cores; one row stays on the CUDA cores
     Int4MmaPlan mp = plan_int4_mma(M, N, K);
-    // AB_INT4_PATH = tiles | tc | batch | decode | mma | simt | row overrides the choice (for
+    // AB_INT4_PATH = tiles | tc | batch | mma | simt | row overrides the choice (for
     // measurements and tests)
     Int4TcPlan tp = plan_int4_tc(M, N, K);
     const int forced = forced_path();
@@ -269,17 +268,15 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     // tcgen05 kernel as built, which stays behind AB_INT4_PATH=tc)
     const bool use_tiles = int4_tiles_ok(N, K) && (forced == 7 || (forced == 0 && prefer_tiles(M, N, K)));
     const bool use_tc = !use_tiles && tp.ok && forced == 1;
-    Int4DecodePlan dp = plan_int4_decode(M, N, K);
-    const bool use_decode = !use_tc && !use_tiles && dp.ok && forced == 6;
     Int4BatchPlan bp = plan_int4_batch(M, N, K);
-    const bool use_batch = !use_tc && !use_tiles && !use_decode && bp.ok && (forced == 4 || (forced == 0 && M >= 2));
+    const bool use_batch = !use_tc && !use_tiles && bp.ok && (forced == 4 || (forced == 0 && M >= 2));
     const bool use_mma = !use_tc && !use_tiles && !use_batch && mp.ok && (forced == 2 || (forced == 0 && M >= 2));
     // one row: the streaming kernel that sums its own K splits (AB_INT4_PATH=simt keeps the older
     // two-kernel form, which is also the fallback when no counter slot is free)
     Int4RowPlan rp = plan_int4_row(N, K);
-    const bool use_row = !use_tc && !use_tiles && !use_mma && !use_batch && !use_decode && rp.ok && M == 1 && forced != 3;
+    const bool use_row = !use_tc && !use_tiles && !use_mma && !use_batch && rp.ok && M == 1 && forced != 3;
     if (l.query_ws) {
-        l.ws_need = use_tiles ? 0 : use_tc ? tp.ws : (use_batch || use_decode ? 0 : (use_mma ? mp.ws : (use_row ? 0 : p.ws)));
+        l.ws_need = use_tiles ? 0 : use_tc ? tp.ws : (use_batch ? 0 : (use_mma ? mp.ws : (use_row ? 0 : p.ws)));
         return AB_OK;
     }
 
@@ -323,15 +320,6 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
         note_selection("%s: tcgen05 kernel (M=128 x N=%d x K=16 MMAs, f16 operands, TMEM f32 "
                        "accumulator), %u column groups x %u K splits of %u rows", name, tp.nmma,
                        tp.groups, tp.splits, tp.kc);
-        return check_cuda(cudaGetLastError(), name);
-    }
-    if (use_decode) {
-        int rc = run_int4_decode(l, dp, out, M, N, K);
-        if (rc) return rc;
-        note_selection("%s: tcgen05 decode kernel (M=128 x N=16 x K=16 MMAs, f16 operands, TMEM f32 "
-                       "accumulator), %u tiles of %d column groups x a cluster of %u K splits of %u "
-                       "rows, %u pass(es) of 16 activation rows", name, dp.tiles, dp.G, dp.splits,
-                       dp.kc, (M + 15) / 16);
         return check_cuda(cudaGetLastError(), name);
     }
     if (use_batch) {
@@ -423,6 +411,17 @@ extern "C" AB_API int ab_quant_matmul_int4_noalloc(void *stream, const float *a,
     int rc = check_cuda(cudaGetDevice(&dev), "ab_quant_matmul_int4_noalloc");
     if (rc) return rc;
     if (dev < 0 || dev >= 64) return fail(AB_ERR_INVALID, "ab_quant_matmul_int4_noalloc: device %d", dev);
+    if (stream) {
+        // the array's address is the CURRENT device's: a stream of another device would be handed
+        // memory its kernels cannot be assumed to reach
+        int sdev = -1;
+        rc = check_cuda(cudaStreamGetDevice(static_cast<cudaStream_t>(stream), &sdev),
+                        "ab_quant_matmul_int4_noalloc: cudaStreamGetDevice");
+        if (rc) return rc;
+        if (sdev != dev)
+            return fail(AB_ERR_INVALID, "ab_quant_matmul_int4_noalloc: the stream belongs to device %d "
+                        "and device %d is current; make the stream's device current first", sdev, dev);
+    }
     if (!scratch_of[dev]) {
         void *p = nullptr;
         rc = check_cuda(cudaGetSymbolAddress(&p, g_static_scratch), "cudaGetSymbolAddress(scratch)");

@@ -239,7 +239,6 @@ Int4MmaPlan plan_int4_mma(uint32_t M, uint32_t N, uint32_t K)
     const uint32_t want = 3u * (uint32_t)sm_count();
     const uint32_t floor_kc = M > 8 ? 256 : 128;
     p.kc = 512;
-    if (const char *e = getenv("AB_INT4_KC")) { p.kc = (uint32_t)atoi(e); } else
     while (p.kc > floor_kc && tiles * ((K + p.kc - 1) / p.kc) < want) p.kc /= 2;
     p.splits = (K + p.kc - 1) / p.kc;
     p.ws = p.splits > 1 ? (size_t)p.splits * M * N * sizeof(float) : 0;

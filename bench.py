@@ -358,6 +358,73 @@ def run_moe(args):
         os._exit(0)
 
 
+def run_allreduce(args):
+    """Latency of one 256 KiB all-reduce (16 rows x 4096 floats, a row-parallel product of the decode
+    step) inside a CUDA graph: this library's one-shot kernel over NVLink peer memory, copying and in
+    place with the residual add and RMSNorm folded in, beside the process group's NCCL all-reduce and
+    NCCL followed by the AddRMSNorm kernel.  Run under torchrun, one rank per GPU."""
+    import torch
+    import torch.distributed as dist
+
+    from accel_b200 import runtime as rt
+    from accel_b200.peer import PeerAllReduce
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    dist.init_process_group("nccl", device_id=dev)
+    ar = PeerAllReduce(16 * 4096, dev, regions=(16 * 4096, 16 * 4096))
+
+    def per_call_us(fn):
+        y = torch.randn(16, 4096, device=dev)
+        st = torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st):
+            for _ in range(64):
+                fn(y)
+            st.synchronize()
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2, stream=st):
+                for _ in range(64):
+                    fn(y)
+            g2.replay()
+            st.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for _ in range(5):
+                g2.replay()
+            e1.record(st)
+            e1.synchronize()
+        return e0.elapsed_time(e1) / (5 * 64) * 1e3
+
+    gain = torch.ones(4096, device=dev)
+    s_out, n_out = torch.empty(16, 4096, device=dev), torch.empty(16, 4096, device=dev)
+    flip = [0]
+
+    def fused_inplace(y):
+        flip[0] ^= 1
+        ar.all_reduce_region_add_rms_norm(flip[0], y, gain, s_out, n_out, 1e-5)
+
+    def nccl_then_norm(y):
+        dist.all_reduce(y)
+        rt.launch("AddRMSNorm", [y, y, gain, s_out, n_out], rt.row_dims(16, 4096, 1e-5))
+
+    line = {"metric": "all_reduce_latency_256KiB", "unit": "us", "n_gpus": world, "higher_is_better": False,
+            "peer_copying": per_call_us(lambda y: ar.all_reduce_(y)),
+            "nccl": per_call_us(lambda y: dist.all_reduce(y)),
+            "peer_inplace_add_rmsnorm": per_call_us(fused_inplace),
+            "nccl_then_add_rmsnorm": per_call_us(nccl_then_norm)}
+    ar.check()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    os._exit(0)
+
+
 def run_b200(args):
     import numpy as np
     import torch
@@ -556,40 +623,59 @@ def run_b200(args):
     roofline = {"bound": "hbm", "kernel": "attn_partition_kernel (+ attn_combine_kernel)",
                 "achieved": attn_gbs, "peak": peak, "unit": "GB/s", "frac": attn_gbs / peak,
                 "peak_source": peak_src, "bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
-                # dram__bytes_read + dram__bytes_write of one launch, from the ncu capture summarised in
-                # profiles/attn_partition_kernel_config4_layer.md (same kernel, same per-launch
-                # size: a launch reads one layer's cache whatever the layer count), scaled by the
-                # bytes of this run when the cache dtype or shard differs
-                "traffic": int(1.0790e9 * attn_bytes / 1087906112)}
+                # dram__bytes_read + dram__bytes_write of one launch: NOT measured in this run (it needs
+                # a profiler); the figure of the committed ncu capture of this kernel at this per-launch
+                # size (a launch reads one layer's cache whatever the layer count), scaled by this
+                # run's bytes when the cache dtype or the shard differs
+                "traffic": int(1.0790e9 * attn_bytes / 1087906112),
+                "traffic_source": "ncu capture of the same kernel and per-launch size, summarised under "
+                                  "profiles/, scaled by bytes; not re-measured by this run"}
 
     # ---- int4 GEMV bandwidth (the metric's second figure): K=4096, N=11008, M=1, rotating over
-    # the layers' gate and up matrices (64 x 24 MB, larger than L2)
+    # the layers' gate and up matrices (64 x 24 MB, larger than L2).  The headline figure is the
+    # kernel the step uses (the load-time prepack of the same matrices); the reference-layout
+    # kernel on quant.Int4Quantize's planes is reported beside it.
     gemv = None
     if world == 1 and cfg.layers >= 4:
         a1 = torch.randn(cfg.d_model, device=dev)
         out1 = torch.empty(cfg.ffn, device=dev)
         mats = [m for L in model.layers for m in (L.wg, L.wu)]
         u = dec._u("<IIII", 0, cfg.ffn, cfg.d_model, 0)
+        gbytes = mats[0].nbytes + cfg.d_model * 4 + cfg.ffn * 4
 
-        def gemv_all():
+        def graph_time(body):
+            body()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            s2 = torch.cuda.Stream(device=dev)
+            s2.wait_stream(stream)
+            with torch.cuda.stream(s2):
+                with torch.cuda.graph(g, stream=s2):
+                    body()
+            stream.wait_stream(s2)
+            g.replay()
+            torch.cuda.synchronize()
+            return time_kernel(g.replay, 5, stream) / len(mats)
+
+        def planes_all():
             for m in mats:
                 rt.launch("QuantMatVecInt4", [a1, m.codes, m.scales, m.zeros, out1], u)
 
-        gemv_all()
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        s2 = torch.cuda.Stream(device=dev)
-        s2.wait_stream(stream)
-        with torch.cuda.stream(s2):
-            with torch.cuda.graph(g, stream=s2):
-                gemv_all()
-        stream.wait_stream(s2)
-        g.replay()
-        torch.cuda.synchronize()
-        ms = time_kernel(g.replay, 5, stream) / len(mats)
-        gbytes = mats[0].nbytes + cfg.d_model * 4 + cfg.ffn * 4
+        ms_planes = graph_time(planes_all)
+        packed = [dec.pack(m) for m in mats]
+
+        def packed_all():
+            for m in packed:
+                rt.launch("QuantMatVecInt4Packed", [a1, m.packed, out1], u)
+
+        ms = graph_time(packed_all)
+        del packed
         gemv = {"shape": "M=1 K=4096 N=11008", "bytes": gbytes, "us": ms * 1e3,
                 "gbs": gbytes / (ms * 1e-3) / 1e9, "frac": gbytes / (ms * 1e-3) / 1e9 / peak,
+                "kernel": "int4_stream_kernel on the load-time prepack (what the step runs)",
+                "reference_layout": {"us": ms_planes * 1e3, "gbs": gbytes / (ms_planes * 1e-3) / 1e9,
+                                     "frac": gbytes / (ms_planes * 1e-3) / 1e9 / peak,
+                                     "kernel": "int4_row_kernel on quant.Int4Quantize's planes"},
                 "matrices_rotated": len(mats)}
 
     # ---- CPU baseline beside it (rank 0, N = 1 only): the oracle's layer sample
@@ -680,6 +766,8 @@ def main():
                          "kernel over NVLink peer memory, or NCCL")
     ap.add_argument("--attention", action="store_true",
                     help="time the paged decode attention of config 3 on its own, f32 and f16 caches")
+    ap.add_argument("--allreduce", action="store_true",
+                    help="under torchrun: latency of one 256 KiB all-reduce, peer kernel beside NCCL")
     ap.add_argument("--moe", action="store_true",
                     help="time the expert-parallel grouped int4 FFN (config 5) instead of the decode step")
     ap.add_argument("--planes", action="store_true",
@@ -690,6 +778,8 @@ def main():
     args = ap.parse_args()
     if args.linear:
         run_linear(args)
+    elif args.allreduce:
+        run_allreduce(args)
     elif args.attention:
         run_attention(args)
     elif args.moe:

@@ -119,6 +119,26 @@ def test_full_size_against_a_binary64_product(M):
     assert_close(got[rows], wo, GEMM_TOL, "oracle rows")
 
 
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (16, 4096, 11008)])
+def test_per_element_bound_on_the_reference_layout(M, K, N):
+    """The bound the reference states for its own kernels, applied to EVERY output of the kernels
+    that read quant.Int4Quantize's planes (not only relative to the largest output):
+    |y - y_f64| <= (gamma(K) + 2^-11) * sum_k |a_k| |w_k|, gamma(K) for the f32 accumulation
+    (internal/kernels/int4_test.go:99-182), 2^-11 for the one operand rounded to f16."""
+    w, p, s, z = quantized(8, K, N)
+    a = normal(9, (M, K))
+    back = orc.int4_dequantize(p, s, z, w.size)
+    want, mag = orc.matmul_definition_f64(a, back, M, N, K)
+    x = torch.from_numpy(a).to(DEV)
+    if M == 1:
+        got = T.int4_matvec(x[0], to_int4(p, s, z, K * N)).cpu().numpy()[None, :]
+    else:
+        got = T.int4_matmul(x, to_int4(p, s, z, K * N)).cpu().numpy()
+    nu = (K - 1) * 2.0 ** -24
+    bound = (nu / (1 - nu) + 2.0 ** -11) * mag
+    assert np.all(np.abs(got - want) <= bound), float(np.max(np.abs(got - want) / mag))
+
+
 def test_device_quantizer_is_bit_identical(rng):
     n = 128 * 4000 + 77
     w = (rng.standard_normal(n) * 0.02).astype(np.float32)
