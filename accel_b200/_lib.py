@@ -62,7 +62,7 @@ class Node(C.Structure):
 
 class Plan(C.Structure):
     _fields_ = [("nodes", C.POINTER(Node)), ("n_nodes", C.c_int32), ("n_slots", C.c_int32),
-                ("collect_timings", C.c_int32), ("_pad", C.c_int32)]
+                ("collect_timings", C.c_int32), ("max_in_flight", C.c_int32)]
 
 
 class SlotBinding(C.Structure):
@@ -125,6 +125,8 @@ SYMBOLS = [
     ("ab_int4_quantize", C.c_int, [_P, C.c_size_t, _P, _P, _P]),
     ("ab_int4_nibble", C.c_uint32, [_P, C.c_size_t]),
     ("ab_int4_dequantize", C.c_int, [_P, _P, _P, C.c_size_t, _P]),
+    ("ab_int8_quantize", C.c_int, [_P, C.c_size_t, _P, _P]),
+    ("ab_int8_dequantize", C.c_int, [_P, _P, C.c_size_t, _P]),
     ("ab_f32_to_f16", C.c_uint16, [_P]),
     ("ab_f16_to_f32", None, [C.c_uint16, _P]),
     ("ab_blockpool_new", C.c_int, [C.c_int, C.c_int, C.POINTER(_P)]),

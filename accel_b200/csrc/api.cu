@@ -98,6 +98,8 @@ int sm_count()
 static const KernelEntry kKernels[] = {
     {"QuantMatVecInt4", 5, 16, launch_quant_matvec_int4},
     {"QuantMatMulInt4", 5, 16, launch_quant_matmul_int4},
+    {"QuantMatVecF32", 4, 16, launch_quant_matvec_f32},
+    {"QuantMatMulTiledF32", 4, 16, launch_quant_matmul_tiled_f32},
     {"QuantMatVecInt4Packed", 3, 16, launch_quant_matvec_int4_packed},
     {"QuantMatMulInt4Packed", 3, 16, launch_quant_matmul_int4_packed},
     {"QuantMatMulInt4PackedSplit3", 5, 32, launch_quant_matmul_int4_packed_split3},
@@ -209,9 +211,12 @@ struct ab_block {
     std::atomic<int> users{0};     // live executables that name this block (directly or by a slot)
 };
 
+namespace ab { struct Instance; }
+
 struct ab_fence {
     ab_device *dev;
     ab_exec *exec;
+    ab::Instance *inst;    // the executable's instance this submission runs on; NULL once released
     cudaEvent_t start, done;
     bool timed;
     int injected;   // a loss injected on the host
@@ -225,9 +230,20 @@ struct Node {
     std::vector<uint8_t> uniform;
     std::vector<void *> ptrs;
     std::vector<uint32_t> lens;
-    void *staging = nullptr;       // pinned payload of a host write
+    std::vector<uint8_t> payload;  // a host write's bytes as last set; copied into the instance at submit
     size_t payload_bytes = 0;
     size_t ws = 0;
+};
+// One lowering of the executable: what a submission owns while it is in flight (CompileOptions.
+// MaxInFlight, tensor/compile.go:19-27: "the plan lowers itself again into a spare graph the first
+// time a submission finds every instance busy, up to this many, each with its own transient memory").
+struct Instance {
+    void *workspace = nullptr;
+    std::vector<void *> staging;   // per node: the pinned payload of a host write (NULL otherwise)
+    cudaGraphExec_t graph = nullptr;
+    uint64_t graph_version = 0;    // the executable's version the graph was captured at
+    cudaEvent_t ev_start = nullptr, ev_done = nullptr;
+    std::atomic<int> busy{0};
 };
 static size_t elem_bytes_of(const char *kernel, int binding);
 }  // namespace ab
@@ -237,14 +253,19 @@ struct ab_exec {
     std::vector<ab::Node> nodes;
     std::vector<ab_slot_binding> slots;    // index = slot - 1
     std::vector<bool> slot_set;
-    void *workspace = nullptr;
     size_t ws_bytes = 0;
     bool timings = false;
-    std::atomic<int> in_flight{0};
+    int max_in_flight = 1;
+    std::mutex mu;                         // instances, their busy flags and the version
+    std::vector<ab::Instance *> inst;      // at least one; spares are lowered on demand
+    uint64_t version = 1;                  // bumped by rebind / set_uniform: graphs captured earlier are stale
     std::vector<ab_block *> held;          // blocks named directly by a node, counted in users
-    cudaGraphExec_t graph = nullptr;
-    bool graph_stale = true;
-    cudaEvent_t ev_start = nullptr, ev_done = nullptr;
+    int busy_count()
+    {
+        int n = 0;
+        for (auto *i : inst) n += i->busy.load();
+        return n;
+    }
 };
 
 namespace ab {
@@ -315,14 +336,44 @@ static int resolve_all(ab_exec *e)
     return AB_OK;
 }
 
-static int run_nodes(ab_exec *e, cudaStream_t s)
+static void free_instance(Instance *in)
+{
+    if (!in) return;
+    if (in->graph) cudaGraphExecDestroy(in->graph);
+    if (in->workspace) cudaFree(in->workspace);
+    for (void *p : in->staging) if (p) cudaFreeHost(p);
+    if (in->ev_start) cudaEventDestroy(in->ev_start);
+    if (in->ev_done) cudaEventDestroy(in->ev_done);
+    delete in;
+}
+
+// A lowering of the executable with transient memory of its own.
+static int new_instance(ab_exec *e, Instance **out)
+{
+    Instance *in = new (std::nothrow) Instance();
+    if (!in) return fail(AB_ERR_OOM, "executable instance: host allocation failed");
+    int rc = AB_OK;
+    if (e->ws_bytes) rc = check_cuda(cudaMalloc(&in->workspace, e->ws_bytes), "executable workspace");
+    in->staging.assign(e->nodes.size(), nullptr);
+    for (size_t n = 0; n < e->nodes.size() && !rc; n++)
+        if (e->nodes[n].op == AB_OP_HOST_WRITE)
+            rc = check_cuda(cudaHostAlloc(&in->staging[n], e->nodes[n].payload_bytes, cudaHostAllocDefault),
+                            "host-write staging");
+    if (!rc) rc = check_cuda(cudaEventCreate(&in->ev_start), "fence events");
+    if (!rc) rc = check_cuda(cudaEventCreate(&in->ev_done), "fence events");
+    if (rc) { cudaGetLastError(); free_instance(in); return rc; }
+    *out = in;
+    return AB_OK;
+}
+
+static int run_nodes(ab_exec *e, Instance *in, cudaStream_t s)
 {
     for (size_t n = 0; n < e->nodes.size(); n++) {
         Node &nd = e->nodes[n];
         if (nd.op == AB_OP_DISPATCH) {
             Launch l{s, nd.ptrs.data(), nd.lens.data(), (int)nd.ptrs.size(),
                      nd.uniform.empty() ? nullptr : nd.uniform.data(), nd.uniform.size(),
-                     e->workspace, e->ws_bytes, false, 0};
+                     in->workspace, e->ws_bytes, false, 0};
             int rc = dispatch(nd.kernel.c_str(), l);
             if (rc) return rc;
         } else if (nd.op == AB_OP_COPY) {
@@ -331,7 +382,7 @@ static int run_nodes(ab_exec *e, cudaStream_t s)
             if (rc) return rc;
         } else if (nd.op == AB_OP_HOST_WRITE) {
             size_t bytes = std::min(nd.payload_bytes, (size_t)nd.bind[0].size);
-            int rc = check_cuda(cudaMemcpyAsync(nd.ptrs[0], nd.staging, bytes, cudaMemcpyHostToDevice, s), "host-write node");
+            int rc = check_cuda(cudaMemcpyAsync(nd.ptrs[0], in->staging[n], bytes, cudaMemcpyHostToDevice, s), "host-write node");
             if (rc) return rc;
         }
     }
@@ -570,9 +621,10 @@ int ab_compile(ab_device *d, const ab_plan *plan, ab_exec **out)
     if (!e) return fail(AB_ERR_OOM, "ab_compile: host allocation failed");
     e->dev = d;
     e->timings = plan->collect_timings != 0;
+    e->max_in_flight = plan->max_in_flight > 1 ? plan->max_in_flight : 1;
     e->slots.resize((size_t)plan->n_slots);
     e->slot_set.assign((size_t)plan->n_slots, false);
-    auto bail = [&](int code) { for (auto &nd : e->nodes) if (nd.staging) cudaFreeHost(nd.staging); delete e; return code; };
+    auto bail = [&](int code) { for (auto *in : e->inst) free_instance(in); delete e; return code; };
 
     size_t ws_max = 0;
     for (int n = 0; n < plan->n_nodes; n++) {
@@ -627,21 +679,18 @@ int ab_compile(ab_device *d, const ab_plan *plan, ab_exec **out)
             if (src.n_bindings != 1 || !src.payload || src.payload_bytes == 0)
                 return bail(fail(AB_ERR_INVALID, "node %d: a host write has one destination and a payload", n));
             nd.payload_bytes = (size_t)src.payload_bytes;
-            rc = check_cuda(cudaHostAlloc(&nd.staging, nd.payload_bytes, cudaHostAllocDefault), "host-write staging");
-            if (rc) return bail(rc);
-            memcpy(nd.staging, src.payload, nd.payload_bytes);
+            nd.payload.assign(static_cast<const uint8_t *>(src.payload),
+                              static_cast<const uint8_t *>(src.payload) + nd.payload_bytes);
         } else {
             return bail(fail(AB_ERR_UNSUPPORTED, "node %d: op %d; this is a compute-only backend", n, src.op));
         }
         e->nodes.push_back(std::move(nd));
     }
-    if (ws_max) {
-        rc = check_cuda(cudaMalloc(&e->workspace, ws_max), "executable workspace");
-        if (rc) { cudaGetLastError(); return bail(rc); }
-        e->ws_bytes = ws_max;
-    }
-    cudaEventCreate(&e->ev_start);
-    cudaEventCreate(&e->ev_done);
+    e->ws_bytes = ws_max;
+    Instance *first = nullptr;
+    rc = new_instance(e, &first);
+    if (rc) return bail(rc);
+    e->inst.push_back(first);
     for (auto &nd : e->nodes)
         for (auto &op : nd.bind)
             if (op.block) { op.block->users.fetch_add(1); e->held.push_back(op.block); }
@@ -653,7 +702,10 @@ int ab_compile(ab_device *d, const ab_plan *plan, ab_exec **out)
 int ab_exec_rebind(ab_exec *e, const ab_slot_binding *b, int n)
 {
     if (!e || (n && !b) || n < 0) return fail(AB_ERR_INVALID, "ab_exec_rebind: NULL argument");
-    if (e->in_flight.load()) return fail(AB_ERR_BUSY, "ab_exec_rebind: a submission is in flight");
+    std::lock_guard<std::mutex> lk(e->mu);
+    // one submission at a time: the executable is busy until its fence is waited for.  Several in
+    // flight: a rebind applies to the submissions that follow (those in flight own their lowering).
+    if (e->max_in_flight == 1 && e->busy_count()) return fail(AB_ERR_BUSY, "ab_exec_rebind: a submission is in flight");
     for (int i = 0; i < n; i++) {       // validate everything first: all or nothing
         if (b[i].slot == 0 || b[i].slot > e->slots.size())
             return fail(AB_ERR_INVALID, "ab_exec_rebind: slot %u of %zu", b[i].slot, e->slots.size());
@@ -676,34 +728,36 @@ int ab_exec_rebind(ab_exec *e, const ab_slot_binding *b, int n)
         saved[at] = b[i];                    // a slot named twice in one call: count the last one
         saved_set[at] = true;
     }
-    e->graph_stale = true;
+    e->version++;
     return AB_OK;
 }
 
 int ab_exec_set_uniform(ab_exec *e, int node, int index, const void *bytes, size_t n)
 {
     if (!e || !bytes) return fail(AB_ERR_INVALID, "ab_exec_set_uniform: NULL argument");
-    if (e->in_flight.load()) return fail(AB_ERR_BUSY, "ab_exec_set_uniform: a submission is in flight");
+    std::lock_guard<std::mutex> lk(e->mu);
+    if (e->max_in_flight == 1 && e->busy_count()) return fail(AB_ERR_BUSY, "ab_exec_set_uniform: a submission is in flight");
     if (node < 0 || node >= (int)e->nodes.size() || e->nodes[node].op != AB_OP_DISPATCH || index != 0)
         return fail(AB_ERR_INVALID, "ab_exec_set_uniform: node %d block %d", node, index);
     Node &nd = e->nodes[node];
     if (n != nd.uniform.size())
         return fail(AB_ERR_INVALID, "ab_exec_set_uniform: node %d's block is %zu bytes, given %zu", node, nd.uniform.size(), n);
     memcpy(nd.uniform.data(), bytes, n);
-    e->graph_stale = true;
+    e->version++;
     return AB_OK;
 }
 
 int ab_exec_set_payload(ab_exec *e, int node, const void *bytes, size_t n)
 {
     if (!e || !bytes) return fail(AB_ERR_INVALID, "ab_exec_set_payload: NULL argument");
-    if (e->in_flight.load()) return fail(AB_ERR_BUSY, "ab_exec_set_payload: a submission is in flight");
+    std::lock_guard<std::mutex> lk(e->mu);
+    if (e->max_in_flight == 1 && e->busy_count()) return fail(AB_ERR_BUSY, "ab_exec_set_payload: a submission is in flight");
     if (node < 0 || node >= (int)e->nodes.size() || e->nodes[node].op != AB_OP_HOST_WRITE)
         return fail(AB_ERR_INVALID, "ab_exec_set_payload: node %d is not a host write", node);
     Node &nd = e->nodes[node];
     if (n != nd.payload_bytes)
         return fail(AB_ERR_INVALID, "ab_exec_set_payload: node %d's payload is %zu bytes, given %zu", node, nd.payload_bytes, n);
-    memcpy(nd.staging, bytes, n);      // the staging buffer's address is what a graph replays
+    memcpy(nd.payload.data(), bytes, n);      // copied into the submission's own staging buffer at submit
     return AB_OK;
 }
 
@@ -713,11 +767,22 @@ int ab_exec_submit(ab_exec *e, ab_fence **out)
     ab_device *d = e->dev;
     int rc = set_device(d);
     if (rc) return rc;
-    int expected = 0;
-    if (!e->in_flight.compare_exchange_strong(expected, 1))
-        return fail(AB_ERR_BUSY, "ab_exec_submit: the previous submission has not been waited for; "
-                    "one submission is in flight per executable");
-    auto release = [&](int code) { e->in_flight.store(0); return note_loss(d, code); };
+    std::lock_guard<std::mutex> lk(e->mu);
+    // an instance nobody is using; else a spare lowered now, up to max_in_flight of them
+    Instance *in = nullptr;
+    for (auto *cand : e->inst) if (!cand->busy.load()) { in = cand; break; }
+    if (!in) {
+        if ((int)e->inst.size() >= e->max_in_flight)
+            return fail(AB_ERR_BUSY, e->max_in_flight == 1
+                        ? "ab_exec_submit: the previous submission has not been waited for; one submission is in "
+                          "flight per executable (compile with max_in_flight for more)"
+                        : "ab_exec_submit: all %d instances of the executable are in flight", e->max_in_flight);
+        rc = new_instance(e, &in);
+        if (rc) return rc;
+        e->inst.push_back(in);
+    }
+    in->busy.store(1);
+    auto release = [&](int code) { in->busy.store(0); return note_loss(d, code); };
     if (!std::all_of(e->slot_set.begin(), e->slot_set.end(), [](bool x) { return x; }))
         return release(fail(AB_ERR_INVALID, "ab_exec_submit: a slot is unbound"));
     for (auto &nd : e->nodes)
@@ -726,32 +791,36 @@ int ab_exec_submit(ab_exec *e, ab_fence **out)
     int seq = d->submissions.fetch_add(1) + 1;
     ab_fence *f = new (std::nothrow) ab_fence();
     if (!f) return release(fail(AB_ERR_OOM, "ab_exec_submit: host allocation failed"));
-    f->dev = d; f->exec = e; f->timed = e->timings; f->start = e->ev_start; f->done = e->ev_done; f->injected = 0;
+    f->dev = d; f->exec = e; f->inst = in; f->timed = e->timings; f->start = in->ev_start; f->done = in->ev_done;
+    f->injected = 0;
     if (d->lose_at > 0 && seq >= d->lose_at) {      // host-side injection: nothing touches the GPU
         d->lost.store(1);
         f->injected = 1;
         *out = f;
         return AB_OK;
     }
+    // this submission's payloads: the instance is idle, so its staging buffers are free to write
+    for (size_t n = 0; n < e->nodes.size(); n++)
+        if (e->nodes[n].op == AB_OP_HOST_WRITE) memcpy(in->staging[n], e->nodes[n].payload.data(), e->nodes[n].payload_bytes);
     if (f->timed) cudaEventRecord(f->start, d->stream);
     if (d->use_graphs) {
-        if (e->graph_stale || !e->graph) {
-            if (e->graph) { cudaGraphExecDestroy(e->graph); e->graph = nullptr; }
+        if (in->graph_version != e->version || !in->graph) {
+            if (in->graph) { cudaGraphExecDestroy(in->graph); in->graph = nullptr; }
             cudaGraph_t g = nullptr;
             rc = check_cuda(cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal), "graph capture");
             if (!rc) {
-                int rn = run_nodes(e, d->stream);
+                int rn = run_nodes(e, in, d->stream);
                 cudaError_t ce = cudaStreamEndCapture(d->stream, &g);
                 rc = rn ? rn : check_cuda(ce, "graph capture");
             }
-            if (!rc) rc = check_cuda(cudaGraphInstantiate(&e->graph, g, 0), "graph instantiate");
+            if (!rc) rc = check_cuda(cudaGraphInstantiate(&in->graph, g, 0), "graph instantiate");
             if (g) cudaGraphDestroy(g);
             if (rc) { delete f; return release(rc); }
-            e->graph_stale = false;
+            in->graph_version = e->version;
         }
-        rc = check_cuda(cudaGraphLaunch(e->graph, d->stream), "graph launch");
+        rc = check_cuda(cudaGraphLaunch(in->graph, d->stream), "graph launch");
     } else {
-        rc = run_nodes(e, d->stream);
+        rc = run_nodes(e, in, d->stream);
     }
     if (rc) { delete f; return release(rc); }
     rc = check_cuda(cudaEventRecord(f->done, d->stream), "fence");
@@ -760,13 +829,20 @@ int ab_exec_submit(ab_exec *e, ab_fence **out)
     return AB_OK;
 }
 
+// The submission is over for the host: its instance takes the next one.
+static void fence_release(ab_fence *f)
+{
+    if (f->inst) f->inst->busy.store(0);
+    f->inst = nullptr;
+    f->exec = nullptr;
+}
+
 int ab_fence_wait(ab_fence *f)
 {
     if (!f) return fail(AB_ERR_INVALID, "ab_fence_wait: fence is NULL");
-    if (f->injected) { if (f->exec) f->exec->in_flight.store(0); f->exec = nullptr; return fail(AB_ERR_DEVICE_LOST, "device lost (injected at this submission)"); }
+    if (f->injected) { fence_release(f); return fail(AB_ERR_DEVICE_LOST, "device lost (injected at this submission)"); }
     int rc = check_cuda(cudaEventSynchronize(f->done), "ab_fence_wait");   // needs no current context
-    if (f->exec) f->exec->in_flight.store(0);
-    f->exec = nullptr;
+    fence_release(f);
     // every outstanding fence reports a loss once the device is lost (internal/driver/plan.go:374-391)
     if (rc == AB_OK && f->dev && f->dev->lost.load())
         return fail(AB_ERR_DEVICE_LOST, "ab_fence_wait: the device was lost");
@@ -779,7 +855,7 @@ int ab_fence_done(ab_fence *f)
     if (f->dev && f->dev->lost.load() && !f->injected)
         return fail(AB_ERR_DEVICE_LOST, "ab_fence_done: the device was lost");
     // a caller may learn of completion here and never wait: the executable is free again
-    auto finished = [&]() { if (f->exec) f->exec->in_flight.store(0); f->exec = nullptr; return 1; };
+    auto finished = [&]() { fence_release(f); return 1; };
     if (f->injected) return finished();
     cudaError_t e = cudaEventQuery(f->done);
     if (e == cudaSuccess) return finished();
@@ -798,9 +874,9 @@ uint64_t ab_fence_elapsed_ns(ab_fence *f)
 void ab_fence_free(ab_fence *f)
 {
     if (!f) return;
-    if (f->exec) {                          // freed unwaited: wait here so the executable is not stuck busy
+    if (f->inst) {                          // freed unwaited: wait here so the instance is not stuck busy
         if (!f->injected) cudaEventSynchronize(f->done);
-        f->exec->in_flight.store(0);
+        fence_release(f);
     }
     delete f;
 }
@@ -811,12 +887,11 @@ int ab_exec_close(ab_exec *e)
     ab_device *d = e->dev;
     if (!d->lost.load() && cudaSetDevice(d->ordinal) == cudaSuccess) {
         cudaStreamSynchronize(d->stream);
-        if (e->graph) cudaGraphExecDestroy(e->graph);
-        if (e->workspace) cudaFree(e->workspace);
-        for (auto &nd : e->nodes) if (nd.staging) cudaFreeHost(nd.staging);
-        if (e->ev_start) cudaEventDestroy(e->ev_start);
-        if (e->ev_done) cudaEventDestroy(e->ev_done);
+        for (auto *in : e->inst) free_instance(in);
+    } else {
+        for (auto *in : e->inst) delete in;
     }
+    e->inst.clear();
     for (ab_block *blk : e->held) blk->users.fetch_sub(1);
     for (size_t i = 0; i < e->slots.size(); i++)
         if (e->slot_set[i] && e->slots[i].block) e->slots[i].block->users.fetch_sub(1);
@@ -878,6 +953,37 @@ int ab_int4_dequantize(const uint32_t *packed, const uint16_t *scales, const uin
         const float s = f16_bits_to_f32(scales[i / 128]), z = f16_bits_to_f32(zeros[i / 128]);
         out[i] = s == 0.f ? z : ((float)ab_int4_nibble(packed, i) - z) * s;
     }
+    return AB_OK;
+}
+
+// quant.Int8Quantize / Int8Dequantize (quant/quant.go:60-134): one f16 scale per 32 weights, quants
+// in [-127, 127], quantized against the scale as the kernel reads it back
+int ab_int8_quantize(const float *w, size_t n, int8_t *quants, uint16_t *scales)
+{
+    if (n && (!w || !quants || !scales)) return fail(AB_ERR_INVALID, "ab_int8_quantize: NULL argument");
+    const size_t blocks = (n + 31) / 32;
+    for (size_t b = 0; b < blocks; b++) {
+        const size_t lo = b * 32, hi = std::min(lo + 32, n);
+        float peak = 0.f;
+        for (size_t i = lo; i < hi; i++) peak = std::max(peak, std::fabs(w[i]));
+        for (size_t i = lo; i < hi; i++) quants[i] = 0;
+        if (peak == 0.f) { scales[b] = f32_to_f16_ref(0.f); continue; }
+        scales[b] = f32_to_f16_ref(peak / 127.0f);
+        const float s16 = f16_bits_to_f32(scales[b]);
+        if (s16 == 0.f) continue;                       // the scale underflowed f16: zeros reconstruct
+        for (size_t i = lo; i < hi; i++) {
+            double q = nearbyint((double)w[i] / (double)s16);
+            q = q > 127.0 ? 127.0 : (q < -127.0 ? -127.0 : q);
+            quants[i] = (int8_t)q;
+        }
+    }
+    return AB_OK;
+}
+
+int ab_int8_dequantize(const int8_t *quants, const uint16_t *scales, size_t n, float *out)
+{
+    if (n && (!quants || !scales || !out)) return fail(AB_ERR_INVALID, "ab_int8_dequantize: NULL argument");
+    for (size_t i = 0; i < n; i++) out[i] = (float)quants[i] * f16_bits_to_f32(scales[i / 32]);
     return AB_OK;
 }
 

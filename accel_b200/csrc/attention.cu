@@ -27,7 +27,7 @@ namespace ab {
 
 static constexpr int kWarps = 4;
 static constexpr int kAttnThreads = kWarps * 32;
-static constexpr int kPartition = 256;      // positions per context partition
+static constexpr int kPartition = 256;      // positions per context partition when the grid fills the device
 static constexpr int kPosUnroll = 4;
 static constexpr float kLog2e = 1.4426950408889634f;
 static constexpr float kNegBig = -3.0e38f;
@@ -43,6 +43,7 @@ struct AttnParams {
     float2 *part_ml;    // [rows][qH][parts]
     uint32_t rows;      // sequences (batched), tokens (ragged), 1 otherwise
     uint32_t batch, q_heads, kv_heads, head_dim, block, max_pages, parts;
+    uint32_t psize;     // positions per context partition: 256, or 128 / 64 where that many would not fill the SMs
     uint32_t capacity;  // positions the page table (or the contiguous cache) can address
     float scale_log2;   // Scale * log2(e)
     int mode;
@@ -117,7 +118,7 @@ attn_partition_kernel(const AttnParams p)
     const bool lane_on = (uint32_t)lane * 4 < D;
 
     const RowView rv = row_view(p, row);
-    const uint32_t begin = part * kPartition;
+    const uint32_t begin = part * p.psize;
     if (rv.zero) {
         if (part == 0) {
             for (uint32_t i = threadIdx.x; i < G * D; i += kAttnThreads)
@@ -126,7 +127,7 @@ attn_partition_kernel(const AttnParams p)
         return;
     }
     if (begin >= rv.len && !(part == 0)) return;     // partition 0 always reports (len 0 -> NaN)
-    const uint32_t end = min(rv.len, begin + kPartition);
+    const uint32_t end = min(rv.len, begin + p.psize);
 
     const T *kc = reinterpret_cast<const T *>(p.k);
     const T *vc = reinterpret_cast<const T *>(p.v);
@@ -290,7 +291,7 @@ attn_partition_gqa_kernel(const AttnParams p)
     const bool lane_on = (uint32_t)sl * 8 < D;
 
     const RowView rv = row_view(p, row);
-    const uint32_t begin = part * kPartition;
+    const uint32_t begin = part * p.psize;
     if (rv.zero) {
         if (part == 0) {
             for (uint32_t i = threadIdx.x; i < G * D; i += kAttnThreads)
@@ -299,7 +300,7 @@ attn_partition_gqa_kernel(const AttnParams p)
         return;
     }
     if (begin >= rv.len && !(part == 0)) return;     // partition 0 always reports (len 0 -> NaN)
-    const uint32_t end = min(rv.len, begin + kPartition);
+    const uint32_t end = min(rv.len, begin + p.psize);
 
     const T *kc = reinterpret_cast<const T *>(p.k);
     const T *vc = reinterpret_cast<const T *>(p.v);
@@ -448,7 +449,7 @@ __global__ void attn_combine_kernel(const AttnParams p)
     const uint32_t h = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
     const RowView rv = row_view(p, row);
     if (rv.zero || d >= p.head_dim) return;
-    uint32_t nparts = (rv.len + kPartition - 1) / kPartition;
+    uint32_t nparts = (rv.len + p.psize - 1) / p.psize;
     if (nparts == 0) nparts = 1;
     const size_t qrow = (size_t)row * p.q_heads + h;
     float mx = kNegBig;
@@ -474,7 +475,19 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
                     "128", name, p.head_dim);
     if (p.block == 0)
         return fail(AB_ERR_INVALID, "%s: a page table addresses blocks, and Block is 0", name);
-    p.parts = (p.capacity + kPartition - 1) / kPartition;
+    // Positions per partition: 256 where that already gives every SM its eight CTAs; a small grid (a
+    // tensor-parallel shard's few KV heads, a short batch) takes 128 or 64 so that the K/V stream is
+    // spread over all SMs (the partial results grow by the same factor and stay small).
+    {
+        const uint32_t group_w = p.q_heads / p.kv_heads;
+        const bool grouped = group_w == 2 || group_w == 4 || group_w == 8;
+        const uint64_t per_part = (uint64_t)(grouped ? p.kv_heads : p.q_heads) * p.rows;
+        const uint64_t slots = 8ull * (uint64_t)sm_count();
+        p.psize = 64;
+        for (uint32_t ps = kPartition; ps >= 128; ps /= 2)
+            if ((uint64_t)((p.capacity + ps - 1) / ps) * per_part >= slots) { p.psize = ps; break; }
+    }
+    p.parts = (p.capacity + p.psize - 1) / p.psize;
     if (p.parts == 0) p.parts = 1;
     const size_t o_bytes = align_up((size_t)p.rows * p.q_heads * p.parts * p.head_dim * 4, 256);
     const size_t ml_bytes = (size_t)p.rows * p.q_heads * p.parts * sizeof(float2);
@@ -529,7 +542,7 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
         if (lerr != cudaSuccess) return check_cuda(lerr, name);
     }
     note_selection("%s: split-K decode, %u partition(s) of %d positions, %u query head(s) sharing "
-                   "each K/V read, %u row(s), %s per position", name, p.parts, kPartition, group, p.rows,
+                   "each K/V read, %u row(s), %s per position", name, p.parts, (int)p.psize, group, p.rows,
                    (gqa || (G == 1 && half_rows)) ? "half a warp" : "a warp");
     return check_cuda(cudaGetLastError(), name);
 }

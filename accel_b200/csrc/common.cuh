@@ -111,6 +111,13 @@ size_t int4_stream_workspace(uint32_t M);
 int run_int4_stream(cudaStream_t stream, const float *a, const float *amax, const unsigned char *packed, float *out,
                     uint32_t M, uint32_t N, uint32_t K, uint32_t ldo, void *scratch, bool dependent);
 int int4_stream_error_flag();
+// the batch int4 kernel over the same prepacked weights: 128-row tiles on tcgen05 (int4_gemm.cu);
+// mode 0 plain, 1 three column ranges, 2 SwiGLU over (gate, up) pairs of groups
+size_t int4_gemm_workspace(uint32_t M, uint32_t K);
+int run_int4_gemm_mode(cudaStream_t stream, const float *a, const unsigned char *packed, int mode, float *out0,
+                       float *out1, float *out2, uint32_t n1, uint32_t n2, uint32_t M, uint32_t N, uint32_t K,
+                       uint32_t ld0, void *scratch);
+int int4_gemm_error_flag();
 int launch_quant_matvec_int4_packed(Launch &);
 int launch_quant_matmul_int4_packed(Launch &);
 int launch_quant_matmul_int4_packed_split3(Launch &);
@@ -118,6 +125,8 @@ int launch_quant_matmul_int4_packed_swiglu(Launch &);
 
 // launchers, one per reference kernel name (defined beside their kernels)
 int launch_quant_matvec_int4(Launch &);
+int launch_quant_matvec_f32(Launch &);
+int launch_quant_matmul_tiled_f32(Launch &);
 int launch_quant_matmul_int4(Launch &);
 int launch_attention_decode(Launch &);
 int launch_attention_decode_f16(Launch &);

@@ -43,7 +43,7 @@
 // there is no CTA-wide barrier in the loop.  K splits of a column group form a thread-block
 // cluster: every CTA stores its partial rows into the shared memory of the CTA that owns the row
 // and arrives on that CTA's mbarrier; the owner adds the splits in split order (deterministic, no
-// workspace, no cluster-wide barrier at the end).  Every wait is bounded: one that runs out sets g_stream_error, the CTA skips its
+// workspace, no cluster-wide barrier at the end).  Every wait is bounded: one that runs out sets g_sm100_error, the CTA skips its
 // remaining work, frees its TMEM and returns.
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
@@ -51,6 +51,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -58,15 +59,9 @@ namespace ab {
 
 static constexpr int kSxThreads = 320;
 static constexpr int kSxExpanders = 256;
-static constexpr uint32_t kSxChunkK = 64;
-static constexpr uint32_t kSxCodeBytes = 4096;
-static constexpr uint32_t kSxChunkBytes = 4352;   // codes + 64 scales + 64 zeros
 static constexpr int kSxNC = 6;                   // ring stages in flight from global memory
 static constexpr int kSxNA = 3;                   // A (TMEM) and B (shared) stages
 __host__ __device__ constexpr uint32_t sx_tmem_cols(int G) { return G == 1 ? 128u : 256u; }   // per group: D (32) + 3 x 32
-static constexpr long long kSxWaitCycles = 1ll << 31;      // about a second
-
-__device__ int g_stream_error;                    // nonzero: a bounded wait ran out
 
 #ifdef SX_TRACE
 // cycle stamps and per-phase cycle sums of CTA (0,0), for tuning builds only
@@ -83,90 +78,6 @@ __device__ long long g_sx_trace[64];
 #define SX_NOW() 0ll
 #define SX_DECL() do { } while (0)
 #endif
-
-__device__ __forceinline__ uint32_t sx_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void sx_bar_init(uint64_t *bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sx_smem(bar)), "r"(count));
-}
-__device__ __forceinline__ void sx_bar_arrive(uint64_t *bar)
-{
-    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(sx_smem(bar)) : "memory");
-}
-__device__ __forceinline__ void sx_bar_expect_tx(uint64_t *bar, uint32_t bytes)
-{
-    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}"
-                 ::"r"(sx_smem(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ uint32_t sx_bar_try(uint32_t addr, uint32_t parity)
-{
-    uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    return done;
-}
-// Bounded wait for the phase of the given parity; false (and the error flag) when it runs out.
-__device__ __noinline__ bool sx_bar_wait_slow(uint32_t addr, uint32_t parity)
-{
-    const long long t0 = clock64();
-    for (;;) {
-        if (sx_bar_try(addr, parity)) return true;
-        if (clock64() - t0 > kSxWaitCycles) break;
-    }
-    atomicExch(&g_stream_error, 1);
-    return false;
-}
-__device__ __forceinline__ bool sx_bar_wait(uint64_t *bar, uint32_t parity)
-{
-    const uint32_t addr = sx_smem(bar);
-    if (sx_bar_try(addr, parity)) return true;
-    if (sx_bar_try(addr, parity)) return true;
-    return sx_bar_wait_slow(addr, parity);
-}
-__device__ __forceinline__ void sx_bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(sx_smem(dst)), "l"(src), "r"(bytes), "r"(sx_smem(bar)) : "memory");
-}
-__device__ __forceinline__ uint64_t sx_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo)
-{   // K-major, no swizzle: start address, K-direction and MN-direction core-matrix strides, all >> 4
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) |
-           ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
-}
-// D[tmem_d] (+)= A[tmem_a] * B[smem]: the A operand is read from tensor memory
-__device__ __forceinline__ void sx_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate)
-{
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void sx_commit(uint64_t *bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(sx_smem(bar)) : "memory");
-}
-__device__ __forceinline__ void sx_tmem_st16(uint32_t taddr, const uint32_t (&r)[16])
-{
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-                   "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
-                   "r"(r[14]), "r"(r[15]) : "memory");
-}
-__device__ __forceinline__ void sx_tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
-                   "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
-                   "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 // acc += f16(lo of b) * f16(lo of z) + f16(hi of b) * f16(hi of z): exact products, f32 sums
 __device__ __forceinline__ void sx_fma_pairs(float &acc, uint32_t b, uint32_t z)
@@ -185,34 +96,6 @@ __host__ __device__ constexpr size_t sx_smem_bytes(int G)
 {
     return (size_t)kSxNC * G * kSxChunkBytes + (size_t)kSxNA * G * kSxBStage + (size_t)G * (kSxRecvRows + kSxNB) * 128 * 4 +
            (size_t)(G + 1) * kSxNB * 4 + (2 * kSxNC + 2 * kSxNA + 2) * 8 + 16 + 128 + 256;
-}
-
-// The exponent that scales a row: floor(log2(largest magnitude)), clamped; 0 for an all-zero row.
-// Bit patterns of non-negative floats order like the floats; Inf and NaN clamp to the top.
-__device__ __forceinline__ int sx_row_exponent(uint32_t amax_bits)
-{
-    int ea = amax_bits ? (int)((amax_bits >> 23) & 0xffu) - 127 : 0;
-    return ea < -80 ? -80 : (ea > 80 ? 80 : ea);
-}
-
-// Where the columns go.  Plain: out[m][ld0 .. ].  Split: the columns from group g1 on go to out1 and
-// those from group g2 on to out2, each a contiguous matrix of its own (the fused q | k | v product).
-// SwiGLU: tiles are (gate, up) pairs of groups and out[m][tile * 128 + t] = gate / (1 + exp(-gate)) * up
-// (internal/kernels/elementwise.go:85), the arithmetic of the SwiGLU kernel on the two sums.
-struct SxEpilogue {
-    float *out0, *out1, *out2;
-    uint32_t g1, g2;              // 0xffffffff: no such destination
-    uint32_t ld0, ld1, ld2;
-    uint32_t swiglu;
-};
-
-__device__ __forceinline__ void sx_store(const SxEpilogue &e, uint32_t m, uint32_t g, uint32_t t, float v)
-{
-    float *base = e.out0;
-    uint32_t ld = e.ld0, gb = 0;
-    if (g >= e.g2) { base = e.out2; ld = e.ld2; gb = e.g2; }
-    else if (g >= e.g1) { base = e.out1; ld = e.ld1; gb = e.g1; }
-    base[(size_t)m * ld + (size_t)(g - gb) * 128 + t] = v;
 }
 
 // grid = (ceil(N / 128 / G), K splits), cluster = (1, splits, 1); a CTA owns G adjacent column
@@ -617,7 +500,7 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
                         if (d) { got = true; break; }
                         if (clock64() - t0 > kSxWaitCycles) break;
                     }
-                    if (!got) { atomicExch(&g_stream_error, 1); *s_abort = 1; }
+                    if (!got) { atomicExch(&g_sm100_error, 1); *s_abort = 1; }
                     if (tid == 0) SX_STAMP(8);
                     if (__all_sync(0xffffffffu, got)) {
                         for (uint32_t m = rank, j = 0; m < M; m += splits, j++) {
@@ -753,8 +636,6 @@ int4_prepack_kernel(const uint32_t *__restrict__ codes, const uint16_t *__restri
         reinterpret_cast<__half *>(dst + kSxCodeBytes + 128)[tid] = __float2half_rn(zn);
     }
 }
-
-static size_t sx_header_bytes(uint32_t N) { return align_up((size_t)(N / 128) * 4, 256); }
 
 bool int4_stream_ok(uint32_t M, uint32_t N, uint32_t K)
 {
@@ -978,7 +859,7 @@ int run_int4_stream(cudaStream_t stream, const float *a, const float *amax, cons
 int int4_stream_error_flag()
 {
     int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_stream_error, sizeof v) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (cudaMemcpyFromSymbol(&v, g_sm100_error, sizeof v) != cudaSuccess) { cudaGetLastError(); return -1; }
     return v;
 }
 
@@ -992,12 +873,21 @@ static bool sx_pdl()
     return pdl;
 }
 
+// From how many activation rows the tile kernel (int4_gemm.cu: weights dequantised once per CTA,
+// 128 rows per tile) takes over from passes of 16 rows of the decode kernel.
+static constexpr uint32_t kPackedTileFromRows = 17;
+static bool packed_tiles(uint32_t M) { return M >= kPackedTileFromRows; }
+static size_t packed_workspace(uint32_t M, uint32_t K)
+{
+    return packed_tiles(M) ? int4_gemm_workspace(M, K) : int4_stream_workspace(M);
+}
+
 static int launch_packed(Launch &l, const char *name, uint32_t M, uint32_t N, uint32_t K)
 {
     if (!int4_stream_ok(M, N, K))
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u; the prepacked form needs N a multiple of 128 and K a "
                     "multiple of 4", name, M, N, K);
-    const size_t ws = int4_stream_workspace(M);
+    const size_t ws = packed_workspace(M, K);
     if (l.query_ws) { l.ws_need = ws; return AB_OK; }
     const size_t need = int4_stream_packed_bytes(N, K);
     if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1] * 4 < need || l.len[2] < (uint64_t)M * N)
@@ -1006,6 +896,9 @@ static int launch_packed(Launch &l, const char *name, uint32_t M, uint32_t N, ui
                     (unsigned long long)M * N, l.len[0], l.len[1], l.len[2]);
     if (ws > l.ws_bytes || (ws && !l.ws))
         return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, ws, l.ws_bytes);
+    if (packed_tiles(M))
+        return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1), kSxPlain,
+                                  ptr<float>(l, 2), nullptr, nullptr, 0, 0, M, N, K, N, l.ws);
     return run_int4_stream(l.stream, ptr<const float>(l, 0), nullptr, ptr<const unsigned char>(l, 1), ptr<float>(l, 2),
                            M, N, K, N, l.ws, sx_pdl());
 }
@@ -1019,7 +912,7 @@ int launch_quant_matmul_int4_packed_split3(Launch &l)
     if (!int4_stream_ok(M, N, K) || N1 % 128 || N2 % 128 || N1 == 0 || N2 == 0 || (uint64_t)N1 + N2 >= N)
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u N1=%u N2=%u; N, N1 and N2 are multiples of 128 with "
                     "N1 + N2 < N, K a multiple of 4", name, M, N, K, N1, N2);
-    const size_t ws = int4_stream_workspace(M);
+    const size_t ws = packed_workspace(M, K);
     if (l.query_ws) { l.ws_need = ws; return AB_OK; }
     const uint32_t N3 = N - N1 - N2;
     if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1] * 4 < int4_stream_packed_bytes(N, K) ||
@@ -1028,6 +921,9 @@ int launch_quant_matmul_int4_packed_split3(Launch &l)
                     name, M, N, K, N1, N2, l.len[0], l.len[1], l.len[2], l.len[3], l.len[4]);
     if (ws > l.ws_bytes || (ws && !l.ws))
         return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, ws, l.ws_bytes);
+    if (packed_tiles(M))
+        return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1), kSxSplit3,
+                                  ptr<float>(l, 2), ptr<float>(l, 3), ptr<float>(l, 4), N1, N1 + N2, M, N, K, N1, l.ws);
     return run_int4_stream_mode(l.stream, ptr<const float>(l, 0), nullptr, ptr<const unsigned char>(l, 1), kSxSplit3,
                                 ptr<float>(l, 2), ptr<float>(l, 3), ptr<float>(l, 4), N1, N1 + N2, M, N, K, N1, l.ws,
                                 sx_pdl());
@@ -1042,13 +938,16 @@ int launch_quant_matmul_int4_packed_swiglu(Launch &l)
     if (!int4_stream_ok(M, N, K) || N % 256)
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u; N is a multiple of 256 (gate and up groups in pairs), K a "
                     "multiple of 4", name, M, N, K);
-    const size_t ws = int4_stream_workspace(M);
+    const size_t ws = packed_workspace(M, K);
     if (l.query_ws) { l.ws_need = ws; return AB_OK; }
     if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1] * 4 < int4_stream_packed_bytes(N, K) || l.len[2] < (uint64_t)M * (N / 2))
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u; a[%u] packed[%u words] out[%u]", name, M, N, K, l.len[0],
                     l.len[1], l.len[2]);
     if (ws > l.ws_bytes || (ws && !l.ws))
         return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, ws, l.ws_bytes);
+    if (packed_tiles(M))
+        return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1), kSxSwiGLU,
+                                  ptr<float>(l, 2), nullptr, nullptr, 0, 0, M, N, K, N / 2, l.ws);
     return run_int4_stream_mode(l.stream, ptr<const float>(l, 0), nullptr, ptr<const unsigned char>(l, 1), kSxSwiGLU,
                                 ptr<float>(l, 2), nullptr, nullptr, 0, 0, M, N, K, N / 2, l.ws, sx_pdl());
 }
@@ -1085,7 +984,8 @@ extern "C" AB_API int ab_int4_prepack(void *stream, const uint32_t *codes, const
 
 extern "C" AB_API int ab_int4_stream_error(void)
 {
-    const int v = ab::int4_stream_error_flag();
-    if (v > 0) return ab::fail(AB_ERR_TIMEOUT, "the int4 stream kernel gave up a bounded wait");
+    int v = ab::int4_stream_error_flag();
+    if (v == 0) v = ab::int4_gemm_error_flag();
+    if (v > 0) return ab::fail(AB_ERR_TIMEOUT, "an int4 kernel over the prepacked stream gave up a bounded wait");
     return v < 0 ? AB_ERR_CUDA : AB_OK;
 }

@@ -179,8 +179,9 @@ class Device:
         return _lib.lib().ab_supports_kernel(self._h, name.encode(), None) == _lib.AB_OK
 
     def compile(self, nodes: Sequence[Union[Dispatch, Copy, HostWrite]], n_slots: int = 0,
-                collect_timings: bool = False) -> Executable:
-        """GraphCompiler.Compile: validates everything knowable now."""
+                collect_timings: bool = False, max_in_flight: int = 0) -> Executable:
+        """GraphCompiler.Compile: validates everything knowable now.  max_in_flight is
+        CompileOptions.MaxInFlight (tensor/compile.go:19-27): zero means one submission at a time."""
         keep: List[object] = []
         arr = (_lib.Node * len(nodes))()
 
@@ -218,7 +219,7 @@ class Device:
                 arr[i].payload_bytes = len(nd.payload)
             else:
                 raise TypeError(f"node {i} is {type(nd)}; this is a compute-only backend")
-        plan = _lib.Plan(arr, len(nodes), n_slots, int(collect_timings), 0)
+        plan = _lib.Plan(arr, len(nodes), n_slots, int(collect_timings), int(max_in_flight))
         h = C.c_void_p()
         _lib.check(_lib.lib().ab_compile(self._h, C.byref(plan), C.byref(h)))
         return Executable(self, h, keep)
@@ -227,3 +228,136 @@ class Device:
         if self._h:
             _lib.check(_lib.lib().ab_close(self._h))
             self._h = None
+
+
+# ---------------------------------------------------------------------------- plan cache, buckets
+@dataclass
+class CompileOptions:
+    """tensor.CompileOptions (tensor/compile.go:15-28)."""
+    label: str = ""
+    max_in_flight: int = 0
+
+
+def plan_identity(nodes: Sequence[Union[Dispatch, Copy, HostWrite]], n_slots: int) -> bytes:
+    """A digest of a recorded plan's structure: every node's kind, kernel name, workgroup count,
+    uniform bytes, payload size and operands (block handle or slot, offset, size), in order.  Two
+    plans with the same shapes and different kernels or wiring have different identities: "shape
+    alone is never a sufficient key" (tensor/cache.go:50-56)."""
+    import hashlib
+    h = hashlib.sha256()
+
+    def put(*items):
+        for it in items:
+            b = it if isinstance(it, bytes) else str(it).encode()
+            h.update(len(b).to_bytes(8, "little"))
+            h.update(b)
+
+    def operand(o: Operand):
+        put("slot" if o.block is None else "block", o.slot if o.block is None else (o.block._h.value or 0),
+            o.offset, o.size)
+
+    put("accel_b200 plan identity v1", n_slots, len(nodes))
+    for nd in nodes:
+        if isinstance(nd, Dispatch):
+            put("dispatch", nd.kernel, *nd.count, nd.uniform or b"", len(nd.bindings))
+            for o in nd.bindings:
+                operand(o)
+        elif isinstance(nd, Copy):
+            put("copy")
+            operand(nd.src)
+            operand(nd.dst)
+        elif isinstance(nd, HostWrite):
+            put("host-write", len(nd.payload))        # the payload's bytes are set per submission
+            operand(nd.dst)
+        else:
+            raise TypeError(f"a plan node is {type(nd)}")
+    return h.digest()
+
+
+class PlanCache:
+    """tensor.PlanCache (tensor/cache.go:16-164): compiled executables kept by what they are, so a
+    caller whose shape varies compiles each distinct plan once.  Never evicts: a plan owns
+    transient device memory a caller may be about to submit against, so the cache grows until
+    close(); a caller who needs a bound gives it a bounded set of shapes (Buckets)."""
+
+    def __init__(self, dev: "Device"):
+        import threading
+        self.dev = dev
+        self._mu = threading.Lock()
+        self._plans: dict = {}
+        self._closed = False
+        self.compiles = 0
+
+    def _key(self, identity: bytes, opts: CompileOptions) -> bytes:
+        # tensor/cache.go:70-110: the graph, the device's identity, and every option that changes
+        # what compiling produces; the label is left out (two plans differing only in what they are
+        # called are the same plan)
+        import hashlib
+        h = hashlib.sha256()
+        h.update(b"accel/tensor plan key v1")
+        h.update(identity)
+        h.update(device_info(self.dev.ordinal)["token"])
+        h.update(b"opts v3")
+        h.update(f"max-in-flight={opts.max_in_flight}".encode())
+        return h.digest()
+
+    def compile(self, record, opts: Optional[CompileOptions] = None) -> Executable:
+        """`record()` returns (nodes, n_slots): recording is cheap and is the only way to learn the
+        identity; what a hit saves is everything after it (validation, workspaces, the lowering)."""
+        opts = opts or CompileOptions()
+        with self._mu:
+            if self._closed:
+                raise AccelError(_lib.AB_ERR_INVALID, "the plan cache is closed")
+            nodes, n_slots = record()
+            k = self._key(plan_identity(nodes, n_slots), opts)
+            hit = self._plans.get(k)
+            if hit is not None:
+                return hit
+            exe = self.dev.compile(nodes, n_slots, max_in_flight=opts.max_in_flight)
+            self.compiles += 1
+            self._plans[k] = exe
+            return exe
+
+    def __len__(self) -> int:
+        with self._mu:
+            return len(self._plans)
+
+    def close(self):
+        with self._mu:
+            if self._closed:
+                return
+            self._closed = True
+            for exe in self._plans.values():
+                exe.close()
+            self._plans = {}
+
+
+class Buckets:
+    """tensor.Buckets (tensor/cache.go:166-246): a sorted set of sequence lengths a caller compiles
+    plans for; a prompt runs in the smallest bucket that fits."""
+
+    def __init__(self, *sizes: int):
+        if not sizes:
+            raise ValueError("a bucket set needs at least one size")
+        out = sorted(int(s) for s in sizes)
+        for i, s in enumerate(out):
+            if s <= 0:
+                raise ValueError(f"bucket {i} is {s}, and a length is positive")
+            if i and out[i] == out[i - 1]:
+                raise ValueError(f"bucket size {s} appears twice")
+        self._sizes = out
+
+    def sizes(self) -> List[int]:
+        return list(self._sizes)
+
+    def for_(self, n: int) -> int:
+        """The smallest bucket that holds n tokens; a prompt longer than the largest bucket is an
+        error rather than a truncation."""
+        import bisect
+        if n <= 0:
+            raise ValueError(f"a prompt of {n} tokens")
+        i = bisect.bisect_left(self._sizes, n)
+        if i == len(self._sizes):
+            raise ValueError(f"a prompt of {n} tokens exceeds the largest bucket, {self._sizes[-1]}; add a "
+                             "bucket or split the prompt, because truncating it would answer a different question")
+        return self._sizes[i]

@@ -40,6 +40,28 @@ def int4_dequantize(packed, scales, zeros, n: int) -> np.ndarray:
     return out
 
 
+INT8_BLOCK = 32       # quant.Int8Block
+INT8_MAX = 127        # quant.Int8Max
+
+
+def int8_quantize(w) -> tuple:
+    """quant.Int8Quantize (quant/quant.go:60): (quants i8[n], scales f16 bits u16[ceil(n/32)])."""
+    w = np.ascontiguousarray(w, dtype=np.float32).ravel()
+    quants = np.zeros(w.size, np.int8)
+    scales = np.zeros((w.size + INT8_BLOCK - 1) // INT8_BLOCK, np.uint16)
+    _lib.check(_lib.lib().ab_int8_quantize(_vp(w), w.size, _vp(quants), _vp(scales)))
+    return quants, scales
+
+
+def int8_dequantize(quants, scales) -> np.ndarray:
+    """quant.Int8Dequantize (quant/quant.go:128)."""
+    quants = np.ascontiguousarray(quants, dtype=np.int8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint16)
+    out = np.zeros(quants.size, np.float32)
+    _lib.check(_lib.lib().ab_int8_dequantize(_vp(quants), _vp(scales), quants.size, _vp(out)))
+    return out
+
+
 def int4_quantize_device(w: torch.Tensor) -> tuple:
     """The same packing computed on the GPU, bit-identical to the host routine.  Returns
     (packed int32 view of the u32 words, scales float16, zeros float16) on w's device."""

@@ -118,6 +118,55 @@ def int4_matmul(a: torch.Tensor, w: Int4) -> torch.Tensor:
     return out
 
 
+# ------------------------------------------------------------------------------- int8 linear
+@dataclass
+class Quantized:
+    """tensor.Quantized (tensor/quantized.go:17): the quant plane [K, N] (i8) and its scales (f16,
+    one per 32 quants along the flat index)."""
+    quants: torch.Tensor
+    scales: torch.Tensor
+
+
+def _check_quantized(q: Quantized, what: str) -> str:
+    # tensor/quantized.go:25-52
+    if q.quants.dtype != torch.int8:
+        return f"{what} quants are {q.quants.dtype} and must be i8"
+    if q.scales.dtype != torch.float16:
+        return f"{what} scales are {q.scales.dtype} and must be f16"
+    n = q.quants.numel()
+    want = (n + 31) // 32
+    if q.scales.numel() != want:
+        return (f"{what} has {n} quants, which is {want} blocks of 32, and {q.scales.numel()} scales")
+    return ""
+
+
+def quant_matmul(x: torch.Tensor, w: Quantized) -> torch.Tensor:
+    """tensor.QuantMatMul (tensor/quantized.go:72) for f32 activations: one row takes the
+    matrix-vector kernel, more rows the tiled one, as the reference selects them."""
+    if w.quants is None or w.scales is None:
+        raise Refused("QuantMatMul", "the weight needs both a quant plane and a scale plane")
+    why = _check_quantized(w, "the weight")
+    if why:
+        raise Refused("QuantMatMul", why)
+    if x.dtype != torch.float32:
+        raise Refused("QuantMatMul", f"activations are {x.dtype}; this backend runs the f32-activation "
+                      "kernels of the int8 path (QuantMatVecF32, QuantMatMulTiledF32)")
+    if x.dim() != 2 or w.quants.dim() != 2:
+        raise Refused("QuantMatMul", f"operands are {tuple(x.shape)} and {tuple(w.quants.shape)}; "
+                      "v0 multiplies two matrices")
+    if x.shape[1] != w.quants.shape[0]:
+        raise Refused("QuantMatMul", f"{tuple(x.shape)} times {tuple(w.quants.shape)}: the contracted "
+                      f"axes are {x.shape[1]} and {w.quants.shape[0]}")
+    m, k = x.shape
+    n = w.quants.shape[1]
+    out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    if m == 0:
+        return out
+    name = "QuantMatVecF32" if m == 1 else "QuantMatMulTiledF32"
+    rt.launch(name, [x.contiguous(), w.quants.contiguous(), w.scales, out], rt.gemm_dims(m, n, k))
+    return out
+
+
 # ------------------------------------------------------------------------------- attention
 @dataclass
 class AttentionOptions:

@@ -125,7 +125,10 @@ typedef struct ab_plan {
     int32_t n_nodes;
     int32_t n_slots;
     int32_t collect_timings;       /* Plan.CollectTimings: time each submission with an event pair */
-    int32_t _pad;
+    int32_t max_in_flight;         /* CompileOptions.MaxInFlight (tensor/compile.go:19-27): submissions that may be
+                                      in flight at once; 0 means 1.  Above one, a submission that finds every
+                                      instance busy lowers a spare (own workspace, staging and graph), up to this
+                                      many; one more is refused with AB_ERR_BUSY. */
 } ab_plan;
 
 typedef struct ab_slot_binding { uint32_t slot; uint32_t _pad; ab_block *block; uint64_t offset; } ab_slot_binding;
@@ -194,6 +197,10 @@ AB_API uint64_t ab_launch_count(void);
  *                    internal/kernels/int4.go:60
  *  QuantMatMulInt4   a f32[M*K], bq, bs, bz, out f32[M*N]                  GEMMDims
  *                    internal/kernels/int4tiled.go:66
+ *  QuantMatVecF32    a f32[K], bq i8[K*N], bs f16[ceil(K*N/32)], out f32[N]    GEMMDims (M is 1)
+ *                    internal/kernels/matvec.go:204
+ *  QuantMatMulTiledF32   a f32[M*K], bq i8, bs f16, out f32[M*N]               GEMMDims
+ *                    internal/kernels/quant.go:195
  *  AttentionDecode, AttentionDecodeF16     q, k, v, lengths u32[1], out    AttnDims{QHeads,KVHeads,HeadDim,Scale f32}@0,4,8,12 (16 B)
  *                    internal/kernels/attention.go:97,422
  *  AttentionDecodePaged, AttentionDecodePagedF16   q, k, v, pages u32[P], lengths u32[1], out
@@ -249,6 +256,10 @@ AB_API int ab_int4_quantize(const float *w, size_t n, uint32_t *packed, uint16_t
 AB_API uint32_t ab_int4_nibble(const uint32_t *packed, size_t i);
 AB_API int ab_int4_dequantize(const uint32_t *packed, const uint16_t *scales,
                               const uint16_t *zeros, size_t n, float *out);
+/* quant.Int8Quantize / Int8Dequantize (quant/quant.go:60-134): n quants in [-127, 127], ceil(n/32) f16
+ * scale bit patterns. */
+AB_API int ab_int8_quantize(const float *w, size_t n, int8_t *quants, uint16_t *scales);
+AB_API int ab_int8_dequantize(const int8_t *quants, const uint16_t *scales, size_t n, float *out);
 /* accel.ToFloat16 / Float16.F32 (internal/kernel/narrow.go:67-140) */
 AB_API uint16_t ab_f32_to_f16(const float *x);     /* by pointer: no float crosses by value */
 AB_API void ab_f16_to_f32(uint16_t h, float *out);

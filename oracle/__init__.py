@@ -150,6 +150,37 @@ def quant_matmul_int4(a, bq, bs, bz, M: int, N: int, K: int, group: int = 128) -
     return out
 
 
+# ---------------------------------------------------------------- int8
+def int8_quantize(w):
+    w = _c(w, np.float32).ravel()
+    quants = np.zeros(w.size, np.int8)
+    scales = np.zeros((w.size + 31) // 32, np.uint16)
+    lib().orc_int8_quantize(_vp(w), C.c_size_t(w.size), _vp(quants), _vp(scales))
+    return quants, scales
+
+
+def int8_dequantize(quants, scales) -> np.ndarray:
+    quants, scales = _c(quants, np.int8), _c(scales, np.uint16)
+    out = np.empty(quants.size, np.float32)
+    lib().orc_int8_dequantize(_vp(quants), _vp(scales), C.c_size_t(quants.size), _vp(out))
+    return out
+
+
+def quant_matvec_f32(a, bq, bs, N: int, K: int) -> np.ndarray:
+    a, bq, bs = _c(a, np.float32), _c(bq, np.int8), _c(bs, np.uint16)
+    out = np.zeros(N, np.float32)
+    lib().orc_quant_matvec_f32(C.c_uint32(N), C.c_uint32(K), _vp(a), _vp(bq), _vp(bs), _vp(out))
+    return out
+
+
+def quant_matmul_tiled_f32(a, bq, bs, M: int, N: int, K: int) -> np.ndarray:
+    a, bq, bs = _c(a, np.float32), _c(bq, np.int8), _c(bs, np.uint16)
+    out = np.zeros((M, N), np.float32)
+    lib().orc_quant_matmul_tiled_f32(C.c_uint32(M), C.c_uint32(N), C.c_uint32(K), _vp(a), _vp(bq),
+                                     _vp(bs), _vp(out))
+    return out
+
+
 def matmul_definition_f64(a, w_dequant, M: int, N: int, K: int):
     a, w = _c(a, np.float32), _c(w_dequant, np.float32)
     want = np.zeros((M, N), np.float64)

@@ -891,6 +891,87 @@ ORC_API void orc_penalty_rows(uint32_t rows, uint32_t vocab, uint32_t history_ca
 }
 
 /* ------------------------------------------------------------------------------------------ */
+/* int8 weights: quant/quant.go:60-122 (Int8Quantize), :128-134 (Int8Dequantize); one f16 scale */
+/* per block of 32 weights along the flat index, quants in [-127, 127].                         */
+/* ------------------------------------------------------------------------------------------ */
+ORC_API void orc_int8_quantize(const float *w, size_t n, int8_t *quants, uint16_t *scales)
+{
+    const size_t block = 32;                      /* Int8Block */
+    size_t blocks = (n + block - 1) / block;
+    for (size_t b = 0; b < blocks; b++) {
+        size_t lo = b * block, hi = lo + block < n ? lo + block : n;
+        float peak = 0;
+        for (size_t i = lo; i < hi; i++) {
+            float a = (float)fabs((double)w[i]);
+            if (a > peak) peak = a;
+        }
+        for (size_t i = lo; i < hi; i++) quants[i] = 0;
+        if (peak == 0) { scales[b] = orc_f32_to_f16(0.0f); continue; }
+        float s = peak / 127.0f;                  /* Int8Max */
+        scales[b] = orc_f32_to_f16(s);
+        float s16 = orc_f16_to_f32(scales[b]);    /* quantize against the scale the kernel reads */
+        if (s16 == 0) continue;                   /* the scale underflowed f16 */
+        for (size_t i = lo; i < hi; i++) {
+            double q = nearbyint((double)w[i] / (double)s16);      /* round half to even */
+            if (q > 127) q = 127;
+            if (q < -127) q = -127;
+            quants[i] = (int8_t)q;
+        }
+    }
+}
+
+ORC_API void orc_int8_dequantize(const int8_t *quants, const uint16_t *scales, size_t n, float *out)
+{
+    for (size_t i = 0; i < n; i++) out[i] = (float)quants[i] * orc_f16_to_f32(scales[i / 32]);
+}
+
+/* QuantMatVecF32, internal/kernels/matvec.go:204-231 (workgroup 32x16): 16 phases of k per      */
+/* column, each acc = acc + a[k] * (q * s), then the phases summed in order.                     */
+ORC_API void orc_quant_matvec_f32(uint32_t N, uint32_t K, const float *a, const int8_t *bq,
+                                  const uint16_t *bs, float *out)
+{
+    const uint32_t phases = 16;
+#pragma omp parallel for schedule(static)
+    for (uint32_t col = 0; col < N; col++) {
+        float part[16];
+        for (uint32_t ly = 0; ly < phases; ly++) {
+            float acc = 0;
+            for (uint32_t k = ly; k < K; k += phases) {
+                uint64_t w = (uint64_t)k * N + col;
+                float q = (float)bq[w];
+                float s = orc_f16_to_f32(bs[w / 32]);
+                acc = acc + a[k] * (q * s);
+            }
+            part[ly] = acc;
+        }
+        float sum = 0;
+        for (uint32_t p = 0; p < phases; p++) sum = sum + part[p];
+        out[col] = sum;
+    }
+}
+
+/* QuantMatMulTiledF32, internal/kernels/quant.go:195-243: one accumulator per output element,   */
+/* sequential in k, each weight dequantized (q * s, rounded to f32) before the product; the     */
+/* zero padding of the tiles adds exact zeros and changes no bits.                              */
+ORC_API void orc_quant_matmul_tiled_f32(uint32_t M, uint32_t N, uint32_t K, const float *a,
+                                        const int8_t *bq, const uint16_t *bs, float *out)
+{
+#pragma omp parallel for schedule(static)
+    for (uint32_t col = 0; col < N; col++) {
+        for (uint32_t m = 0; m < M; m++) {
+            const float *am = a + (size_t)m * K;
+            float acc = 0;
+            for (uint32_t k = 0; k < K; k++) {
+                uint64_t w = (uint64_t)k * N + col;
+                float wv = (float)bq[w] * orc_f16_to_f32(bs[w / 32]);
+                acc = acc + am[k] * wv;
+            }
+            out[(size_t)m * N + col] = acc;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------ */
 /* Grouped (per-expert) products, internal/kernels/grouped.go:49-97, groupedtiled.go:77-134,    */
 /* segment.go:40                                                                                */
 /* ------------------------------------------------------------------------------------------ */

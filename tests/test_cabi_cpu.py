@@ -91,6 +91,15 @@ def test_host_quantizer_is_bit_identical_to_the_oracle(n):
         assert quant.int4_nibble(got[0], i) == orc.int4_nibble(want[0], i)
 
 
+@pytest.mark.parametrize("n", [5, 64, 200, 4096 * 3 + 7])
+def test_int8_host_quantizer_is_bit_identical_to_the_oracle(n, rng):
+    w = (rng.standard_normal(n) * 0.3).astype(np.float32)
+    q, s = quant.int8_quantize(w)
+    oq, os_ = orc.int8_quantize(w)
+    assert np.array_equal(q, oq) and np.array_equal(s, os_)
+    assert np.array_equal(quant.int8_dequantize(q, s), orc.int8_dequantize(oq, os_))
+
+
 def test_reference_packing_fixtures_through_the_c_abi():
     # quant/int4_test.go:261-286 and :225-253
     w = np.full(128, 0.5, np.float32)
@@ -190,3 +199,41 @@ def test_group_aligned_shards_pack_bit_identically(rng):
         assert np.array_equal(sc, codes[:, b:e])
         assert np.array_equal(shard[1].reshape(K, -1), full[1].reshape(K, -1)[:, b // 128:e // 128])
         assert np.array_equal(shard[2].reshape(K, -1), full[2].reshape(K, -1)[:, b // 128:e // 128])
+
+
+def test_buckets():
+    # tensor/cache.go:166-246 and tensor/cache_test.go: sorted, no duplicates, smallest that fits,
+    # a prompt past the largest bucket is an error rather than a truncation
+    from accel_b200.driver import Buckets
+    b = Buckets(512, 128, 256)
+    assert b.sizes() == [128, 256, 512]
+    assert [b.for_(n) for n in (1, 100, 128, 129, 256, 300, 512)] == [128, 128, 128, 256, 256, 512, 512]
+    with pytest.raises(ValueError, match="exceeds the largest bucket"):
+        b.for_(513)
+    with pytest.raises(ValueError, match="a prompt of 0"):
+        b.for_(0)
+    with pytest.raises(ValueError, match="appears twice"):
+        Buckets(128, 128)
+    with pytest.raises(ValueError, match="at least one"):
+        Buckets()
+    with pytest.raises(ValueError, match="positive"):
+        Buckets(0, 4)
+
+
+def test_plan_identity_is_structure_not_shape():
+    from accel_b200 import driver as D
+    from accel_b200 import runtime as rt
+    o = lambda slot, size: D.Operand(slot=slot, size=size)
+    base = [D.Dispatch("RMSNorm", [o(1, 4096), o(2, 1024), o(3, 4096)], rt.row_dims(4, 256, 1e-5))]
+    same = [D.Dispatch("RMSNorm", [o(1, 4096), o(2, 1024), o(3, 4096)], rt.row_dims(4, 256, 1e-5))]
+    other_kernel = [D.Dispatch("ElemAdd", [o(1, 4096), o(2, 1024), o(3, 4096)])]
+    other_uniform = [D.Dispatch("RMSNorm", [o(1, 4096), o(2, 1024), o(3, 4096)], rt.row_dims(4, 256, 1e-6))]
+    other_wiring = [D.Dispatch("RMSNorm", [o(3, 4096), o(2, 1024), o(1, 4096)], rt.row_dims(4, 256, 1e-5))]
+    ident = D.plan_identity(base, 3)
+    assert ident == D.plan_identity(same, 3)
+    for p in (other_kernel, other_uniform, other_wiring):
+        assert D.plan_identity(p, 3) != ident
+    assert D.plan_identity(base, 4) != ident
+    # a host write's payload is set per submission and is not part of what the plan is
+    hw = lambda payload: [D.HostWrite(o(1, 16), payload)]
+    assert D.plan_identity(hw(b"\0" * 16), 1) == D.plan_identity(hw(b"\1" * 16), 1)

@@ -202,3 +202,73 @@ def test_every_outstanding_fence_reports_an_injected_loss():
     with pytest.raises(D.DeviceLost):
         f2.wait()
     e1.close(); e2.close(); b.free(); dev.close()
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_several_submissions_in_flight(graphs):
+    """CompileOptions.MaxInFlight (tensor/compile.go:19-27): above one, a submission that finds every
+    instance busy lowers a spare, each with its own payload staging, up to the limit; a rebind
+    between two submissions applies to the second only."""
+    M, K = 4, 256
+    g = normal(2, (K,))
+    xs = [normal(10 + i, (M, K)) for i in range(3)]
+    dev = D.Device(0, use_graphs=graphs)
+    bx, bg = dev.alloc(M * K * 4), dev.upload(g)
+    outs = [dev.alloc(M * K * 4) for _ in range(3)]
+    nodes = [D.HostWrite(op(bx), xs[0].tobytes()),
+             D.Dispatch("RMSNorm", [op(bx), op(bg), D.Operand(slot=1, size=M * K * 4)], rt.row_dims(M, K, 1e-5))]
+    exe = dev.compile(nodes, n_slots=1, max_in_flight=2)
+    fences = []
+    for i in range(2):
+        exe.rebind([(1, outs[i], 0)])              # allowed with submissions in flight
+        exe.set_payload(0, xs[i].tobytes())
+        fences.append(exe.submit())
+    with pytest.raises(D.AccelError, match="all 2 instances"):
+        exe.submit()
+    fences[0].wait()
+    exe.rebind([(1, outs[2], 0)])
+    exe.set_payload(0, xs[2].tobytes())
+    fences.append(exe.submit())                   # the first instance again
+    for f in fences[1:]:
+        f.wait()
+    for i in range(3):
+        got = outs[i].read(0, np.zeros((M, K), np.float32))
+        assert np.array_equal(got, orc.rmsnorm(xs[i], g, 1e-5)), i
+    with pytest.raises(D.AccelError, match="executable"):
+        outs[2].free()                            # still named by the executable's slot
+    exe.close()
+    for b in (bx, bg, *outs):
+        b.free()
+    dev.close()
+
+
+def test_plan_cache_keys_on_what_the_plan_is():
+    """tensor.PlanCache (tensor/cache.go:16-164): the same recorded plan compiles once; another
+    kernel over the same shapes, or another MaxInFlight, is another plan; the label is not part of
+    the key; a closed cache refuses."""
+    M, K = 4, 256
+    dev = D.Device(0)
+    bx, bg, bo = dev.alloc(M * K * 4), dev.alloc(K * 4), dev.alloc(M * K * 4)
+
+    def record(kernel):
+        def rec():
+            u = rt.row_dims(M, K, 1e-5) if kernel == "RMSNorm" else None
+            binds = [op(bx), op(bg), op(bo)] if kernel == "RMSNorm" else [op(bx), op(bx), op(bo)]
+            return [D.Dispatch(kernel, binds, u)], 0
+        return rec
+
+    cache = D.PlanCache(dev)
+    a = cache.compile(record("RMSNorm"), D.CompileOptions(label="first"))
+    b = cache.compile(record("RMSNorm"), D.CompileOptions(label="second"))
+    assert a is b and len(cache) == 1 and cache.compiles == 1
+    c = cache.compile(record("ElemAdd"))
+    assert c is not a and len(cache) == 2
+    d = cache.compile(record("RMSNorm"), D.CompileOptions(max_in_flight=4))
+    assert d is not a and len(cache) == 3
+    a.submit().wait()
+    cache.close()
+    with pytest.raises(D.AccelError, match="closed"):
+        cache.compile(record("RMSNorm"))
+    for blk in (bx, bg, bo):
+        blk.free()
+    dev.close()

@@ -535,3 +535,85 @@ def test_softmax_is_a_distribution_and_matches_binary64(rng):
     e = np.exp(x.astype(np.float64) - x.max(axis=1, keepdims=True))
     assert np.max(np.abs(y - e / e.sum(axis=1, keepdims=True))) < 1e-6
     assert np.all(np.abs(y.sum(axis=1) - 1) < 1e-5)
+
+
+# ---------------------------------------------------------------- int8 weights
+def test_int8_dequantize_is_quant_times_scale():
+    # quant/quant_test.go:227-238
+    got = orc.int8_dequantize(np.array([1, -2, 127, -127], np.int8), orc.to_f16_bits(np.array([0.5], np.float32)))
+    assert np.array_equal(got, np.array([0.5, -1, 63.5, -63.5], np.float32))
+
+
+def _int8_cases():
+    smooth = np.array([math.sin(i * 0.31) * 3 for i in range(200)], np.float32)
+    outlier = np.full(128, 0.01, np.float32)
+    outlier[::32] = 100
+    half_zero = np.zeros(64, np.float32)
+    half_zero[32:] = np.arange(32, 64)
+    return {"smooth": smooth, "one outlier per block": outlier, "ragged": np.array([1, -2, 3, -4, 5], np.float32),
+            "zeros": np.zeros(64, np.float32), "a block of zeros beside values": half_zero,
+            "negatives": -np.arange(1, 41, dtype=np.float32)}
+
+
+@pytest.mark.parametrize("name", sorted(_int8_cases()))
+def test_int8_every_weight_is_within_half_a_step(name):
+    # quant/quant_test.go:22-100
+    w = _int8_cases()[name]
+    q, s = orc.int8_quantize(w)
+    assert q.size == w.size and s.size == (w.size + 31) // 32
+    back = orc.int8_dequantize(q, s)
+    step = orc.from_f16_bits(s)[np.arange(w.size) // 32].astype(np.float64)
+    assert np.all(np.abs(back.astype(np.float64) - w) <= step / 2 * (1 + 1e-3))
+    assert q.min() >= -127 and q.max() <= 127
+
+
+def test_int8_clamp_and_underflow():
+    # quant/quant_test.go:110-133: values a few ulps under the peak must not wrap to -128
+    peak = np.float32(1.0)
+    w = (np.full(32, peak.view(np.uint32), np.uint32) - np.arange(32, dtype=np.uint32)).view(np.float32)
+    q, s = orc.int8_quantize(w)
+    assert q.min() >= 0 and np.all(orc.int8_dequantize(q, s) >= 0)
+    # quant/quant_test.go:203-224: a scale that underflows f16 gives zero quants and zeros back
+    q, s = orc.int8_quantize(np.full(32, 1e-12, np.float32))
+    assert orc.from_f16_bits(s)[0] == 0 and not q.any() and not orc.int8_dequantize(q, s).any()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 8, 32), (1, 5, 64), (4, 8, 32), (3, 7, 96), (1, 16, 256)])
+def test_int8_products_are_exact_where_the_arithmetic_is(m, n, k):
+    """internal/kernels/f32variants_test.go:770-850: activations in quarters, quants i % 201 - 100,
+    scales 1/4 + (i % 3) / 8.  Every product and partial sum is a small dyadic rational, exact in
+    f32 in any order, so both kernels must return the integer arithmetic's answer bit for bit."""
+    a = np.array([((i % 13) - 6) / 4 for i in range(m * k)], np.float32)
+    bq = np.array([i % 201 - 100 for i in range(k * n)], np.int8)
+    sv = np.array([0.25 + (i % 3) / 8 for i in range((k * n + 31) // 32)], np.float32)
+    bs = orc.to_f16_bits(sv)
+    want = np.zeros((m, n), np.float64)
+    for r in range(m):
+        for c in range(n):
+            idx = np.arange(k) * n + c
+            want[r, c] = np.sum(a[r * k:(r + 1) * k].astype(np.float64) * bq[idx] * sv[idx // 32].astype(np.float64))
+    got = orc.quant_matmul_tiled_f32(a, bq, bs, m, n, k)
+    assert np.array_equal(got.astype(np.float64), want)
+    if m == 1:
+        assert np.array_equal(orc.quant_matvec_f32(a, bq, bs, n, k).astype(np.float64), want[0])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 8, 64), (4, 16, 128), (3, 5, 33), (2, 7, 96)])
+def test_int8_products_meet_the_reference_budget(m, n, k):
+    # internal/kernels/quant_test.go:45-117: half a scale step per term plus gamma(K-1) of accumulation
+    a = np.array([math.sin(i * 0.23) * 2 for i in range(m * k)], np.float32)
+    w = np.array([math.cos(i * 0.31) * 1.5 for i in range(k * n)], np.float32)
+    bq, bs = orc.int8_quantize(w)
+    sc = orc.from_f16_bits(bs).astype(np.float64)
+    outs = [orc.quant_matmul_tiled_f32(a, bq, bs, m, n, k)]
+    if m == 1:
+        outs.append(orc.quant_matvec_f32(a, bq, bs, n, k)[None, :])
+    nu = (k - 1) / (1 << 24)
+    for out in outs:
+        for r in range(m):
+            for c in range(n):
+                idx = np.arange(k) * n + c
+                x = a[r * k:(r + 1) * k].astype(np.float64)
+                exact = np.sum(x * w[idx])
+                budget = np.sum(np.abs(x) * sc[idx // 32] / 2) + nu / (1 - nu) * np.sum(np.abs(x * w[idx]))
+                assert abs(out[r, c] - exact) <= budget
