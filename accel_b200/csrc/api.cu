@@ -119,6 +119,7 @@ static const KernelEntry kKernels[] = {
     {"GroupedMatVec", 4, 16, launch_grouped_matvec},
     {"GroupedMatMul", 4, 16, launch_grouped_matmul},
     {"GroupedMatMulInt4", 6, 16, launch_grouped_matmul_int4},
+    {"GroupedMatMulInt4Packed", 4, 16, launch_grouped_matmul_int4_packed},
     {"SegmentOffsets", 2, 16, launch_segment_offsets},
     {"ScatterRows", 3, 16, launch_scatter_rows},
     {"ScatterRowsF16", 3, 16, launch_scatter_rows_f16},
@@ -129,6 +130,8 @@ static const KernelEntry kKernels[] = {
     {"SwiGLU", 3, 0, launch_swiglu},
     {"ElemAdd", 3, 0, launch_elem_add},
     {"SampleArgmax", 2, 16, launch_sample_argmax},
+    {"ArgmaxShard", 2, 32, launch_argmax_shard},
+    {"ArgmaxMerge", 2, 16, launch_argmax_merge},
     {"Softmax", 2, 16, launch_softmax},
     {"ScaleRows", 3, 16, launch_scale_rows},
     {"LogitBias", 4, 16, launch_logit_bias},
@@ -289,6 +292,7 @@ static size_t elem_bytes_of(const char *k, int i)
     auto is = [&](const char *n) { return strcmp(k, n) == 0; };
     if (is("QuantMatVecInt4") || is("QuantMatMulInt4")) return (i == 2 || i == 3) ? 2 : 4;
     if (is("GroupedMatMulInt4")) return (i == 2 || i == 3) ? 2 : 4;
+    if (is("QuantMatVecF32") || is("QuantMatMulTiledF32")) return i == 1 ? 1 : (i == 2 ? 2 : 4);
     if (is("AttentionPrefillF16") || is("AttentionPrefillPagedF16")) return (i == 1 || i == 2) ? 2 : 4;
     if (is("AttentionDecodeF16") || is("AttentionDecodePagedF16") || is("AttentionDecodeBatchedF16") ||
         is("AttentionRaggedF16"))

@@ -96,11 +96,6 @@ int run_int4_batch(const Launch &l, const Int4BatchPlan &p, float *out, uint32_t
 bool int4_tiles_ok(uint32_t N, uint32_t K);
 int run_int4_tiles(const Launch &l, float *out, uint32_t M, uint32_t N, uint32_t K);
 
-// the tcgen05 / TMEM int4 kernel (int4_tc.cu)
-struct Int4TcPlan { bool ok; uint32_t groups, splits, kc; int nmma; size_t ws; };
-Int4TcPlan plan_int4_tc(uint32_t M, uint32_t N, uint32_t K);
-int run_int4_tc(const Launch &l, const Int4TcPlan &p, float *dst, uint32_t M, uint32_t N, uint32_t K);
-int int4_tc_error_flag();       // nonzero once a bounded device-side wait has run out
 
 // the decode-batch int4 kernel over prepacked weights: bulk copies, tensor memory, tcgen05 (int4_stream.cu)
 bool int4_stream_ok(uint32_t M, uint32_t N, uint32_t K);
@@ -118,6 +113,7 @@ int run_int4_gemm_mode(cudaStream_t stream, const float *a, const unsigned char 
                        float *out1, float *out2, uint32_t n1, uint32_t n2, uint32_t M, uint32_t N, uint32_t K,
                        uint32_t ld0, void *scratch);
 int int4_gemm_error_flag();
+int launch_grouped_matmul_int4_packed(Launch &);
 int launch_quant_matvec_int4_packed(Launch &);
 int launch_quant_matmul_int4_packed(Launch &);
 int launch_quant_matmul_int4_packed_split3(Launch &);
@@ -172,6 +168,8 @@ int launch_penalty_count(Launch &);
 int launch_penalty_apply(Launch &);
 int launch_int4_quantize(Launch &);
 int launch_decode_step_inputs(Launch &);
+int launch_argmax_shard(Launch &);
+int launch_argmax_merge(Launch &);
 int launch_add_rmsnorm(Launch &);
 int launch_rope_scatter_qkv(Launch &);
 int launch_rope_scatter_qkv_f16(Launch &);

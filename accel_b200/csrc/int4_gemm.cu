@@ -48,9 +48,8 @@ static constexpr int kGmNA = 4;                                     // A stages 
 // stages of the shared-memory ring (weights + B tile): as deep as lets two CTAs of one group, or one
 // CTA of two groups, share an SM; what is in flight per SM has to cover the latency of L2
 __host__ __device__ constexpr int gm_stages(int G) { return G == 1 ? 5 : 8; }
-// B: stride between 8-k blocks of a tile (+16: the two blocks one MMA reads start in different banks)
-static constexpr uint32_t kGmLbo = kGmBN * 16 + 16;
-static constexpr uint32_t kGmBTile = 8 * kGmLbo;                    // one B tile: 128 rows x 64 k, f16
+static constexpr uint32_t kGmLbo = kGmBN * 16;                      // B: stride between 8-k blocks of a tile
+static constexpr uint32_t kGmBTile = 8 * kGmLbo;                    // one B tile: 128 rows x 64 k, f16, 16 KB
 static constexpr uint32_t kGmPassRows = 4096;                       // activation rows converted per pass
 __host__ __device__ constexpr uint32_t gm_stage_bytes(int G) { return (uint32_t)G * kSxChunkBytes + kGmBTile; }
 __host__ __device__ constexpr uint32_t gm_tmem_cols(int G) { return G == 1 ? 256u : 512u; }     // D: G x 128, A: G x 4 x 32
@@ -72,18 +71,51 @@ __device__ long long g_gm_trace[64];
 #define GM_STAMP(i) do { } while (0)
 #endif
 
+// Which rows a block of 128 tile rows stands for.  Dense product: block rb is rows 128 rb ... of the
+// one matrix (table NULL).  Grouped product (rows sorted by expert, internal/kernels/groupedtiled.go:77):
+// every expert's segment is cut into blocks of its own, so a tile never mixes experts; entry rb of
+// the table holds {expert, first row, rows (1..128)} and *total the number of blocks in use.
+struct GmRows {
+    const uint4 *table;
+    const uint32_t *total;
+    unsigned long long expert_stride;      // bytes between the experts' packed matrices
+};
+
+// offsets[e] .. offsets[e + 1]: expert e's rows (SegmentOffsets, internal/kernels/segment.go:40).
+// One thread: at most a few thousand blocks.
+__global__ void gm_group_plan_kernel(const uint32_t *__restrict__ offsets, uint32_t experts, uint32_t tokens,
+                                     uint4 *table, uint32_t *total, uint32_t capacity)
+{
+    if (threadIdx.x || blockIdx.x) return;
+    uint32_t n = 0;
+    for (uint32_t e = 0; e < experts; e++) {
+        const uint32_t lo = min(offsets[e], tokens), hi = min(offsets[e + 1], tokens);
+        for (uint32_t r = lo; r < hi && n < capacity; r += kGmBN)
+            table[n++] = make_uint4(e, r, min((uint32_t)kGmBN, hi - r), 0u);
+    }
+    *total = n;
+}
+
 // ---- activations: f32 [M][K] -> f16 B tiles + the rows' power-of-two factors ------------------------
-// grid = padded rows / 8, one warp per row.  Tile (row block rb, chunk c) is 16512 bytes at
-// (rb * nchunks + c) * 16512; inside it element (r, k) sits at (k / 8) * 2064 + (r / 8) * 128 +
-// (r % 8) * 16 + (k % 8) * 2.  Rows past M and k past K are zeros.
+// grid = padded rows / 8, one warp per row.  Tile (row block rb, chunk c) is 16 KB at
+// (rb * nchunks + c) * 16 KB; inside it element (r, k) sits at (k / 8) * 2048 + (r / 8) * 128 +
+// (r % 8) * 16 + (k % 8) * 2.  Rows past M and k past K are zeros.  unscale is
+// indexed like the tiles' rows.
 __global__ void __launch_bounds__(256)
 int4_act_tiles_kernel(const float *__restrict__ a, unsigned char *__restrict__ tiles, float *__restrict__ unscale,
-                      uint32_t M, uint32_t K, uint32_t nchunks)
+                      uint32_t M, uint32_t K, uint32_t nchunks, const GmRows rows)
 {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t r = blockIdx.x * 8 + warp;
-    const bool live = r < M;
-    const float *row = a + (size_t)(live ? r : 0) * K;
+    const uint32_t r = blockIdx.x * 8 + warp;            // a row of the tiles
+    bool live = r < M;
+    uint32_t src = r;                                    // the activation row it holds
+    if (rows.table) {
+        if ((r >> 7) >= *rows.total) return;             // a block nobody multiplies
+        const uint4 e = rows.table[r >> 7];
+        live = (r & 127u) < e.z;
+        src = e.y + (r & 127u);
+    }
+    const float *row = a + (size_t)(live ? src : 0) * K;
     uint32_t mx = 0;
     if (live) {
         for (uint32_t k = lane * 4; k < K; k += 128) {
@@ -95,7 +127,7 @@ int4_act_tiles_kernel(const float *__restrict__ a, unsigned char *__restrict__ t
     mx = __reduce_max_sync(0xffffffffu, mx);
     const int ea = sx_row_exponent(mx);
     const float pa = __uint_as_float((uint32_t)(127 + 14 - ea) << 23);                 // 2^(14 - E_a)
-    if (lane == 0 && live) unscale[r] = __uint_as_float((uint32_t)(127 + ea - 14) << 23);
+    if (lane == 0) unscale[r] = live ? __uint_as_float((uint32_t)(127 + ea - 14) << 23) : 0.f;
     const uint32_t rb = r >> 7, rin = r & 127u;
     unsigned char *base = tiles + (size_t)rb * nchunks * kGmBTile + (rin >> 3) * 128u + (rin & 7u) * 16u;
     for (uint32_t kb = lane; kb < nchunks * 8; kb += 32) {
@@ -128,7 +160,7 @@ template <int G>
 __global__ void __launch_bounds__(kGmThreads)
 int4_gemm_kernel(const unsigned char *__restrict__ packed, const unsigned char *__restrict__ tiles,
                  const float *__restrict__ unscale, const SxEpilogue ep, uint32_t M, uint32_t N, uint32_t nchunks,
-                 uint32_t header_bytes, uint32_t nrb)
+                 uint32_t header_bytes, uint32_t nrb, const GmRows rows)
 {
     extern __shared__ __align__(128) unsigned char gm_raw[];
     constexpr uint32_t kStage = gm_stage_bytes(G);
@@ -151,6 +183,15 @@ int4_gemm_kernel(const unsigned char *__restrict__ packed, const unsigned char *
     if (tid == 0) GM_STAMP(0);
     const uint32_t groups = N / 128;
     const uint32_t rb = blockIdx.x % nrb, g0 = (blockIdx.x / nrb) * G;
+    // the rows this block stands for: row0 .. row0 + nrows - 1 of the activations and of the output
+    uint32_t row0 = rb * kGmBN, nrows = M > row0 ? min((uint32_t)kGmBN, M - row0) : 0u;
+    if (rows.table) {
+        if (rb >= *rows.total) return;                   // the whole CTA: nothing is set up yet
+        const uint4 e = rows.table[rb];
+        packed += (size_t)e.x * rows.expert_stride;
+        row0 = e.y;
+        nrows = e.z;
+    }
     const uint32_t gcount = min((uint32_t)G, groups - g0);
     const unsigned char *wsrc = packed + header_bytes + (size_t)g0 * nchunks * kSxChunkBytes;
     const size_t group_stride = (size_t)nchunks * kSxChunkBytes;
@@ -189,8 +230,7 @@ int4_gemm_kernel(const unsigned char *__restrict__ packed, const unsigned char *
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (tid < kGmBN) {
-        const uint32_t m = rb * kGmBN + (uint32_t)tid;
-        uns[tid] = m < M ? __ldg(unscale + m) : 0.f;
+        uns[tid] = (uint32_t)tid < nrows ? __ldg(unscale + rb * kGmBN + (uint32_t)tid) : 0.f;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -356,8 +396,8 @@ int4_gemm_kernel(const unsigned char *__restrict__ packed, const unsigned char *
                     sx_tmem_ld16(tmem + tlane + 128 + col0, ru);
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
-                        const uint32_t m = rb * kGmBN + col0 + j;
-                        if (m < M) {
+                        const uint32_t m = row0 + col0 + j;
+                        if (col0 + j < nrows) {
                             const float f = uns[col0 + j];
                             const float gate = __uint_as_float(rg[j]) * (f * es[0]);
                             const float upv = __uint_as_float(ru[j]) * (f * es[G - 1]);
@@ -377,8 +417,8 @@ int4_gemm_kernel(const unsigned char *__restrict__ packed, const unsigned char *
                             sx_tmem_ld16(tmem + tlane + gi * 128 + col0, r);
 #pragma unroll
                             for (int j = 0; j < 16; j++) {
-                                const uint32_t m = rb * kGmBN + col0 + j;
-                                if (m < M)
+                                const uint32_t m = row0 + col0 + j;
+                                if (col0 + j < nrows)
                                     sx_store(ep, m, g0 + gi, tcol, __uint_as_float(r[j]) * (uns[col0 + j] * es[gi]));
                             }
                         }
@@ -419,17 +459,17 @@ template <int G> static int gm_prepare()
     return AB_OK;
 }
 
-// Two groups per CTA halve the B-tile traffic from L2 but leave one CTA per SM and half as many
-// tiles; one group per CTA lets two CTAs share an SM.  Wide matrices with enough row blocks to
-// fill the SMs either way take two.
+// One group per CTA, two CTAs per SM, measured faster than two groups per CTA (one CTA per SM,
+// half the B-tile traffic, but a single lane issuing every MMA): 4096 x 11008 at 2048 rows 237 us
+// against 262 us, at 512 rows 91 us against 105 us.  The SwiGLU epilogue needs the (gate, up) pair
+// of groups in one CTA.
 static int gm_groups_per_cta(uint32_t M, uint32_t N, bool swiglu)
 {
-    if (swiglu) return 2;
+    (void)M; (void)N;
 #ifdef GM_TRACE
     if (getenv("GM_G")) return atoi(getenv("GM_G"));
 #endif
-    const uint32_t groups = N / 128, nrb = (M + kGmBN - 1) / kGmBN;
-    return (groups / 2) * nrb >= 2u * (uint32_t)sm_count() ? 2 : 1;
+    return swiglu ? 2 : 1;
 }
 
 // The product in passes of at most kGmPassRows activation rows.  mode and the destinations are
@@ -452,7 +492,8 @@ int run_int4_gemm_mode(cudaStream_t stream, const float *a, const unsigned char 
     for (uint32_t m0 = 0; m0 < M; m0 += kGmPassRows) {
         const uint32_t rows = M - m0 < kGmPassRows ? M - m0 : kGmPassRows;
         const uint32_t nrb = (rows + kGmBN - 1) / kGmBN;
-        int4_act_tiles_kernel<<<nrb * (kGmBN / 8), 256, 0, stream>>>(a + (size_t)m0 * K, tiles, unscale, rows, K, nchunks);
+        int4_act_tiles_kernel<<<nrb * (kGmBN / 8), 256, 0, stream>>>(a + (size_t)m0 * K, tiles, unscale, rows, K, nchunks,
+                                                                     GmRows{nullptr, nullptr, 0ull});
         count_launch();
         SxEpilogue ep{};
         ep.g1 = ep.g2 = 0xffffffffu;
@@ -469,10 +510,10 @@ int run_int4_gemm_mode(cudaStream_t stream, const float *a, const unsigned char 
         const uint32_t ctas = ((groups + G - 1) / G) * nrb;
         if (G == 2)
             int4_gemm_kernel<2><<<ctas, kGmThreads, gm_smem_bytes(2), stream>>>(packed, tiles, unscale, ep, rows, N,
-                                                                                 nchunks, hb, nrb);
+                                                                                 nchunks, hb, nrb, GmRows{nullptr, nullptr, 0ull});
         else
             int4_gemm_kernel<1><<<ctas, kGmThreads, gm_smem_bytes(1), stream>>>(packed, tiles, unscale, ep, rows, N,
-                                                                                 nchunks, hb, nrb);
+                                                                                 nchunks, hb, nrb, GmRows{nullptr, nullptr, 0ull});
         count_launch();
         rc = check_cuda(cudaGetLastError(), "int4_gemm_kernel");
         if (rc) return rc;
@@ -482,6 +523,74 @@ int run_int4_gemm_mode(cudaStream_t stream, const float *a, const unsigned char 
                    "tiles of %d groups x %u row blocks of 128, %u chunks of 64 weight rows", (groups + G - 1) / G, G,
                    (M + kGmBN - 1) / kGmBN, nchunks);
     return AB_OK;
+}
+
+// ---- grouped product: rows sorted by expert, one prepacked [K, N] matrix per expert --------------------
+static uint32_t gm_group_blocks(uint32_t experts, uint32_t tokens) { return (tokens + kGmBN - 1) / kGmBN + experts; }
+
+size_t int4_gemm_grouped_workspace(uint32_t experts, uint32_t tokens, uint32_t K)
+{
+    const size_t nb = gm_group_blocks(experts, tokens), nchunks = (K + kSxChunkK - 1) / kSxChunkK;
+    return align_up(nb * sizeof(uint4), 256) + 256 + align_up(nb * kGmBN * 4, 256) + nb * nchunks * kGmBTile;
+}
+
+int run_int4_gemm_grouped(cudaStream_t stream, const float *x, const unsigned char *packed, const uint32_t *offsets,
+                          float *out, uint32_t experts, uint32_t tokens, uint32_t N, uint32_t K, void *scratch)
+{
+    if (tokens == 0 || experts == 0) return AB_OK;
+    if (!scratch) return fail(AB_ERR_INVALID, "the grouped prepacked int4 product needs %zu bytes of scratch",
+                              int4_gemm_grouped_workspace(experts, tokens, K));
+    int rc = gm_prepare<1>();
+    if (rc) return rc;
+    const uint32_t nb = gm_group_blocks(experts, tokens), nchunks = (K + kSxChunkK - 1) / kSxChunkK, groups = N / 128;
+    unsigned char *ws = static_cast<unsigned char *>(scratch);
+    uint4 *table = reinterpret_cast<uint4 *>(ws);
+    ws += align_up((size_t)nb * sizeof(uint4), 256);
+    uint32_t *total = reinterpret_cast<uint32_t *>(ws);
+    ws += 256;
+    float *unscale = reinterpret_cast<float *>(ws);
+    ws += align_up((size_t)nb * kGmBN * 4, 256);
+    unsigned char *tiles = ws;
+    const GmRows rows{table, total, (unsigned long long)int4_stream_packed_bytes(N, K)};
+    gm_group_plan_kernel<<<1, 32, 0, stream>>>(offsets, experts, tokens, table, total, nb);
+    count_launch();
+    int4_act_tiles_kernel<<<nb * (kGmBN / 8), 256, 0, stream>>>(x, tiles, unscale, tokens, K, nchunks, rows);
+    count_launch();
+    SxEpilogue ep{};
+    ep.g1 = ep.g2 = 0xffffffffu;
+    ep.ld0 = N;
+    ep.out0 = out;
+    int4_gemm_kernel<1><<<groups * nb, kGmThreads, gm_smem_bytes(1), stream>>>(packed, tiles, unscale, ep, tokens, N, nchunks,
+                                                                             (uint32_t)sx_header_bytes(N), nb, rows);
+    count_launch();
+    rc = check_cuda(cudaGetLastError(), "int4_gemm_kernel (grouped)");
+    if (rc) return rc;
+    note_selection("grouped int4 tile kernel on tcgen05 (every expert's segment in blocks of 128 rows of its own, "
+                   "weights dequantised into tensor memory, M=128 x N=128 x K=16 MMAs), %u experts, %u rows, up to "
+                   "%u row blocks x %u column groups", experts, tokens, nb, groups);
+    return AB_OK;
+}
+
+// x f32[T*K], packed (Experts matrices, each ab_int4_prepack_bytes(K, N) bytes, end to end), offsets
+// u32[E+1], out f32[T*N]; GroupedTiledDims{Experts,Tokens,K,N}
+int launch_grouped_matmul_int4_packed(Launch &l)
+{
+    const char *name = "GroupedMatMulInt4Packed";
+    const uint32_t E = u32_at(l.u, 0), T = u32_at(l.u, 4), K = u32_at(l.u, 8), N = u32_at(l.u, 12);
+    if (E == 0 || N == 0 || N % 128 || K == 0 || K % 4)
+        return fail(AB_ERR_INVALID, "%s: Experts=%u Tokens=%u K=%u N=%u; N is a multiple of 128 and K of 4", name, E, T, K, N);
+    const size_t ws = T ? int4_gemm_grouped_workspace(E, T, K) : 0;
+    if (l.query_ws) { l.ws_need = ws; return AB_OK; }
+    const size_t per = int4_stream_packed_bytes(N, K);
+    if (l.len[0] < (uint64_t)T * K || (uint64_t)l.len[1] * 4 < (uint64_t)E * per || l.len[2] < E + 1 ||
+        l.len[3] < (uint64_t)T * N)
+        return fail(AB_ERR_INVALID, "%s: Experts=%u Tokens=%u K=%u N=%u needs x[%llu] packed[%llu bytes] offsets[%u] "
+                    "out[%llu]; the lengths block says %u, %u words, %u, %u", name, E, T, K, N, (unsigned long long)T * K,
+                    (unsigned long long)E * per, E + 1, (unsigned long long)T * N, l.len[0], l.len[1], l.len[2], l.len[3]);
+    if (ws > l.ws_bytes || (ws && !l.ws))
+        return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, ws, l.ws_bytes);
+    return run_int4_gemm_grouped(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1), ptr<const uint32_t>(l, 2),
+                                 ptr<float>(l, 3), E, T, N, K, l.ws);
 }
 
 int int4_gemm_error_flag()

@@ -233,25 +233,17 @@ static int forced_path()
     return v;
 }
 
-// From how many activation rows the 128-row tile kernel is used instead of passes of 16 rows.
-// AB_INT4_TC_MIN_ROWS fixes it; otherwise a cost model fitted to measurements on a B200: a pass of
-// the batch kernel costs about 4 us + 0.53 bytes per weight at 1.65 TB/s, a wave of tiles about
-// 130 us per 4096 rows of K whatever the width of the matrix.
-static bool prefer_tiles(uint32_t M, uint32_t N, uint32_t K)
+// From this many activation rows the reference-layout product runs on the tcgen05 tile kernel
+// (int4_gemm.cu), which reads the prepacked stream: the three planes are permuted into the
+// workspace first, every call (about 20 us for 4096 x 11008, a fifth of the product at 512 rows; a
+// host that keeps its weights prepacks them once with ab_int4_prepack and calls the packed entry
+// points instead).  Measured on a B200 at 4096 x 11008: 64 rows, 4 passes of the 16-row kernel 73 us
+// against 70 us; 512 rows, 351 us on the warp-level tile kernel against 112 us.
+static constexpr uint32_t kTcFromRows = 64;
+static bool tc_tiles_ok(uint32_t M, uint32_t N, uint32_t K) { return M >= kTcFromRows && int4_stream_ok(M, N, K); }
+static size_t tc_tiles_workspace(uint32_t M, uint32_t N, uint32_t K)
 {
-    static int fixed = -2;
-    if (fixed == -2) {
-        const char *e = getenv("AB_INT4_TC_MIN_ROWS");
-        fixed = e ? atoi(e) : -1;
-    }
-    if (fixed >= 0) return M >= (uint32_t)fixed;
-    if (M < 64) return false;
-    const double pass_us = 4.0 + 0.53125 * (double)K * N / 1.65e6;
-    const double batch_us = (double)((M + 15) / 16) * pass_us;
-    const double ctas = (double)(N / kGroup) * ((M + 127) / 128);
-    const double waves = (double)(uint64_t)((ctas + sm_count() - 1) / sm_count());
-    const double tiles_us = waves * 130.0 * (double)K / 4096.0;
-    return tiles_us < batch_us;
+    return align_up(int4_stream_packed_bytes(N, K), 256) + int4_gemm_workspace(M, K);
 }
 
 static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint32_t K)
@@ -262,12 +254,11 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     Int4MmaPlan mp = plan_int4_mma(M, N, K);
     // AB_INT4_PATH = tiles | tc | batch | mma | simt | row overrides the choice (for
     // measurements and tests)
-    Int4TcPlan tp = plan_int4_tc(M, N, K);
     const int forced = forced_path();
-    // from about a hundred rows: 128-row tiles on the warp-level MMAs (measured faster than the
-    // tcgen05 kernel as built, which stays behind AB_INT4_PATH=tc)
-    const bool use_tiles = int4_tiles_ok(N, K) && (forced == 7 || (forced == 0 && prefer_tiles(M, N, K)));
-    const bool use_tc = !use_tiles && tp.ok && forced == 1;
+    // large batches: the tcgen05 tile kernel; AB_INT4_PATH=tiles keeps the warp-level MMA tile
+    // kernel (the one the grouped product also uses)
+    const bool use_tiles = int4_tiles_ok(N, K) && forced == 7;
+    const bool use_tc = !use_tiles && int4_stream_ok(M, N, K) && (forced == 1 || (forced == 0 && tc_tiles_ok(M, N, K)));
     Int4BatchPlan bp = plan_int4_batch(M, N, K);
     const bool use_batch = !use_tc && !use_tiles && bp.ok && (forced == 4 || (forced == 0 && M >= 2));
     const bool use_mma = !use_tc && !use_tiles && !use_batch && mp.ok && (forced == 2 || (forced == 0 && M >= 2));
@@ -276,7 +267,7 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     Int4RowPlan rp = plan_int4_row(N, K);
     const bool use_row = !use_tc && !use_tiles && !use_mma && !use_batch && rp.ok && M == 1 && forced != 3;
     if (l.query_ws) {
-        l.ws_need = use_tiles ? 0 : use_tc ? tp.ws : (use_batch ? 0 : (use_mma ? mp.ws : (use_row ? 0 : p.ws)));
+        l.ws_need = use_tiles ? 0 : use_tc ? tc_tiles_workspace(M, N, K) : (use_batch ? 0 : (use_mma ? mp.ws : (use_row ? 0 : p.ws)));
         return AB_OK;
     }
 
@@ -307,20 +298,15 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
         return AB_OK;
     }
     if (use_tc) {
-        if (tp.ws > l.ws_bytes || (tp.ws && !l.ws))
-            return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, tp.ws,
-                        l.ws_bytes);
-        float *tdst = tp.splits > 1 ? reinterpret_cast<float *>(l.ws) : out;
-        int rc = run_int4_tc(l, tp, tdst, M, N, K);
+        const size_t need = tc_tiles_workspace(M, N, K);
+        if (need > l.ws_bytes || !l.ws)
+            return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, need, l.ws_bytes);
+        unsigned char *packed = static_cast<unsigned char *>(l.ws);
+        int rc = run_int4_prepack(l.stream, ptr<const uint32_t>(l, 1), ptr<const uint16_t>(l, 2), ptr<const uint16_t>(l, 3),
+                                  packed, N, K);
         if (rc) return rc;
-        if (tp.splits > 1) {
-            size_t mn = (size_t)M * N;
-            int4_reduce_kernel<<<(unsigned)((mn / 4 + 128) / 128), 128, 0, l.stream>>>(tdst, out, tp.splits, mn); count_launch();
-        }
-        note_selection("%s: tcgen05 kernel (M=128 x N=%d x K=16 MMAs, f16 operands, TMEM f32 "
-                       "accumulator), %u column groups x %u K splits of %u rows", name, tp.nmma,
-                       tp.groups, tp.splits, tp.kc);
-        return check_cuda(cudaGetLastError(), name);
+        return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), packed, 0, out, nullptr, nullptr, 0, 0, M, N, K, N,
+                                  packed + align_up(int4_stream_packed_bytes(N, K), 256));
     }
     if (use_batch) {
         int rc = run_int4_batch(l, bp, out, M, N, K);

@@ -562,19 +562,24 @@ int4_row_absmax_kernel(const float *__restrict__ a, float *__restrict__ amax, ui
 }
 
 // ---- prepack ----------------------------------------------------------------------------------------
+// Three passes, each reading and writing whole sectors (the permutation also runs per call when a
+// large batch arrives in the reference layout, so it is worth keeping near the copy rate).
+//
 // header word g <- the f16 bits of the group's largest finite scale (scales are non-negative, so
-// their bit patterns order like their values)
-__global__ void int4_prepack_smax_kernel(const uint16_t *__restrict__ scales, uint32_t *header, uint32_t groups,
-                                         uint32_t K)
+// their bit patterns order like their values).  grid = blocks of 64 weight rows; a thread walks
+// groups g, g + 256, ... of its block's rows, so a warp reads 64 contiguous bytes per row.
+__global__ void __launch_bounds__(256)
+int4_prepack_smax_kernel(const uint16_t *__restrict__ scales, uint32_t *header, uint32_t groups, uint32_t K)
 {
-    const uint32_t g = blockIdx.x;
-    uint32_t mx = 0;
-    for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) {
-        const uint32_t sb = scales[(size_t)k * groups + g];
-        if (!(sb & 0x8000u) && sb < 0x7c00u) mx = max(mx, sb);
+    const uint32_t k0 = blockIdx.x * 64, k1 = min(K, k0 + 64);
+    for (uint32_t g = threadIdx.x; g < groups; g += 256) {
+        uint32_t mx = 0;
+        for (uint32_t k = k0; k < k1; k++) {
+            const uint32_t sb = scales[(size_t)k * groups + g];
+            if (!(sb & 0x8000u) && sb < 0x7c00u) mx = max(mx, sb);
+        }
+        if (mx) atomicMax(&header[g], mx);
     }
-    mx = __reduce_max_sync(0xffffffffu, mx);
-    if ((threadIdx.x & 31) == 0) atomicMax(&header[g], mx);
 }
 
 // header word g: the largest scale's f16 bits  ->  the float 2^floor(log2(largest scale))
@@ -588,52 +593,74 @@ __global__ void int4_prepack_header_kernel(uint32_t *header, uint32_t groups)
     header[g] = (uint32_t)(127 + es) << 23;
 }
 
-// grid = (groups, chunks): the codes of 64 weight rows x 128 columns, regrouped per column and 32 k,
-// and the chunk's scales (normalised by the group's power of two) and zeros.
+// Codes.  grid = (groups, ceil(chunks / 8)), 256 threads: 32 threads per chunk of 64 weight rows x 128
+// columns.  Thread (h, wc) reads the 32 words that hold rows 32 h .. 32 h + 31 of columns
+// 8 wc .. 8 wc + 7 (a half warp reads 64 contiguous bytes per row), transposes the 32 x 8 nibbles in
+// registers and writes each column's 16 bytes (32 consecutive k, word i = k 8i .. 8i + 7 in nibbles
+// 0,4,1,5,2,6,3,7): 128 contiguous bytes per thread.
 __global__ void __launch_bounds__(256)
-int4_prepack_kernel(const uint32_t *__restrict__ codes, const uint16_t *__restrict__ scales,
-                    const uint16_t *__restrict__ zeros, unsigned char *__restrict__ packed, uint32_t N, uint32_t K,
-                    uint32_t nchunks, uint32_t header_bytes)
+int4_prepack_codes_kernel(const uint32_t *__restrict__ codes, unsigned char *__restrict__ packed, uint32_t N, uint32_t K,
+                          uint32_t nchunks, uint32_t header_bytes)
 {
-    const uint32_t g = blockIdx.x, c = blockIdx.y, tid = threadIdx.x;
+    const uint32_t g = blockIdx.x, c = blockIdx.y * 8 + (threadIdx.x >> 5);
+    if (c >= nchunks) return;
+    const uint32_t t = threadIdx.x & 31, h = t >> 4, wc = t & 15;
     unsigned char *dst = packed + header_bytes + ((size_t)g * nchunks + c) * kSxChunkBytes;
-    const uint32_t h = tid >> 7, t = tid & 127, n = g * 128 + t;
-    uint32_t words[4];
+    const uint32_t kbase = c * kSxChunkK + h * 32;
+    const size_t word0 = ((size_t)g * 128 + wc * 8) >> 3;           // N is a multiple of 128: rows start on words
+    const size_t row_words = N >> 3;
+    uint32_t in[32];
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        uint32_t w = 0;
+    for (int r = 0; r < 32; r++) in[r] = kbase + r < K ? __ldg(codes + (size_t)(kbase + r) * row_words + word0) : 0u;
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const uint32_t k = c * kSxChunkK + h * 32 + 8 * i + j;
-            uint32_t code = 0;
-            if (k < K) {
-                const size_t flat = (size_t)k * N + n;
-                code = (codes[flat >> 3] >> (4 * (flat & 7))) & 0xFu;
+    for (int j = 0; j < 8; j++) {                                   // column 8 wc + j
+        uint32_t out[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const int pos = (q >> 1) + 4 * (q & 1);              // k0 k1 k2 k3 ... -> nibbles 0 4 1 5 2 6 3 7
+                w |= ((in[8 * i + q] >> (4 * j)) & 0xFu) << (4 * pos);
             }
-            const int pos = (j >> 1) + 4 * (j & 1);          // k0 k1 k2 k3 ... -> nibbles 0 4 1 5 2 6 3 7
-            w |= code << (4 * pos);
+            out[i] = w;
         }
-        words[i] = w;
+        *reinterpret_cast<uint4 *>(dst + (h * 128 + wc * 8 + j) * 16) = make_uint4(out[0], out[1], out[2], out[3]);
     }
-    *reinterpret_cast<uint4 *>(dst + (h * 128 + t) * 16) = make_uint4(words[0], words[1], words[2], words[3]);
-    if (tid < kSxChunkK) {
-        const uint32_t k = c * kSxChunkK + tid;
-        uint32_t sb = 0, zb = 0;
-        if (k < K) {
-            const size_t gi = (size_t)k * (N / 128) + g;
-            sb = scales[gi];
-            zb = zeros[gi];
-        }
-        // Rows whose codes sit four bits up in the A operand (k % 8 in 2, 3, 6, 7) carry 1/16 in
-        // their scale and 16 in their zero: powers of two, exact unless the value leaves the f16
-        // range.  A constant row (scale 0) keeps its value as it is: its B is 0 and the expander
-        // threads add it in f32.
+}
+
+// Scales and zeros.  grid = (ceil(groups / 32), chunks), 256 threads: the chunk's 64 rows of 32 adjacent
+// groups are read row by row (64 contiguous bytes per plane and row), turned in shared memory, and
+// written as each group's 64 scales and 64 zeros (128 contiguous bytes each).
+//
+// Rows whose codes sit four bits up in the A operand (k % 8 in 2, 3, 6, 7) carry 1/16 in their
+// scale and 16 in their zero: powers of two, exact unless the value leaves the f16 range.  A
+// constant row (scale 0) keeps its value as it is: the kernels add it apart.
+__global__ void __launch_bounds__(256)
+int4_prepack_meta_kernel(const uint16_t *__restrict__ scales, const uint16_t *__restrict__ zeros,
+                         unsigned char *__restrict__ packed, uint32_t N, uint32_t K, uint32_t nchunks, uint32_t header_bytes)
+{
+    __shared__ uint16_t ss[64][33], zs[64][33];
+    const uint32_t groups = N / 128, g0 = blockIdx.x * 32, c = blockIdx.y;
+    for (uint32_t i = threadIdx.x; i < 64 * 32; i += 256) {
+        const uint32_t kk = i >> 5, gi = i & 31, k = c * kSxChunkK + kk, g = g0 + gi;
+        uint16_t sb = 0, zb = 0;
+        if (k < K && g < groups) { sb = scales[(size_t)k * groups + g]; zb = zeros[(size_t)k * groups + g]; }
+        ss[kk][gi] = sb;
+        zs[kk][gi] = zb;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < 32 * 64; i += 256) {
+        const uint32_t gi = i >> 6, kk = i & 63, g = g0 + gi;
+        if (g >= groups) continue;
+        const uint32_t sb = ss[kk][gi], zb = zs[kk][gi];
         const float es = reinterpret_cast<const float *>(packed)[g];                  // 2^E_s
         float sn = __half2float(__ushort_as_half((unsigned short)sb)) / es;
         float zn = __half2float(__ushort_as_half((unsigned short)zb));
-        if ((tid & 2) && (sb & 0x7fffu) != 0u) { sn *= 0.0625f; zn *= 16.f; }
-        reinterpret_cast<__half *>(dst + kSxCodeBytes)[tid] = __float2half_rn(sn);
-        reinterpret_cast<__half *>(dst + kSxCodeBytes + 128)[tid] = __float2half_rn(zn);
+        if ((kk & 2) && (sb & 0x7fffu) != 0u) { sn *= 0.0625f; zn *= 16.f; }
+        unsigned char *dst = packed + header_bytes + ((size_t)g * nchunks + c) * kSxChunkBytes + kSxCodeBytes;
+        reinterpret_cast<__half *>(dst)[kk] = __float2half_rn(sn);
+        reinterpret_cast<__half *>(dst + 128)[kk] = __float2half_rn(zn);
     }
 }
 
@@ -662,11 +689,14 @@ int run_int4_prepack(cudaStream_t stream, const uint32_t *codes, const uint16_t 
     const size_t hb = sx_header_bytes(N);
     int rc = check_cuda(cudaMemsetAsync(packed, 0, hb, stream), "int4 prepack header");
     if (rc) return rc;
-    int4_prepack_smax_kernel<<<groups, 128, 0, stream>>>(scales, reinterpret_cast<uint32_t *>(packed), groups, K);
+    int4_prepack_smax_kernel<<<(K + 63) / 64, 256, 0, stream>>>(scales, reinterpret_cast<uint32_t *>(packed), groups, K);
     count_launch();
     int4_prepack_header_kernel<<<(groups + 127) / 128, 128, 0, stream>>>(reinterpret_cast<uint32_t *>(packed), groups);
     count_launch();
-    int4_prepack_kernel<<<dim3(groups, nchunks), 256, 0, stream>>>(codes, scales, zeros, packed, N, K, nchunks, (uint32_t)hb);
+    int4_prepack_codes_kernel<<<dim3(groups, (nchunks + 7) / 8), 256, 0, stream>>>(codes, packed, N, K, nchunks, (uint32_t)hb);
+    count_launch();
+    int4_prepack_meta_kernel<<<dim3((groups + 31) / 32, nchunks), 256, 0, stream>>>(scales, zeros, packed, N, K, nchunks,
+                                                                                  (uint32_t)hb);
     count_launch();
     return check_cuda(cudaGetLastError(), "int4 prepack");
 }

@@ -4,13 +4,13 @@
 // (internal/kernels/quant.go:195-243).
 //
 // The product is HBM-bound on the quants (one byte per weight).  A CTA of 256 threads owns 256
-// columns and a range of K: thread (ty, tx) streams rows k = ty, ty + 8, ... of columns 8 tx .. 8 tx + 7,
-// one 8-byte load per row (a warp reads 256 contiguous bytes), with up to 8 activation rows'
+// columns and a range of K: thread (ty, tx) streams rows k = ty, ty + 16, ... of columns 16 tx .. 16 tx + 15,
+// one 16-byte load per row (a half warp reads 256 contiguous bytes), with up to 4 activation rows'
 // accumulators in registers.  An int8 becomes a float by a byte permute into the mantissa of 2^23
-// and one subtraction, exactly.  Partial sums meet in shared memory (the 8 row phases of a CTA) and
+// and one subtraction, exactly.  Partial sums meet in shared memory (the 16 row phases of a CTA) and
 // then across the CTAs of a thread-block cluster (the K splits of a column tile) through
 // distributed shared memory, in a fixed order: deterministic, no workspace, no atomics.  More than
-// 8 activation rows run as passes of 8.  Arithmetic is f32 throughout (q s rounded once, then one
+// 4 activation rows run as passes of 4.  Arithmetic is f32 throughout (q s rounded once, then one
 // fused multiply-add per term), so the only difference from the reference kernels is the order of
 // the sums.
 //
@@ -26,8 +26,8 @@ namespace ab {
 
 static constexpr int kI8Threads = 256;
 static constexpr int kI8Cols = 256;          // columns per CTA
-static constexpr int kI8Phases = 8;          // row phases per CTA (threadIdx / 32)
-static constexpr int kI8MaxRows = 8;         // activation rows per pass
+static constexpr int kI8Phases = 16;         // row phases per CTA (threadIdx / 16)
+static constexpr int kI8MaxRows = 4;         // activation rows per pass
 static constexpr int kI8MaxSplits = 8;       // K splits of a column tile = cluster size
 
 __device__ __forceinline__ float i8_scale(const __half *bs, uint64_t flat)
@@ -63,66 +63,73 @@ __device__ __forceinline__ void i8_unpack4(uint32_t w, float (&f)[4])
 }
 
 // grid = (ceil(N / 256), splits), cluster = (1, splits, 1).  MR activation rows (m0 .. m0 + MR - 1).
+// Thread (ty, tx): tx = threadIdx % 16 owns columns 16 tx .. 16 tx + 15 (one 16-byte load per row, a
+// half warp reads 256 contiguous bytes), ty = threadIdx / 16 the rows k = ty, ty + 16, ...; eight rows
+// (four for MR = 4) are in flight per thread, about 10 MB over the device.
 template <int MR>
 __global__ void __launch_bounds__(kI8Threads)
 int8_rows_kernel(const float *__restrict__ a, const int8_t *__restrict__ bq, const __half *__restrict__ bs,
                  float *__restrict__ out, uint32_t N, uint32_t K, uint32_t kc, uint32_t m0)
 {
-    __shared__ float part[MR][kI8Cols];          // the CTA's sums over its 8 row phases
+    __shared__ float part[MR][kI8Cols];          // the CTA's sums over its 16 row phases
     cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const uint32_t col = blockIdx.x * kI8Cols + tx * 8;
+    constexpr int kFlight = MR <= 2 ? 8 : 4;
+    const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const uint32_t col = blockIdx.x * kI8Cols + tx * 16;
     const uint32_t kbeg = blockIdx.y * kc, kend = min(K, kbeg + kc);
-    const bool on = col < N;                     // N is a multiple of 32: 8 columns are all in or all out
-    float acc[MR][8];
+    const bool on = col < N;                     // N is a multiple of 32: 16 columns are all in or all out
+    float acc[MR][16];
 #pragma unroll
     for (int m = 0; m < MR; m++)
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc[m][j] = 0.f;
+        for (int j = 0; j < 16; j++) acc[m][j] = 0.f;
     if (on) {
         const float *ar = a + (size_t)m0 * K;
-        // four rows in flight per thread
-        for (uint32_t k = kbeg + ty; k < kend; k += 4 * kI8Phases) {
-            uint2 q[4];
-            float s[4];
+        for (uint32_t k = kbeg + ty; k < kend; k += kFlight * kI8Phases) {
+            uint4 q[kFlight];
+            float s[kFlight];
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < kFlight; u++) {
                 const uint32_t kk = k + u * kI8Phases;
-                q[u] = make_uint2(0u, 0u);
+                q[u] = make_uint4(0u, 0u, 0u, 0u);
                 s[u] = 0.f;
                 if (kk < kend) {
                     const uint64_t flat = (uint64_t)kk * N + col;
-                    q[u] = __ldg(reinterpret_cast<const uint2 *>(bq + flat));
+                    q[u] = __ldg(reinterpret_cast<const uint4 *>(bq + flat));
                     s[u] = i8_scale(bs, flat);
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < kFlight; u++) {
                 const uint32_t kk = k + u * kI8Phases;
                 if (kk < kend) {
-                    float w[8], lo[4], hi[4];
-                    i8_unpack4(q[u].x, lo);
-                    i8_unpack4(q[u].y, hi);
+                    float w[16];
+                    const uint32_t words[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
 #pragma unroll
-                    for (int j = 0; j < 4; j++) { w[j] = lo[j] * s[u]; w[4 + j] = hi[j] * s[u]; }
+                    for (int i = 0; i < 4; i++) {
+                        float f[4];
+                        i8_unpack4(words[i], f);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) w[4 * i + j] = f[j] * s[u];
+                    }
 #pragma unroll
                     for (int m = 0; m < MR; m++) {
                         const float av = __ldg(ar + (size_t)m * K + kk);
 #pragma unroll
-                        for (int j = 0; j < 8; j++) acc[m][j] = fmaf(av, w[j], acc[m][j]);
+                        for (int j = 0; j < 16; j++) acc[m][j] = fmaf(av, w[j], acc[m][j]);
                     }
                 }
             }
         }
     }
-    // the CTA's sums over its 8 phases, added in phase order
+    // the CTA's sums over its 16 phases, added in phase order
     for (int p = 0; p < kI8Phases; p++) {
         if ((int)ty == p) {
 #pragma unroll
             for (int m = 0; m < MR; m++)
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    float &dst = part[m][tx * 8 + j];
+                for (int j = 0; j < 16; j++) {
+                    float &dst = part[m][tx * 16 + j];
                     dst = p == 0 ? acc[m][j] : dst + acc[m][j];
                 }
         }
@@ -178,11 +185,11 @@ static int launch_int8(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     const int8_t *bq = ptr<const int8_t>(l, 1);
     const __half *bs = ptr<const __half>(l, 2);
     float *out = ptr<float>(l, 3);
-    if (N % 32 != 0 || reinterpret_cast<uintptr_t>(bq) % 8) {
+    if (N % 32 != 0 || reinterpret_cast<uintptr_t>(bq) % 16) {
         const uint64_t mn = (uint64_t)M * N;
         int8_generic_kernel<<<(unsigned)((mn + 127) / 128), 128, 0, l.stream>>>(a, bq, bs, out, M, N, K);
         count_launch();
-        note_selection("%s: one thread per output (N=%u is not a multiple of 32, or the quants are not 8-byte "
+        note_selection("%s: one thread per output (N=%u is not a multiple of 32, or the quants are not 16-byte "
                        "aligned)", name, N);
         return check_cuda(cudaGetLastError(), name);
     }
@@ -195,14 +202,13 @@ static int launch_int8(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     for (uint32_t m0 = 0; m0 < M;) {
         const uint32_t left = M - m0;
         int rc;
-        if (left >= 8) { rc = launch_rows<8>(l.stream, a, bq, bs, out, N, K, splits, kc, m0); m0 += 8; }
-        else if (left >= 4) { rc = launch_rows<4>(l.stream, a, bq, bs, out, N, K, splits, kc, m0); m0 += 4; }
+        if (left >= 4) { rc = launch_rows<4>(l.stream, a, bq, bs, out, N, K, splits, kc, m0); m0 += 4; }
         else if (left >= 2) { rc = launch_rows<2>(l.stream, a, bq, bs, out, N, K, splits, kc, m0); m0 += 2; }
         else { rc = launch_rows<1>(l.stream, a, bq, bs, out, N, K, splits, kc, m0); m0 += 1; }
         if (rc) return rc;
     }
-    note_selection("%s: int8 streaming kernel (8-byte loads, f32 arithmetic), %u column tiles of 256 x a cluster of "
-                   "%u K splits of %u rows, passes of up to 8 activation rows", name, tiles, splits, kc);
+    note_selection("%s: int8 streaming kernel (16-byte loads, f32 arithmetic), %u column tiles of 256 x a cluster of "
+                   "%u K splits of %u rows, passes of up to 4 activation rows", name, tiles, splits, kc);
     return AB_OK;
 }
 

@@ -205,6 +205,93 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
     }
 }
 
+// The greedy token of a vocabulary split by columns over `parts` ranks (a tensor-parallel lm_head).
+// ArgmaxShard: this rank's logits [rows][width] -> pairs [rows][parts][2] f32 where slot `rank` holds
+// (largest logit, its index in the WHOLE vocabulary as a float) and every other slot is zero, so the
+// element-wise sum of all ranks' pairs (x + 0 = x exactly) is the gather of their slots: 8 bytes per
+// rank and row cross NVLink instead of the padded logits.  ArgmaxMerge picks the largest value,
+// the lowest index among equals: the row's SampleArgmax over the unsplit logits
+// (internal/kernels/sample.go), since every rank applies the same rule to its columns.
+__global__ void __launch_bounds__(256) argmax_shard_kernel(const float *__restrict__ logits, float *__restrict__ pairs,
+                                                           uint32_t width, uint32_t parts, uint32_t rank, uint32_t first)
+{
+    __shared__ float bv[8];
+    __shared__ uint32_t bi[8];
+    pdl_enter();
+    const size_t base = (size_t)blockIdx.x * width;
+    float v = -3.4e38f;
+    uint32_t idx = 0;
+    for (uint32_t i = threadIdx.x; i < width; i += 256) {
+        float x = logits[base + i];
+        if (x > v) { v = x; idx = i; }
+    }
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, sh);
+        uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, sh);
+        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = v; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    float *row = pairs + (size_t)blockIdx.x * parts * 2;
+    for (uint32_t i = threadIdx.x; i < parts * 2; i += 256)
+        if (i / 2 != rank) row[i] = 0.f;
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++)
+            if (bv[w] > v || (bv[w] == v && bi[w] < idx)) { v = bv[w]; idx = bi[w]; }
+        row[2 * rank] = v;
+        row[2 * rank + 1] = (float)(first + idx);        // exact: the vocabulary is below 2^24
+    }
+}
+
+__global__ void argmax_merge_kernel(const float *__restrict__ pairs, uint32_t *__restrict__ out, uint32_t rows,
+                                    uint32_t parts)
+{
+    pdl_enter();
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const float *row = pairs + (size_t)r * parts * 2;
+    float v = row[0];
+    uint32_t idx = (uint32_t)row[1];
+    for (uint32_t s = 1; s < parts; s++) {
+        const float ov = row[2 * s];
+        const uint32_t oi = (uint32_t)row[2 * s + 1];
+        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    out[r] = idx;
+}
+
+int launch_argmax_shard(Launch &l)
+{   // logits, pairs; {Width, Rows, Parts, Rank, First, 0, 0, 0}
+    if (l.query_ws) { l.ws_need = 0; return AB_OK; }
+    const uint32_t width = u32_at(l.u, 0), rows = u32_at(l.u, 4), parts = u32_at(l.u, 8), rank = u32_at(l.u, 12),
+                   first = u32_at(l.u, 16);
+    if (parts == 0 || rank >= parts || (uint64_t)first + width > (1u << 24))
+        return fail(AB_ERR_INVALID, "ArgmaxShard: Parts=%u Rank=%u First=%u Width=%u; indices are carried as floats "
+                    "and stay below 2^24", parts, rank, first, width);
+    if (l.len[0] < (uint64_t)rows * width || l.len[1] < (uint64_t)rows * parts * 2)
+        return fail(AB_ERR_INVALID, "ArgmaxShard: Rows=%u Width=%u Parts=%u; logits[%u] pairs[%u]", rows, width, parts,
+                    l.len[0], l.len[1]);
+    if (rows == 0) return AB_OK;
+    cudaError_t e = launch_dependent(argmax_shard_kernel, dim3(rows), dim3(256), 0, l.stream, ptr<const float>(l, 0),
+                                     ptr<float>(l, 1), width, parts, rank, first);
+    count_launch();
+    return check_cuda(e, "ArgmaxShard");
+}
+
+int launch_argmax_merge(Launch &l)
+{   // pairs, out; {Rows, Parts, 0, 0}
+    if (l.query_ws) { l.ws_need = 0; return AB_OK; }
+    const uint32_t rows = u32_at(l.u, 0), parts = u32_at(l.u, 4);
+    if (parts == 0 || l.len[0] < (uint64_t)rows * parts * 2 || l.len[1] < rows)
+        return fail(AB_ERR_INVALID, "ArgmaxMerge: Rows=%u Parts=%u; pairs[%u] out[%u]", rows, parts, l.len[0], l.len[1]);
+    if (rows == 0) return AB_OK;
+    cudaError_t e = launch_dependent(argmax_merge_kernel, dim3((rows + 63) / 64), dim3(64), 0, l.stream,
+                                     ptr<const float>(l, 0), ptr<uint32_t>(l, 1), rows, parts);
+    count_launch();
+    return check_cuda(e, "ArgmaxMerge");
+}
+
 int launch_sample_argmax(Launch &l)
 {   // logits, out; SampleDims{Vocab,Rows}; rows = len(out), one reference workgroup per row
     if (l.query_ws) { l.ws_need = 0; return AB_OK; }

@@ -322,16 +322,20 @@ class DecodeEngine:
         self.proj = z(B, d)
         self.gate, self.up, self.act = z(B, len(sh.ffn)), z(B, len(sh.ffn)), z(B, len(sh.ffn))
         self.logits_local = z(B, len(sh.vocab))
-        self.logits = z(B, cfg.vocab) if sh.tp > 1 else self.logits_local
+        # with the vocabulary split over ranks the step exchanges each rank's (largest logit,
+        # index) per row, not the logits; full_logits() gathers them when a caller wants them
+        self.logits = self.logits_local if sh.tp == 1 else None
+        self.top_pairs = z(B, sh.tp, 2)          # every rank's (value, index) per row, after the exchange
+        self._my_pairs = z(B, sh.tp, 2)          # this rank's slot filled, the others zero
         self.next_tokens = z(B, dt=I32)
         self._proj = [self.proj, self.proj]      # where wo and down write their partial results
         if sh.tp > 1 and collective == "peer":
             # the row-parallel products write straight into this rank's peer buffer: two regions
             # used alternately (wo, down), a third for the vocabulary logits
             from .peer import PeerAllReduce
-            self._peer = PeerAllReduce(4, dev, group, regions=(B * d, B * d, B * cfg.vocab))
+            self._peer = PeerAllReduce(4, dev, group, regions=(B * d, B * d, B * sh.tp * 2))
             self._proj = [self._peer.region(0).view(B, d), self._peer.region(1).view(B, d)]
-            self.logits_padded = self._peer.region(2).view(B, cfg.vocab)
+            self._my_pairs = self._peer.region(2).view(B, sh.tp, 2)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.overlap = True          # run the independent linears of a layer side by side
         self._side: List[torch.cuda.Stream] = []
@@ -539,21 +543,37 @@ class DecodeEngine:
         add_norm(self.model.g_final, 1)
         self._linear(self.h, self.model.lm_head_p if self.use_packed else self.model.lm_head, self.logits_local)
         if self.shard.tp > 1:
-            # each rank owns a column range of the vocabulary: place it in a zeroed full-width
-            # buffer and sum across ranks (x + 0 = x exactly), then every rank takes the argmax
+            # each rank owns a column range of the vocabulary: it reduces its columns to one (largest
+            # logit, index) pair per row, the ranks exchange the pairs (a sum over slots the others
+            # left zero: 8 bytes per rank and row), and every rank merges them by SampleArgmax's rule
+            tp, vr = self.shard.tp, self.shard.vocab
+            L("ArgmaxShard", [self.logits_local, self._my_pairs],
+              _u("<IIIIIIII", len(vr), B, tp, self.shard.rank, vr.start, 0, 0, 0))
             if self._peer is not None:
-                self.logits_padded.zero_()
-                self.logits_padded[:, self.shard.vocab.start:self.shard.vocab.stop].copy_(self.logits_local)
-                self._peer.all_reduce_region(2, self.logits)
+                self._peer.all_reduce_region(2, self.top_pairs)
                 self._count += 1
             else:
-                self.logits.zero_()
-                self.logits[:, self.shard.vocab.start:self.shard.vocab.stop].copy_(self.logits_local)
-                self._all_reduce(self.logits)
-        L("SampleArgmax", [self.logits, self.next_tokens], _u("<IIII", cfg.vocab, B, 0, 0))
+                self.top_pairs.copy_(self._my_pairs)
+                self._all_reduce(self.top_pairs)
+            L("ArgmaxMerge", [self.top_pairs, self.next_tokens], _u("<IIII", B, tp, 0, 0))
+        else:
+            L("SampleArgmax", [self.logits, self.next_tokens], _u("<IIII", cfg.vocab, B, 0, 0))
         self.launches_per_step = self._count                      # dispatches by kernel name
         self.kernel_launches_per_step = count() - kernels0        # CUDA kernels they launched
         self._final_x = x
+
+    def full_logits(self) -> torch.Tensor:
+        """The last step's logits over the whole vocabulary [batch, vocab].  With the vocabulary
+        split over ranks this is a collective (every rank calls it) outside the recorded step."""
+        if self.shard.tp == 1:
+            return self.logits_local
+        import torch.distributed as dist
+        widths = {len(Shard.plan(self.cfg, self.shard.tp, r).vocab) for r in range(self.shard.tp)}
+        if len(widths) != 1:
+            raise ValueError("full_logits: the ranks' vocabulary shards differ in width")
+        parts = [torch.empty_like(self.logits_local) for _ in range(self.shard.tp)]
+        dist.all_gather(parts, self.logits_local.contiguous(), group=self.group)
+        return torch.cat(parts, dim=1)
 
     def prepare(self):
         if self.cfg.cache_dtype == torch.float16 and not hasattr(self, "_k16"):

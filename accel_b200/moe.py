@@ -35,6 +35,7 @@ class ExpertWeights:
     zeros: torch.Tensor
     K: int
     N: int
+    packed: Optional[torch.Tensor] = None     # the experts' load-time prepacks, end to end (CUDA only)
 
 
 def expert_range(experts: int, world: int, rank: int) -> range:
@@ -60,6 +61,7 @@ class ExpertParallelFFN:
         self.device = torch.device(device)
         self.local = expert_range(experts, self.world, self.rank)
         self._init_dev = self.device if init_on_device else torch.device("cpu")
+        self.use_packed = True         # False: the kernel over quant.Int4Quantize's planes as they are
         if quantize is None:
             from . import quant
             quantize = quant.int4_quantize_device
@@ -76,13 +78,22 @@ class ExpertParallelFFN:
             w = (torch.randn(K, N, generator=g, device=self._init_dev) * std).to(self.device)
             planes.append(quantize(w))
         cat = lambda i: torch.cat([p[i].reshape(-1) for p in planes])
-        return ExpertWeights(cat(0), cat(1), cat(2), K, N)
+        packed = None
+        if self.device.type == "cuda" and self.ops is rt and N % 128 == 0 and K % 4 == 0:
+            # the permutation the tcgen05 tile kernel streams (each expert's matrix on its own)
+            from . import quant
+            packed = torch.cat([quant.int4_prepack(c, s_, z, K, N).view(torch.uint8).reshape(-1) for c, s_, z in planes])
+        return ExpertWeights(cat(0), cat(1), cat(2), K, N, packed)
 
     # -- the pieces, separately testable ---------------------------------------------------
     def _grouped(self, x, w: ExpertWeights, counts, out):
         n_local = len(self.local)
         offsets = torch.zeros(n_local + 1, dtype=I32, device=x.device)
         self.ops.launch("SegmentOffsets", [counts, offsets], rt.segment_dims(n_local))
+        if w.packed is not None and self.use_packed:
+            self.ops.launch("GroupedMatMulInt4Packed", [x, w.packed.view(I32), offsets, out],
+                            rt.grouped_tiled_dims(n_local, x.shape[0], w.K, w.N))
+            return out
         self.ops.launch("GroupedMatMulInt4", [x, w.codes, w.scales, w.zeros, offsets, out],
                         rt.grouped_tiled_dims(n_local, x.shape[0], w.K, w.N))
         return out

@@ -193,6 +193,8 @@ def run_linear(args):
     torch.cuda.set_device(0)
     torch.manual_seed(7)
     nm = max(2, min(8, (1 << 30) // (K * N // 2)))
+    if args.int8:
+        return run_linear_int8(args, M, K, N, nm)
     mats = [quant.int4_quantize_device(torch.randn(K, N, device=dev) * 0.02) for _ in range(nm)]
     a = torch.randn(M, K, device=dev)
     out = torch.empty(M, N, device=dev)
@@ -233,6 +235,55 @@ def run_linear(args):
                       "bytes": nbytes, "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / peak,
                       "tflops": 2.0 * M * K * N / us / 1e6, "peak_source": src, "matrices_rotated": nm,
                       "kernel": rt.last_selection()}))
+
+
+def run_linear_int8(args, M, K, N, nm):
+    """The int8 path's product (quant.Int8Quantize weights, f32 activations) timed like run_linear."""
+    import numpy as np
+    import torch
+
+    from accel_b200 import runtime as rt
+    dev = "cuda:0"
+    rng = np.random.default_rng(7)
+    mats = []
+    for _ in range(nm):
+        # quants and scales of the right shape and range; the time does not depend on the values
+        q = torch.from_numpy(rng.integers(-127, 128, (K, N), dtype=np.int8)).to(dev)
+        sc = (torch.rand(K * N // 32, device=dev) * 0.01 + 0.001).half()
+        mats.append((q, sc))
+    a = torch.randn(M, K, device=dev)
+    out = torch.empty(M, N, device=dev)
+    name = "QuantMatMulTiledF32" if M > 1 else "QuantMatVecF32"
+    u = rt.gemm_dims(M, N, K)
+
+    def body():
+        for m in mats:
+            rt.launch(name, [a, *m, out], u)
+
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        body()
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            body()
+    torch.cuda.current_stream().wait_stream(s)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        g.replay()
+    e1.record()
+    e1.synchronize()
+    us = e0.elapsed_time(e1) / (10 * nm) * 1e3
+    nbytes = K * N + (K * N // 32) * 2 + M * K * 4 + M * N * 4
+    peak, src = measured_peaks()
+    print(json.dumps({"metric": "int8 linear", "shape": {"M": M, "K": K, "N": N}, "us": us, "bytes": nbytes,
+                      "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / peak, "peak_source": src,
+                      "matrices_rotated": nm, "kernel": rt.last_selection()}))
 
 
 def run_attention(args):
@@ -506,7 +557,7 @@ def run_b200(args):
         engine.set_inputs(first)
         engine.run_step()
         torch.cuda.synchronize()
-        tp_logits = engine.logits.clone()
+        tp_logits = engine.full_logits().clone()
         tp_ids = engine.next_tokens.clone()
         if rank == 0:
             m1 = dec.DecodeModel(cfg, dec.Shard.plan(cfg, 1, 0), dev, seed=1234)
@@ -519,7 +570,7 @@ def run_b200(args):
             e1.prepare()
             e1.record_step()
             torch.cuda.synchronize()
-            ref = e1.logits
+            ref = e1.full_logits()
             top2 = torch.topk(ref, 2, dim=1).values
             clear = (top2[:, 0] - top2[:, 1]) > 2e-3 * ref.abs().max()
             tp_parity = {
@@ -773,6 +824,7 @@ def main():
     ap.add_argument("--planes", action="store_true",
                     help="with --linear: read quant.Int4Quantize's three planes as they are (the reference's "
                          "layout) instead of the load-time prepack")
+    ap.add_argument("--int8", action="store_true", help="with --linear: the int8 path (QuantMatVecF32 / QuantMatMulTiledF32)")
     ap.add_argument("--linear", default=None, metavar="M,K,N",
                     help="time one int4 product on its own instead of the decode step")
     args = ap.parse_args()

@@ -108,7 +108,7 @@ def gpu_step_of(sample: "LayerSample", device="cuda:0"):
     eng.prepare()
     eng.record_step()
     torch.cuda.synchronize()
-    return (eng._final_x.cpu().numpy(), eng.logits.cpu().numpy(),
+    return (eng._final_x.cpu().numpy(), eng.full_logits().cpu().numpy(),
             eng.next_tokens.cpu().numpy().astype(np.int64))
 
 

@@ -68,6 +68,27 @@ def launch(name, bindings, uniform=None, lengths=None, workspace=None):
         rows = b[1].numel()
         out = orc.sample_argmax(_np(b[0]).reshape(rows, vocab))
         b[1].copy_(torch.from_numpy(out.view(np.int32)))
+    elif name == "ArgmaxShard":
+        # this rank's columns -> (largest logit, index in the whole vocabulary) in its slot, zeros elsewhere
+        width, rows, parts, rank, first = struct.unpack("<IIIII", u[:20])
+        logits = _np(b[0]).reshape(rows, width)
+        idx = orc.sample_argmax(logits).astype(np.int64)
+        pairs = np.zeros((rows, parts, 2), np.float32)
+        pairs[:, rank, 0] = logits[np.arange(rows), idx]
+        pairs[:, rank, 1] = (first + idx).astype(np.float32)
+        b[1].copy_(torch.from_numpy(pairs).view_as(b[1]))
+    elif name == "ArgmaxMerge":
+        rows, parts = struct.unpack("<II", u[:8])
+        pairs = _np(b[0]).reshape(rows, parts, 2)
+        out = np.zeros(rows, np.int32)
+        for r in range(rows):
+            v, i = pairs[r, 0]
+            for s_ in range(1, parts):
+                ov, oi = pairs[r, s_]
+                if ov > v or (ov == v and oi < i):
+                    v, i = ov, oi
+            out[r] = int(i)
+        b[1].copy_(torch.from_numpy(out))
     elif name == "SegmentOffsets":
         rows = struct.unpack("<I", u[:4])[0]
         b[1].copy_(torch.from_numpy(orc.segment_offsets(_np(b[0], np.uint32)[:rows]).view(np.int32)))

@@ -55,7 +55,7 @@ def test_decode_steps_match_the_oracle(cache_dtype):
             e.set_inputs(tok)
             e.run_step()
             e.lengths_host += 1
-        g_logits, c_logits = gpu.logits.cpu().numpy(), cpu.logits.numpy()
+        g_logits, c_logits = gpu.full_logits().cpu().numpy(), cpu.full_logits().numpy()
         assert_close(g_logits, c_logits, 5e-3, f"logits at step {t}")
         g_next = gpu.next_tokens.cpu().numpy()
         c_next = cpu.next_tokens.numpy()
@@ -123,7 +123,7 @@ def test_fused_support_kernels_equal_the_chain_of_reference_operators(cache):
         tok_f = fused.step(tok_f)
         tok_c = chain.step(tok_c)
         assert np.array_equal(tok_f, tok_c), t
-        assert torch.equal(fused.logits, chain.logits), t
+        assert torch.equal(fused.full_logits(), chain.full_logits()), t
     assert fused.launches_per_step < chain.launches_per_step
     for li in range(cfg.layers):
         assert torch.equal(fused.k_cache[li], chain.k_cache[li])
@@ -151,7 +151,7 @@ def test_prepacked_products_give_the_step_of_the_reference_planes():
     for t in range(steps):
         a = planes.step(tok)
         b = packed.step(tok)
-        la, lb = planes.logits.cpu().numpy(), packed.logits.cpu().numpy()
+        la, lb = planes.full_logits().cpu().numpy(), packed.full_logits().cpu().numpy()
         assert_close(lb, la, 3e-3, f"logits at step {t}")
         top2 = np.sort(la, axis=1)[:, -2:]
         clear = (top2[:, 1] - top2[:, 0]) > 1e-2 * np.abs(la).max()

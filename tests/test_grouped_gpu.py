@@ -96,6 +96,34 @@ def test_int4_grouped_is_the_composition(K, kernel):
     assert_close(got, want, GEMM_TOL, "int4 grouped")
 
 
+@pytest.mark.parametrize("E,K,N,counts", [(4, 256, 384, [70, 0, 129, 1]), (8, 4096, 1024, None), (3, 100, 128, [128, 128, 5]),
+                                          (2, 512, 256, [0, 0])])
+def test_int4_grouped_on_the_prepacked_stream(E, K, N, counts):
+    """GroupedMatMulInt4Packed (the tcgen05 tile kernel, every expert's segment in row blocks of its
+    own) against the reference GroupedMatMul over each expert's dequantized weights: segments that
+    are empty, one row, exact multiples of 128 and ragged."""
+    from accel_b200 import quant
+    rows = 512 if counts is None else int(np.sum(counts))
+    if counts is None:
+        counts = np.random.default_rng(5).multinomial(rows, np.ones(E) / E)
+    counts = np.asarray(counts, np.uint32)
+    x = normal(9, (max(rows, 1), K))[:rows]
+    w = normal(10, (E, K, N), 0.02)
+    w[E - 1, 5, :128] = 0.125                             # a constant group: scale 0, weight = zero point
+    planes = [orc.int4_quantize(w[e]) for e in range(E)]
+    back = np.stack([orc.int4_dequantize(*planes[e], K * N).reshape(K, N) for e in range(E)])
+    f16 = lambda a: torch.from_numpy(a.view(np.float16)).to(DEV)
+    packed = torch.cat([quant.int4_prepack(dev(p[0]), f16(p[1]), f16(p[2]), K, N) for p in planes])
+    off = orc.segment_offsets(counts)
+    out = torch.full((rows, N), float("nan"), device=DEV)
+    runtime.launch("GroupedMatMulInt4Packed", [dev(x), packed, dev(off), out], runtime.grouped_tiled_dims(E, rows, K, N))
+    torch.cuda.synchronize()
+    quant.int4_stream_check()
+    if rows:
+        assert "grouped int4 tile kernel on tcgen05" in runtime.last_selection()
+        assert_close(out.cpu().numpy(), orc.grouped_matmul(x, back, off, rows, E, K, N), GEMM_TOL, "int4 grouped, packed")
+
+
 def test_refusals():
     x = torch.zeros(4, 8, device=DEV)
     w = torch.zeros(2, 8, 3, device=DEV)

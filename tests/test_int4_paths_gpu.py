@@ -18,7 +18,7 @@ PATHS = {
     "simt": (["1x4096x1024", "3x512x384"], "row kernel"),
     "mma": (["5x4096x1024", "16x512x384", "20x256x128"], "m16n8k16"),
     "batch": (["1x4096x1024", "16x4096x11008", "16x1024x384", "20x4096x512", "3x48x640"], "cluster"),
-    "tc": (["16x512x256", "128x4096x1024", "300x512x256"], "tcgen05 kernel"),
+    "tc": (["16x512x256", "128x4096x1024", "300x512x256", "5x100x256"], "tcgen05"),
     "tiles": (["16x512x256", "128x4096x1024", "300x512x256", "130x64x128"], "tile kernel"),
 }
 

@@ -76,6 +76,36 @@ def test_argmax_ties_go_to_the_lowest_index():
     assert got[1] == 10 and got[2] == 0 and got[3] == 31999
 
 
+@pytest.mark.parametrize("parts", [2, 4, 8])
+def test_argmax_over_a_vocabulary_split_by_columns_equals_sample_argmax(parts):
+    """The tensor-parallel lm_head's exchange on one GPU: every shard's (largest logit, index)
+    pairs summed slot by slot (what the all-reduce over ranks does, the other slots being zero),
+    merged, against SampleArgmax over the unsplit logits, ties and all."""
+    import struct
+    from accel_b200 import runtime as rt
+    rows, vocab = 16, 32000
+    logits = normal(31, (rows, vocab))
+    logits[3, 100] = logits[3, 31000] = 9.0              # a tie across shards: the lowest index wins
+    logits[4, :] = -1.0                                  # all equal: index 0
+    logits[5, 17] = np.nan                               # a NaN is never the largest
+    logits[5, 18] = 8.0
+    x = torch.from_numpy(logits).to(DEV)
+    want = torch.empty(rows, dtype=torch.int32, device=DEV)
+    rt.launch("SampleArgmax", [x, want], rt.sample_dims(vocab, rows))
+    width = vocab // parts
+    total = torch.zeros(rows, parts, 2, device=DEV)
+    for r in range(parts):
+        shard = x[:, r * width:(r + 1) * width].contiguous()
+        pairs = torch.full((rows, parts, 2), float("nan"), device=DEV)
+        rt.launch("ArgmaxShard", [shard, pairs], struct.pack("<IIIIIIII", width, rows, parts, r, r * width, 0, 0, 0))
+        total += pairs
+    got = torch.empty(rows, dtype=torch.int32, device=DEV)
+    rt.launch("ArgmaxMerge", [total, got], struct.pack("<IIII", rows, parts, 0, 0))
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    assert got[3].item() == 100 and got[4].item() == 0 and got[5].item() == 18
+
+
 def test_casts_round_as_the_reference_does():
     rng = np.random.default_rng(10)
     x = (rng.standard_normal(100000) * np.exp(rng.uniform(-20, 12, 100000))).astype(np.float32)

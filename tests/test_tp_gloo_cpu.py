@@ -33,7 +33,7 @@ def _run_steps(engine, steps, batch):
         engine.lengths_host += 1
         tok = engine.next_tokens.numpy().copy()
         toks.append(tok)
-        logits.append(engine.logits.numpy().copy())
+        logits.append(engine.full_logits().numpy().copy())
     return np.array(toks), np.array(logits)
 
 

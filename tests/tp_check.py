@@ -27,14 +27,14 @@ def run(engine, steps, batch, graph):
         for _ in range(steps):
             engine.run_step()
             toks.append(engine.next_tokens.cpu().numpy().copy())
-            logits.append(engine.logits.cpu().numpy().copy())
+            logits.append(engine.full_logits().cpu().numpy().copy())
             engine.advance_on_device()
     else:
         tok = first
         for _ in range(steps):
             tok = engine.step(tok)
             toks.append(tok.copy())
-            logits.append(engine.logits.cpu().numpy().copy())
+            logits.append(engine.full_logits().cpu().numpy().copy())
     return np.array(toks), np.array(logits)
 
 
