@@ -84,6 +84,7 @@ SYMBOLS = [
     ("ab_alloc", C.c_int, [_P, C.c_int, C.c_size_t, C.c_char_p, C.POINTER(_P)]),
     ("ab_block_bytes", _P, [_P]),
     ("ab_block_device_ptr", _P, [_P]),
+    ("ab_block_import", C.c_int, [_P, _P, C.c_size_t, C.POINTER(_P)]),
     ("ab_block_size", C.c_size_t, [_P]),
     ("ab_block_write", C.c_int, [_P, C.c_size_t, _P, C.c_size_t]),
     ("ab_block_read", C.c_int, [_P, C.c_size_t, _P, C.c_size_t]),

@@ -212,6 +212,7 @@ struct ab_block {
     void *dptr;     // device address (== host address mapping for pinned memory)
     void *hptr;     // host address for AB_MEMORY_HOST_VISIBLE
     std::atomic<int> users{0};     // live executables that name this block (directly or by a slot)
+    bool borrowed = false;         // memory the caller owns (ab_block_import): never freed here
 };
 
 namespace ab { struct Instance; }
@@ -382,7 +383,8 @@ static int run_nodes(ab_exec *e, Instance *in, cudaStream_t s)
             if (rc) return rc;
         } else if (nd.op == AB_OP_COPY) {
             size_t bytes = (size_t)std::min(nd.bind[0].size, nd.bind[1].size);
-            int rc = check_cuda(cudaMemcpyAsync(nd.ptrs[1], nd.ptrs[0], bytes, cudaMemcpyDeviceToDevice, s), "copy node");
+            // (either side may be a host-visible block: the runtime sorts out the direction)
+            int rc = check_cuda(cudaMemcpyAsync(nd.ptrs[1], nd.ptrs[0], bytes, cudaMemcpyDefault, s), "copy node");
             if (rc) return rc;
         } else if (nd.op == AB_OP_HOST_WRITE) {
             size_t bytes = std::min(nd.payload_bytes, (size_t)nd.bind[0].size);
@@ -554,6 +556,24 @@ int ab_alloc(ab_device *d, int kind, size_t bytes, const char *label, ab_block *
     return AB_OK;
 }
 
+int ab_block_import(ab_device *d, void *device_ptr, size_t bytes, ab_block **out)
+{
+    if (!out || !device_ptr || bytes == 0) return fail(AB_ERR_INVALID, "ab_block_import: NULL or empty");
+    int rc = set_device(d);
+    if (rc) return rc;
+    cudaPointerAttributes at{};
+    rc = check_cuda(cudaPointerGetAttributes(&at, device_ptr), "ab_block_import");
+    if (rc) return rc;
+    if (at.type != cudaMemoryTypeDevice || at.device != d->ordinal)
+        return fail(AB_ERR_INVALID, "ab_block_import: the address is not device memory of device %d", d->ordinal);
+    ab_block *b = new (std::nothrow) ab_block();
+    if (!b) return fail(AB_ERR_OOM, "ab_block_import: host allocation failed");
+    b->dev = d; b->kind = AB_MEMORY_DEVICE; b->size = bytes; b->dptr = device_ptr; b->hptr = nullptr; b->borrowed = true;
+    d->live.fetch_add(1);
+    *out = b;
+    return AB_OK;
+}
+
 void *ab_block_bytes(ab_block *b) { return b ? b->hptr : nullptr; }
 void *ab_block_device_ptr(ab_block *b) { return b ? b->dptr : nullptr; }
 size_t ab_block_size(ab_block *b) { return b ? b->size : 0; }
@@ -595,7 +615,9 @@ int ab_block_free(ab_block *b)
                         "them (or rebind their slots) first", b->users.load());
     if (!d->lost.load() && cudaSetDevice(d->ordinal) == cudaSuccess) {
         cudaStreamSynchronize(d->stream);
-        if (b->hptr) cudaFreeHost(b->hptr); else cudaFree(b->dptr);
+        if (b->borrowed) { /* the caller's memory */ }
+        else if (b->hptr) cudaFreeHost(b->hptr);
+        else cudaFree(b->dptr);
     }
     d->live.fetch_sub(1);
     delete b;

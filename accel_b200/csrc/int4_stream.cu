@@ -904,8 +904,10 @@ static bool sx_pdl()
 }
 
 // From how many activation rows the tile kernel (int4_gemm.cu: weights dequantised once per CTA,
-// 128 rows per tile) takes over from passes of 16 rows of the decode kernel.
-static constexpr uint32_t kPackedTileFromRows = 17;
+// 128 rows per tile) takes over from passes of 16 rows of the decode kernel.  Measured at 4096 x
+// 11008: a pass of 16 rows 15.6 us, a wave of tiles 52 us whatever the rows: three passes are
+// cheaper, four are not.
+static constexpr uint32_t kPackedTileFromRows = 49;
 static bool packed_tiles(uint32_t M) { return M >= kPackedTileFromRows; }
 static size_t packed_workspace(uint32_t M, uint32_t K)
 {

@@ -87,18 +87,21 @@ int8_rows_kernel(const float *__restrict__ a, const int8_t *__restrict__ bq, con
         const float *ar = a + (size_t)m0 * K;
         for (uint32_t k = kbeg + ty; k < kend; k += kFlight * kI8Phases) {
             uint4 q[kFlight];
-            float s[kFlight];
+            unsigned short sbits[kFlight];       // raw: converting here would wait for each load in turn
 #pragma unroll
             for (int u = 0; u < kFlight; u++) {
                 const uint32_t kk = k + u * kI8Phases;
                 q[u] = make_uint4(0u, 0u, 0u, 0u);
-                s[u] = 0.f;
+                sbits[u] = 0;
                 if (kk < kend) {
                     const uint64_t flat = (uint64_t)kk * N + col;
                     q[u] = __ldg(reinterpret_cast<const uint4 *>(bq + flat));
-                    s[u] = i8_scale(bs, flat);
+                    sbits[u] = __ldg(reinterpret_cast<const unsigned short *>(bs) + (flat >> 5));
                 }
             }
+            float s[kFlight];
+#pragma unroll
+            for (int u = 0; u < kFlight; u++) s[u] = __half2float(__ushort_as_half(sbits[u]));
 #pragma unroll
             for (int u = 0; u < kFlight; u++) {
                 const uint32_t kk = k + u * kI8Phases;

@@ -373,6 +373,85 @@ class DecodeEngine:
                 cache[rows] = part.to(cache.dtype)
         self.lengths_host[:] = context
 
+    def prefill(self, prompts: np.ndarray, chunk: int = 256) -> float:
+        """Runs the prompts [batch, T] (token ids) through the model and leaves their K/V in the paged
+        cache: the real fill of the context a decode loop starts from.  Every sequence advances
+        `chunk` positions at a time, so a product sees batch x chunk rows of activations (the
+        batch kernels over the same prepacked weights), RoPE and the scatter into the pages are the
+        decode step's fused kernel over those rows, and attention is the paged causal prefill
+        kernel, one launch per sequence and layer (internal/kernels/prefill.go:409: row s sees the
+        positions <= Base + s).  Pages for T positions are reserved here.  The row-parallel
+        products of a sharded model are summed by the process group.  Returns the seconds it took
+        (device time)."""
+        if not (self.use_packed and self.fuse):
+            raise ValueError("prefill runs on the prepacked weights and the fused support kernels")
+        cfg, B, D, d = self.cfg, self.batch, self.cfg.head_dim, self.cfg.d_model
+        self._count = 0
+        prompts = np.asarray(prompts)
+        T = prompts.shape[1]
+        assert prompts.shape[0] == B and T > 0
+        base0 = int(self.lengths_host[0])
+        assert np.all(self.lengths_host == base0), "prefill starts every sequence at the same position"
+        for sq in range(B):
+            self.reserve(sq, base0 + T)
+        self.upload_pages()
+        dev, blk = self.dev, cfg.block
+        f16 = cfg.cache_dtype == torch.float16
+        z = lambda *sh, dt=torch.float32: torch.zeros(sh, dtype=dt, device=dev)
+        S = min(chunk, T)
+        M = B * S
+        x, x2, h, proj = z(M, d), z(M, d), z(M, d), z(M, d)
+        q, k, v = z(M, self.hq * D), z(M, self.hk * D), z(M, self.hk * D)
+        attn, act = z(M, self.hq * D), z(M, len(self.shard.ffn))
+        scale = float(np.float32(1.0) / np.float32(np.sqrt(D)))
+        launch = self.ops.launch
+        pages_of = [self.pages[sq].contiguous() for sq in range(B)]
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for p0 in range(base0, base0 + T, S):
+            s_now = min(S, base0 + T - p0)
+            m = B * s_now
+            pos = p0 + np.arange(s_now)
+            toks = torch.from_numpy(np.ascontiguousarray(prompts[:, p0 - base0:p0 - base0 + s_now]).reshape(-1).astype(np.int32)).to(dev)
+            rows_pos = np.tile(pos, B)                                        # row b * s_now + s -> position
+            slots = np.concatenate([[self.page_rows[sq][p // blk] * blk + p % blk for p in pos] for sq in range(B)])
+            pos_q = torch.from_numpy(np.repeat(rows_pos, self.hq).astype(np.int32)).to(dev)
+            pos_k = torch.from_numpy(np.repeat(rows_pos, self.hk).astype(np.int32)).to(dev)
+            slots_t = torch.from_numpy(slots.astype(np.int32)).to(dev)
+            kv_len = torch.full((1,), p0 + s_now, dtype=I32, device=dev)
+            xa, xb = x[:m], x2[:m]
+            launch("GatherRows", [self.model.embedding, toks, xa], _u("<IIII", m, d, cfg.vocab, 0))
+            norm_u = _u("<IIfI", m, d, cfg.eps, 0)
+            for li, lay in enumerate(self.model.layers):
+                if li == 0:
+                    launch("RMSNorm", [xa, lay.g1, h[:m]], norm_u)
+                else:
+                    self._all_reduce(proj[:m])
+                    launch("AddRMSNorm", [xa, proj[:m], lay.g1, xb, h[:m]], norm_u)
+                    xa, xb = xb, xa
+                w = lay.wqkv
+                launch("QuantMatMulInt4PackedSplit3", [h[:m], w.packed, q[:m], k[:m], v[:m]],
+                       _u("<IIIIIIII", m, w.N, w.K, self.hq * D, self.hk * D, 0, 0, 0))
+                launch("RopeScatterQKVF16" if f16 else "RopeScatterQKV",
+                       [pos_q, pos_k, slots_t, q[:m], k[:m], v[:m], self.k_cache[li], self.v_cache[li]],
+                       _u("<IIIIIIfI", m, self.hq, self.hk, D, D, self.capacity, cfg.rope_base, 0))
+                for sq in range(B):
+                    rows = slice(sq * s_now, (sq + 1) * s_now)
+                    launch("AttentionPrefillPagedF16" if f16 else "AttentionPrefillPaged",
+                           [q[rows], self.k_cache[li], self.v_cache[li], pages_of[sq], kv_len, attn[rows]],
+                           _u("<IIIIIIfI", self.hq, self.hk, D, s_now, p0, blk, scale, 0))
+                self._linear(attn[:m], lay.wo_p, proj[:m])
+                self._all_reduce(proj[:m])
+                launch("AddRMSNorm", [xa, proj[:m], lay.g2, xb, h[:m]], norm_u)
+                xa, xb = xb, xa
+                w = lay.wgu
+                launch("QuantMatMulInt4PackedSwiGLU", [h[:m], w.packed, act[:m]], _u("<IIII", m, w.N, w.K, 0))
+                self._linear(act[:m], lay.wd_p, proj[:m])
+        t1.record()
+        t1.synchronize()
+        self.lengths_host += T
+        return t0.elapsed_time(t1) / 1e3
+
     def step_inputs_host(self, token_ids: np.ndarray) -> np.ndarray:
         """The per-step host buffers for the CURRENT lengths, laid out as `self.inputs` is:
         tokens | positions of q rows | positions of k rows | slots | lengths + 1."""
@@ -643,3 +722,72 @@ class DecodeEngine:
         sequence, K and V, once per KV head, in every layer."""
         e = 2 if self.cfg.cache_dtype == torch.float16 else 4
         return int(self.cfg.layers * 2 * self.hk * self.cfg.head_dim * e * (self.lengths_host + 1).sum())
+
+
+class SeamStep:
+    """The recorded decode step driven through the driver seam, as the reference's device layer drives
+    a backend (internal/driver/plan.go:360-400): the step is recorded once as a plan - a host-write node
+    for the per-step inputs, one dispatch node per kernel, a copy of the sampled ids into a
+    host-visible block - compiled with ab_compile, and every step is set_payload + ab_exec_submit +
+    ab_fence_wait + a read of the host-visible block.  The weights, caches and activations are the
+    engine's own tensors, imported as blocks (the engine keeps them alive).  One GPU: the peer
+    all-reduce of a sharded step is not a registered kernel."""
+
+    def __init__(self, engine: "DecodeEngine", use_graphs: bool = True, max_in_flight: int = 0):
+        from . import driver as drv
+        if engine.shard.tp != 1:
+            raise ValueError("SeamStep records the unsharded step")
+        self.engine, self.drv = engine, drv
+        self.dev = drv.Device(engine.dev.index or 0, use_graphs=use_graphs)
+        self._blocks: dict = {}
+        nodes: list = []
+
+        def operand(t: torch.Tensor):
+            key = (t.data_ptr(), t.numel() * t.element_size())
+            blk = self._blocks.get(key)
+            if blk is None:
+                blk = self.dev.import_ptr(*key)
+                self._blocks[key] = blk
+            return drv.Operand(block=blk, offset=0, size=key[1])
+
+        class Recorder:
+            @staticmethod
+            def launch(name, bindings, uniform=None):
+                nodes.append(drv.Dispatch(name, [operand(t) for t in bindings], uniform))
+
+            @staticmethod
+            def launch_count():
+                return 0
+
+        engine.prepare()
+        n_in = engine.inputs.numel() * 4
+        nodes.append(drv.HostWrite(operand(engine.inputs), bytes(n_in)))
+        ops, engine.ops = engine.ops, Recorder
+        try:
+            engine.record_step()
+        finally:
+            engine.ops = ops
+        self.ids = self.dev.alloc(max(engine.batch * 4, 256), drv.MEMORY_HOST_VISIBLE, "sampled ids")
+        nodes.append(drv.Copy(operand(engine.next_tokens), drv.Operand(block=self.ids, offset=0, size=engine.batch * 4)))
+        self.nodes = len(nodes)
+        self.exe = self.dev.compile(nodes, max_in_flight=max_in_flight)
+        self._out = np.zeros(engine.batch, np.int32)
+
+    def step(self, token_ids: np.ndarray) -> np.ndarray:
+        """Host token ids in, host next-token ids out, through the compiled plan."""
+        e = self.engine
+        self.exe.set_payload(0, e.step_inputs_host(token_ids).astype(np.int32).tobytes())
+        f = self.exe.submit()
+        f.wait()
+        f.free()
+        e.lengths_host += 1
+        return self.ids.read(0, self._out).copy()
+
+    def close(self):
+        self.exe.close()
+        self.ids.free()
+        for b in self._blocks.values():
+            b.free()
+        self._blocks = {}
+        self.dev.close()
+

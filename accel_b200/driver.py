@@ -165,6 +165,13 @@ class Device:
         _lib.check(_lib.lib().ab_alloc(self._h, kind, nbytes, label.encode(), C.byref(h)))
         return Block(self, h)
 
+    def import_ptr(self, device_ptr: int, nbytes: int) -> Block:
+        """A block over device memory the caller owns (a torch tensor's storage, say); the caller
+        keeps that memory alive for as long as a plan names the block."""
+        h = C.c_void_p()
+        _lib.check(_lib.lib().ab_block_import(self._h, C.c_void_p(device_ptr), nbytes, C.byref(h)))
+        return Block(self, h)
+
     def upload(self, arr: np.ndarray, label: str = "") -> Block:
         arr = np.ascontiguousarray(arr)
         b = self.alloc(max(arr.nbytes, 1), MEMORY_DEVICE, label)

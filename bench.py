@@ -512,7 +512,7 @@ def run_b200(args):
     t_setup = time.perf_counter()
     model = dec.DecodeModel(cfg, shard, dev, seed=1234)
     B, ctx = args.batch, args.context
-    total_steps = 2 * (args.steps + args.warmup) + 8
+    total_steps = 3 * (args.steps + args.warmup) + 8
     collective, why = (args.collective if world > 1 else "none"), ""
     engine = None
     if collective == "peer":
@@ -532,12 +532,32 @@ def run_b200(args):
     engine.overlap = not args.no_overlap
     log = (lambda m: print(f"[rank {rank}] {m}", file=sys.stderr, flush=True)) if args.verbose else (lambda m: None)
     log("engine built")
-    engine.fill_context(ctx, seed=7)
-    for s in range(B):
-        engine.reserve(s, ctx + total_steps + 8)
-    engine.upload_pages()
     rng = np.random.default_rng(99)
+    prompts = rng.integers(0, cfg.vocab, (B, ctx))       # seeded random token ids, as config 4 says
     first = rng.integers(0, cfg.vocab, B)
+
+    def fill(eng):
+        """The 2048-token context: a real prefill through the batch kernels and the paged causal
+        prefill attention (--kv-fill prefill), or seeded N(0,1) K/V rows (--kv-fill random)."""
+        info = {"kv_fill": "seeded N(0,1) rows stand in for the prefill (--kv-fill random)"}
+        if args.kv_fill == "prefill":
+            try:
+                secs = eng.prefill(prompts, chunk=args.prefill_chunk)
+                info = {"kv_fill": "prefill of the seeded random prompts through the batch int4 kernels and "
+                                   "AttentionPrefillPaged, %d positions per sequence at a time" % args.prefill_chunk,
+                        "prefill_s": round(secs, 3), "prefill_tok_s": round(B * ctx / secs, 1)}
+            except Exception as e:                 # noqa: BLE001 - said in the JSON line; the run goes on
+                eng.lengths_host[:] = 0
+                eng.fill_context(ctx, seed=7)
+                info = {"kv_fill": f"seeded N(0,1) rows; the prefill failed: {type(e).__name__}: {e}"[:300]}
+        else:
+            eng.fill_context(ctx, seed=7)
+        for s_ in range(B):
+            eng.reserve(s_, ctx + total_steps + 8)
+        eng.upload_pages()
+        return info
+
+    fill_info = fill(engine)
     engine.set_inputs(first)
     log("context filled")
     if args.no_graph:
@@ -562,10 +582,7 @@ def run_b200(args):
         if rank == 0:
             m1 = dec.DecodeModel(cfg, dec.Shard.plan(cfg, 1, 0), dev, seed=1234)
             e1 = dec.DecodeEngine(m1, B, max_context=ctx + total_steps + 16)
-            e1.fill_context(ctx, seed=7)
-            for s_ in range(B):
-                e1.reserve(s_, ctx + total_steps + 8)
-            e1.upload_pages()
+            fill(e1)
             e1.set_inputs(first)
             e1.prepare()
             e1.record_step()
@@ -648,6 +665,28 @@ def run_b200(args):
     e2e_s = max_over_ranks(w1 - w0)
     e2e_value = B * args.steps / e2e_s
 
+    # ---- the same loop through the driver seam (N = 1): the step recorded as a plan (host-write node
+    # for the inputs, a dispatch node per kernel, the ids copied into a host-visible block), compiled
+    # once and driven with set_payload / ab_exec_submit / ab_fence_wait, replayed as a CUDA graph
+    e2e_seam = None
+    if world == 1 and not args.no_seam:
+        try:
+            seam = dec.SeamStep(engine, use_graphs=True)
+            for _ in range(min(args.warmup, 3)):
+                tok = seam.step(tok)
+            torch.cuda.synchronize()
+            s0 = time.perf_counter()
+            for _ in range(args.steps):
+                tok = seam.step(tok)
+            s1 = time.perf_counter()
+            e2e_seam = {"value": B * args.steps / (s1 - s0), "unit": "tok/s", "plan_nodes": seam.nodes,
+                        "h2d_bytes_per_step": engine.h2d_bytes_per_step,
+                        "d2h_bytes_per_step": engine.d2h_bytes_per_step,
+                        "what": "ab_compile once; per step ab_exec_set_payload + ab_exec_submit + ab_fence_wait + "
+                                "a read of the host-visible ids block (use_graphs = 1)"}
+            seam.close()
+        except Exception as e:                     # noqa: BLE001 - reported in the JSON line, the run goes on
+            e2e_seam = {"error": f"{type(e).__name__}: {e}"[:300]}
     log("e2e timed")
     # ---- roofline of the dominant kernel: the paged decode attention (K/V of every cached
     # position, once per KV head), timed alone with events on its launching stream, one launch per
@@ -767,11 +806,11 @@ def run_b200(args):
                        "l2": "inputs larger than L2: each step streams "
                              f"{weight_bytes / 1e9:.2f} GB of int4 weights and "
                              f"{kv_bytes_first / 1e9:.1f} GB of K/V per rank",
-                       "kv_fill": "seeded N(0,1) rows stand in for the 2048-token prefill",
-                       "setup_s": round(t_setup, 1)},
+                       **fill_info, "setup_s": round(t_setup, 1)},
             "e2e": {"value": e2e_value, "unit": "tok/s",
                     "h2d_bytes_per_step": engine.h2d_bytes_per_step,
                     "d2h_bytes_per_step": engine.d2h_bytes_per_step},
+            "e2e_seam": e2e_seam,
             "gpu_launches": gpu_launches,
             "roofline": roofline,
             "step_hbm": {"bytes_per_step_per_rank": weight_bytes + kv_bytes_first,
@@ -806,8 +845,12 @@ def main():
     ap.add_argument("--kv", default="f32", choices=["f32", "f16"],
                     help="KV cache dtype; f32 is what the reference's batched decode kernel reads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kv-fill", default="prefill", choices=["prefill", "random"],
+                    help="how the context's K/V get into the cache before the timed steps")
+    ap.add_argument("--prefill-chunk", type=int, default=256, help="positions per sequence and prefill pass")
     ap.add_argument("--no-tp-parity", action="store_true",
                     help="skip the N-rank against one-rank comparison of the first step (N > 1)")
+    ap.add_argument("--no-seam", action="store_true", help="skip the end-to-end loop through ab_compile / ab_exec_submit")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="keep every operator on one stream")
     ap.add_argument("--force-overlap", action="store_true", help="side-stream overlap at N > 1 too")

@@ -75,6 +75,10 @@ AB_API int ab_lost(ab_device *dev);    /* Device.Lost(): AB_OK or AB_ERR_DEVICE_
 /* driver.Block (internal/driver/driver.go:219-238).  kind: */
 enum { AB_MEMORY_DEVICE = 0, AB_MEMORY_HOST_VISIBLE = 1 };
 AB_API int ab_alloc(ab_device *dev, int kind, size_t bytes, const char *label, ab_block **out);
+/* A block over device memory the caller allocated and keeps owning (weights another runtime loaded,
+ * a framework's tensor): the block can be named by plans like any other; freeing it releases the
+ * handle only.  No accel analogue. */
+AB_API int ab_block_import(ab_device *dev, void *device_ptr, size_t bytes, ab_block **out);
 AB_API void *ab_block_bytes(ab_block *b);         /* Block.Bytes(): NULL for AB_MEMORY_DEVICE    */
 AB_API void *ab_block_device_ptr(ab_block *b);    /* the device address (no accel analogue)      */
 AB_API size_t ab_block_size(ab_block *b);
@@ -229,6 +233,40 @@ AB_API uint64_t ab_launch_count(void);
  *  SwiGLU, ElemAdd   a, b, out                                               none   internal/kernels/elementwise.go:85,22
  *  SampleArgmax      logits f32[rows*vocab], out u32[rows]                   SampleDims{Vocab,Rows}@0,4 (16 B)   internal/kernels/sample.go:50
  *  CastF32ToF16, CastF16ToF32    in, out                                     none   internal/kernels/cast.go:30,38
+ *  AttentionPrefill, AttentionPrefillF16   q f32[QSeq*QHeads*HeadDim], k, v, lengths u32[1], out
+ *                    PrefillDims{QHeads,KVHeads,HeadDim,QSeq,Base,Scale f32}@0..20 (32 B)   internal/kernels/prefill.go:66,225
+ *  AttentionPrefillPaged, AttentionPrefillPagedF16   q, k, v, pages u32[P], lengths u32[1], out
+ *                    PagedPrefillDims{QHeads,KVHeads,HeadDim,QSeq,Base,Block,Scale f32}@0..24 (32 B)
+ *                    internal/kernels/prefill.go:409, pagedprefillf16.go:31.  Query row s sees positions <= Base + s.
+ *  Softmax           x f32[rows*width], out                                 RowDims   internal/kernels/norm.go:95
+ *  ScaleRows         x, factors f32[rows], out                              RowSampleDims{Vocab,Rows,History,Slots}@0..12 (16 B)
+ *                    internal/kernels/rowsample.go:226
+ *  LogitBias         logits, ids u32[rows*Slots], values f32[rows*Slots], out   RowSampleDims   rowsample.go:304
+ *  TopKMaskRows, TopPMaskRows   weights, ks u32[rows] | ps f32[rows], out   RowSampleDims   rowsample.go:42,126
+ *  TopKMask, TopPMask           weights, out                                TopDims{Vocab,K,P f32}@0,4,8 (16 B)   topk.go:59,153
+ *  SampleRows        probs, draws f32[rows], factors f32[rows], out u32[rows]   RowSampleDims   rowsample.go:246
+ *  SampleCategorical probs, draws f32[rows], out u32[rows]                  SampleDims   sample.go:133
+ *  PenaltyClearRows / PenaltyCountRows / PenaltyApplyRows   counts u32[rows*Vocab] / history u32[rows*History],
+ *                    filled u32[rows], counts / logits, counts, repetition f32[rows], presence, frequency, out
+ *                    RowSampleDims   rowsample.go:325,336,356
+ *  PenaltyClear / PenaltyCount / PenaltyApply   counts / history, counts / logits, counts, out
+ *                    PenaltyDims{Vocab,History,Count,Repetition f32,Presence f32,Frequency f32}@0..20 (32 B)   penalty.go:60,98,136
+ *                    Every sampling kernel reproduces the reference's order of sums (128 strided partials and a
+ *                    binary tree; the categorical walk in index order), so ids and masks are bit-exact.
+ *  QuantMatVecInt4Packed, QuantMatMulInt4Packed   a f32, packed u32 words (ab_int4_prepack), out f32   GEMMDims
+ *                    No reference kernel: QuantMatVecInt4 / QuantMatMulInt4 over the load-time prepack of the same
+ *                    matrix.  Up to 48 rows: the tcgen05 decode kernel in passes of 16; beyond: the tcgen05 tile kernel.
+ *  QuantMatMulInt4PackedSplit3   a, packed, out0 f32[M*N1], out1 f32[M*N2], out2 f32[M*(N-N1-N2)]
+ *                    {M,N,K,N1,N2}@0..16 (32 B).  One product whose column ranges land in three matrices (q | k | v).
+ *  QuantMatMulInt4PackedSwiGLU   a, packed, out f32[M*N/2]                  GEMMDims.  The 128-column groups of the packed
+ *                    matrix alternate gate, up; out = SwiGLU(gate, up) (elementwise.go:85) from the epilogue.
+ *  GroupedMatMulInt4Packed   x f32[T*K], packed (Experts prepacked matrices end to end), offsets u32[E+1], out f32[T*N]
+ *                    GroupedTiledDims.  GroupedMatMulInt4 over prepacked experts, on the tcgen05 tile kernel.
+ *  ArgmaxShard       logits f32[rows*Width], pairs f32[rows*Parts*2]        {Width,Rows,Parts,Rank,First}@0..16 (32 B)
+ *  ArgmaxMerge       pairs f32[rows*Parts*2], out u32[rows]                 {Rows,Parts}@0,4 (16 B).  No reference kernels:
+ *                    SampleArgmax over a vocabulary split by columns over Parts ranks; slot Rank of a row's pairs holds
+ *                    (largest logit, its index in the whole vocabulary), the other slots zero, so the sum over ranks is
+ *                    the gather; the merge takes the largest value, the lowest index among equals.
  *  Int4Quantize      w f32[n], packed u32, scales f16, zeros f16            none.  quant.Int4Quantize
  *                    (quant/int4.go:71) run on the device, bit-identical to the host routine.
  *  DecodeStepInputs  sampled u32[B], pages u32[B*MaxPages], tokens u32[B], pos_q u32[B*QHeads], pos_k u32[B*KVHeads],

@@ -175,3 +175,68 @@ def test_tensor_parallel_step_on_the_gpus_matches_one_gpu():
                          env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-3000:])
     assert "OK world=" in out.stdout
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_the_step_through_the_driver_seam_equals_the_direct_step(graphs):
+    """The same step recorded as a plan and driven with ab_compile / set_payload / ab_exec_submit /
+    ab_fence_wait (what the reference's device layer does with a backend) against the engine's own
+    loop: same kernels, same order, so the sampled ids and the logits are equal bit for bit."""
+    cfg = small_cfg()
+    batch, steps = 3, 6
+    engines = []
+    for _ in range(2):
+        model = dec.DecodeModel(cfg, dec.Shard.plan(cfg, 1, 0), DEV, seed=3, std=0.08)
+        e = dec.DecodeEngine(model, batch, max_context=64)
+        e.fill_context(9, seed=4)
+        for s in range(batch):
+            e.reserve(s, 9 + steps + 1)
+        e.upload_pages()
+        engines.append(e)
+    direct, other = engines
+    seam = dec.SeamStep(other, use_graphs=graphs)
+    tok_a = tok_b = np.arange(batch) + 5
+    for t in range(steps):
+        tok_a = direct.step(tok_a)
+        tok_b = seam.step(tok_b)
+        assert np.array_equal(tok_a, tok_b), t
+        assert torch.equal(direct.full_logits(), other.full_logits()), t
+    assert seam.nodes > 10
+    seam.close()
+
+
+@pytest.mark.parametrize("cache_dtype", [torch.float32, torch.float16])
+def test_prefill_leaves_the_cache_a_token_by_token_decode_leaves(cache_dtype):
+    """DecodeEngine.prefill (batch kernels over batch x chunk rows, the paged causal prefill
+    attention) against feeding the same prompt one token at a time through the decode step: the
+    K/V the two leave in the pages agree, and so does the step that follows."""
+    cfg = small_cfg(cache_dtype)
+    batch, T = 3, 23
+    rng = np.random.default_rng(2)
+    prompt = rng.integers(0, cfg.vocab, (batch, T))
+    engines = []
+    for _ in range(2):
+        model = dec.DecodeModel(cfg, dec.Shard.plan(cfg, 1, 0), DEV, seed=3, std=0.08)
+        engines.append(dec.DecodeEngine(model, batch, max_context=64))
+    stepwise, bulk = engines
+    for s in range(batch):
+        stepwise.reserve(s, T + 2)
+    stepwise.upload_pages()
+    for t in range(T):
+        stepwise.step(prompt[:, t])
+    secs = bulk.prefill(prompt, chunk=5)                 # 4 chunks of 5 and one of 3
+    assert secs > 0 and np.array_equal(bulk.lengths_host, stepwise.lengths_host)
+    assert bulk.page_rows[0][:2] == stepwise.page_rows[0][:2]
+    for li in range(cfg.layers):
+        for a, b in ((stepwise.k_cache[li], bulk.k_cache[li]), (stepwise.v_cache[li], bulk.v_cache[li])):
+            assert_close(b.float().cpu().numpy(), a.float().cpu().numpy(), 5e-3, f"layer {li} cache")
+    for s in range(batch):
+        bulk.reserve(s, T + 2)
+    bulk.upload_pages()
+    nxt = rng.integers(0, cfg.vocab, batch)
+    ta, tb = stepwise.step(nxt), bulk.step(nxt)
+    assert_close(bulk.full_logits().cpu().numpy(), stepwise.full_logits().cpu().numpy(), 5e-3, "the step after")
+    la = stepwise.full_logits().cpu().numpy()
+    top2 = np.sort(la, axis=1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 1e-2 * np.abs(la).max()
+    assert np.array_equal(ta[clear], tb[clear])

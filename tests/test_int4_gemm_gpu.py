@@ -1,6 +1,6 @@
 """The batch int4 kernel over prepacked weights (tcgen05, weights dequantised into tensor memory,
-activation tiles by bulk copies) against the oracle, on a B200.  From 17 activation rows the packed
-entry points select it; the decode kernel's tests (test_int4_stream_gpu.py) cover 1..16 rows."""
+activation tiles by bulk copies) against the oracle, on a B200.  From 49 activation rows the packed
+entry points select it; the decode kernel's tests (test_int4_stream_gpu.py) cover fewer rows."""
 import struct
 
 import numpy as np
@@ -37,8 +37,8 @@ def with_constant_groups(seed, K, N, std=0.02):
     return w
 
 
-@pytest.mark.parametrize("M,K,N", [(17, 4096, 1024), (64, 4096, 4096), (128, 1024, 384), (130, 512, 256),
-                                   (40, 4100, 512), (300, 100, 256), (32, 4096, 11008), (257, 2048, 1536)])
+@pytest.mark.parametrize("M,K,N", [(49, 4096, 1024), (64, 4096, 4096), (128, 1024, 384), (130, 512, 256),
+                                   (70, 4100, 512), (300, 100, 256), (64, 4096, 11008), (257, 2048, 1536)])
 def test_matches_the_oracle(M, K, N):
     w = with_constant_groups(2, K, N)
     p, s, z = orc.int4_quantize(w)
@@ -66,7 +66,7 @@ def test_full_size_against_a_binary64_product(M):
 
 @pytest.mark.parametrize("factor", [1e-4, 1e4, 1e-20, 1e20])
 def test_activation_magnitude_does_not_matter(factor):
-    M, K, N = 48, 2048, 512
+    M, K, N = 80, 2048, 512
     p, s, z = orc.int4_quantize(normal(4, (K, N), 0.02))
     a = normal(5, (M, K)) * np.float32(factor)
     a[1] *= np.float32(1e-3)                          # rows of very different magnitude in one call
@@ -78,7 +78,7 @@ def test_activation_magnitude_does_not_matter(factor):
 
 @pytest.mark.parametrize("std", [1e-5, 30.0])
 def test_weight_magnitude_does_not_matter(std):
-    M, K, N = 48, 2048, 512
+    M, K, N = 80, 2048, 512
     p, s, z = orc.int4_quantize(normal(6, (K, N), std))
     a = normal(7, (M, K))
     got = product(a, packed_of(p, s, z, K, N), M, K, N)
