@@ -76,6 +76,22 @@ template <typename T> inline T *ptr(const Launch &l, int i) { return reinterpret
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// The f16-operand int4 kernels round a * s to f16.  An exact power of two per activation row, taken
+// from the row's largest magnitude and undone in the f32 epilogue, keeps that product a normal f16
+// whatever the magnitude of the activations (the reference's f32 arithmetic is scale-invariant).
+// floor(log2(largest magnitude)), clamped; 0 for an all-zero row.  Bit patterns of non-negative
+// floats order like the floats; Inf and NaN clamp to the top.
+__host__ __device__ inline int ab_row_exponent(uint32_t amax_bits)
+{
+    int ea = amax_bits ? (int)((amax_bits >> 23) & 0xffu) - 127 : 0;
+    return ea < -80 ? -80 : (ea > 80 ? 80 : ea);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ float ab_pow2(int e) { return __uint_as_float((uint32_t)(127 + e) << 23); }
+#endif
+// the largest magnitude of each of M rows of K floats -> amax[M] (int4_stream.cu)
+int run_row_absmax(cudaStream_t stream, const float *a, float *amax, uint32_t M, uint32_t K, bool dependent);
+
 // the tensor-core int4 kernel for small batches (int4_mma.cu), driven by the int4 launcher
 struct Int4MmaPlan { bool ok; uint32_t groups, splits, kc; size_t ws; };
 Int4MmaPlan plan_int4_mma(uint32_t M, uint32_t N, uint32_t K);
@@ -89,11 +105,13 @@ int run_int4_row(const Launch &l, const Int4RowPlan &p, float *out, uint32_t N, 
 // the decode-batch int4 kernel: 16 rows per pass, K splits summed inside a cluster (int4_batch.cu)
 struct Int4BatchPlan { bool ok; int G; uint32_t tiles, splits, kc; };    // G groups per column tile
 Int4BatchPlan plan_int4_batch(uint32_t M, uint32_t N, uint32_t K);
+size_t int4_batch_workspace(uint32_t M);      // the rows' largest magnitudes
 int run_int4_batch(const Launch &l, const Int4BatchPlan &p, float *out, uint32_t M, uint32_t N, uint32_t K);
 
 
 // the 128 x 128 warp-MMA tile kernel of the grouped product, as a plain int4 product (grouped.cu)
 bool int4_tiles_ok(uint32_t N, uint32_t K);
+size_t int4_tiles_workspace(uint32_t M);
 int run_int4_tiles(const Launch &l, float *out, uint32_t M, uint32_t N, uint32_t K);
 
 

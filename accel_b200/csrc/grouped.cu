@@ -29,6 +29,7 @@ struct GroupedParams {
     float *out;
     uint32_t experts, tokens, K, N;
     uint64_t words_per_expert, groups_per_expert;
+    const float *amax;          // int4 tensor-core form: the rows' largest magnitudes (NULL: none)
 };
 
 __device__ __forceinline__ bool find_tile(const GroupedParams &p, uint32_t t, uint32_t &e,
@@ -220,6 +221,14 @@ __global__ void __launch_bounds__(kGmThreads) grouped_int4_mma_kernel(const Grou
     // k values 4 (tid % 16) ..): a half-warp reads 256 contiguous bytes of a row and its shared
     // stores fall on distinct banks
     const int srow = tid >> 4, skq = tid & 15;
+    // every staged row times an exact power of two that puts its largest activation in [2^8, 2^9):
+    // x * s stays a normal f16 whatever the activations' magnitude; undone where the sums are stored
+    float xscale[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t row = row0 + 16 * i + srow;
+        xscale[i] = (p.amax && row < last) ? ab_pow2(8 - ab_row_exponent(__float_as_uint(fabsf(__ldg(p.amax + row))))) : 1.f;
+    }
 
     float acc[2][8][4], accz[2][4];
 #pragma unroll
@@ -256,6 +265,7 @@ __global__ void __launch_bounds__(kGmThreads) grouped_int4_mma_kernel(const Grou
             const uint32_t row = row0 + 16 * i + srow;
             xv[i] = row < last ? __ldg(reinterpret_cast<const float4 *>(p.x + (size_t)row * p.K + k0 + 4 * skq))
                                : make_float4(0.f, 0.f, 0.f, 0.f);
+            xv[i].x *= xscale[i]; xv[i].y *= xscale[i]; xv[i].z *= xscale[i]; xv[i].w *= xscale[i];
         }
         __syncthreads();
         const uint2 s4 = *reinterpret_cast<const uint2 *>(s_s + 4 * skq);
@@ -362,15 +372,16 @@ __global__ void __launch_bounds__(kGmThreads) grouped_int4_mma_kernel(const Grou
                 add += cs;
             }
             float *o = p.out + (size_t)row * p.N + (size_t)g * kGroup + 64 * wc + 16 * t;
+            const float un = p.amax ? ab_pow2(ab_row_exponent(__float_as_uint(fabsf(__ldg(p.amax + row)))) - 8) : 1.f;
 #pragma unroll
             for (int nn = 0; nn < 2; nn++)
 #pragma unroll
                 for (int j = 0; j < 8; j += 4) {
                     float4 v;
-                    v.x = acc[mt][j][2 * h + nn] * 16777216.f + add;
-                    v.y = acc[mt][j + 1][2 * h + nn] * 1048576.f + add;
-                    v.z = acc[mt][j + 2][2 * h + nn] * 16777216.f + add;
-                    v.w = acc[mt][j + 3][2 * h + nn] * 1048576.f + add;
+                    v.x = (acc[mt][j][2 * h + nn] * 16777216.f + add) * un;
+                    v.y = (acc[mt][j + 1][2 * h + nn] * 1048576.f + add) * un;
+                    v.z = (acc[mt][j + 2][2 * h + nn] * 16777216.f + add) * un;
+                    v.w = (acc[mt][j + 3][2 * h + nn] * 1048576.f + add) * un;
                     *reinterpret_cast<float4 *>(o + 8 * nn + j) = v;
                 }
         }
@@ -381,6 +392,8 @@ __global__ void __launch_bounds__(kGmThreads) grouped_int4_mma_kernel(const Grou
 // 16 rows.  K % 64 == 0 and N % 128 == 0.
 bool int4_tiles_ok(uint32_t N, uint32_t K) { return N % kGroup == 0 && K % kGmChunk == 0 && N > 0 && K > 0; }
 
+size_t int4_tiles_workspace(uint32_t M) { return align_up((size_t)M * 4, 256); }     // the rows' largest magnitudes
+
 int run_int4_tiles(const Launch &l, float *out, uint32_t M, uint32_t N, uint32_t K)
 {
     GroupedParams p{};
@@ -390,6 +403,13 @@ int run_int4_tiles(const Launch &l, float *out, uint32_t M, uint32_t N, uint32_t
     p.experts = 1; p.tokens = M; p.K = K; p.N = N;
     p.words_per_expert = ((uint64_t)K * N + 7) / 8;
     p.groups_per_expert = ((uint64_t)K * N + kGroup - 1) / kGroup;
+    if (!l.ws || l.ws_bytes < int4_tiles_workspace(M))
+        return fail(AB_ERR_INVALID, "QuantMatMulInt4 (tiles): needs %zu bytes of workspace, given %zu",
+                    int4_tiles_workspace(M), l.ws_bytes);
+    float *amax = static_cast<float *>(l.ws);
+    int rc = run_row_absmax(l.stream, p.x, amax, M, K, false);
+    if (rc) return rc;
+    p.amax = amax;
     dim3 grid(N / kGroup, (M + kGmRows - 1) / kGmRows);
     grouped_int4_mma_kernel<<<grid, kGmThreads, 0, l.stream>>>(p); count_launch();
     return check_cuda(cudaGetLastError(), "QuantMatMulInt4 (tiles)");
@@ -398,14 +418,21 @@ int run_int4_tiles(const Launch &l, float *out, uint32_t M, uint32_t N, uint32_t
 static int run_grouped(Launch &l, GroupedParams &p, bool int4, bool zero_tail, uint32_t out_rows,
                        const char *name)
 {
-    if (l.query_ws) { l.ws_need = 0; return AB_OK; }
-    if (p.experts == 0 || p.K == 0 || p.N == 0)
-        return fail(AB_ERR_INVALID, "%s: Experts=%u K=%u N=%u", name, p.experts, p.K, p.N);
-    if (p.tokens == 0) return AB_OK;
     bool fast = p.K % BK == 0 && (int4 ? p.N % kGroup == 0 : p.N % 4 == 0);
     static const bool simt_only = getenv("AB_GROUPED_SIMT") != nullptr;       // for measurements
     const bool mma = int4 && fast && p.K % kGmChunk == 0 && !simt_only;
+    const size_t ws_need = mma ? align_up((size_t)p.tokens * 4, 256) : 0;     // the rows' largest magnitudes
+    if (l.query_ws) { l.ws_need = ws_need; return AB_OK; }
+    if (p.experts == 0 || p.K == 0 || p.N == 0)
+        return fail(AB_ERR_INVALID, "%s: Experts=%u K=%u N=%u", name, p.experts, p.K, p.N);
+    if (p.tokens == 0) return AB_OK;
     if (mma) {
+        if (!l.ws || l.ws_bytes < ws_need)
+            return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, ws_need, l.ws_bytes);
+        float *amax = static_cast<float *>(l.ws);
+        int rc = run_row_absmax(l.stream, p.x, amax, p.tokens, p.K, false);
+        if (rc) return rc;
+        p.amax = amax;
         dim3 grid(p.N / kGroup, (p.tokens + kGmRows - 1) / kGmRows + p.experts);
         grouped_int4_mma_kernel<<<grid, kGmThreads, 0, l.stream>>>(p); count_launch();
     } else if (fast) {

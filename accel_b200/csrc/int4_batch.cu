@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(128 * G, 4 / G)
 int4_batch_kernel(const float *__restrict__ a, const uint2 *__restrict__ bq,
                   const __half *__restrict__ bs, const __half *__restrict__ bz,
                   float *__restrict__ out, uint32_t N, uint32_t K, uint32_t kc, uint32_t m0,
-                  uint32_t mrows)
+                  uint32_t mrows, const float *__restrict__ amax)
 {
     constexpr int kThreads = 128 * G, kChunks = 8 * G;      // staging: 16 rows x kChunks 4-wide chunks
     extern __shared__ __align__(16) unsigned char smem[];
@@ -160,13 +160,20 @@ int4_batch_kernel(const float *__restrict__ a, const uint2 *__restrict__ bq,
     const int m = tid / kChunks, kch = tid % kChunks;      // staging: row m, chunks kch, kch + kChunks, ...
     const bool row_on = (uint32_t)m < mrows;
     const float *arow = a + (size_t)(m0 + (row_on ? m : 0)) * K + kbeg;
+    // The row's activations times an exact power of two that puts the largest of the row in
+    // [2^8, 2^9) (amax: the rows' largest magnitudes; NULL: as they are): a * s stays a normal f16
+    // whatever the activations' magnitude.  Undone where the sums are stored.
+    const float pa = (amax && row_on) ? ab_pow2(8 - ab_row_exponent(__float_as_uint(fabsf(__ldg(amax + m0 + m))))) : 1.f;
     float4 av[kBActBatch];
     auto load_acts = [&](uint32_t k0) {
 #pragma unroll
         for (int i = 0; i < kBActBatch; i++) {
             const uint32_t k = k0 + 4 * kChunks * i;
-            av[i] = (row_on && k < nrows) ? __ldg(reinterpret_cast<const float4 *>(arow + k))
-                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+            av[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row_on && k < nrows) {
+                const float4 x = __ldg(reinterpret_cast<const float4 *>(arow + k));
+                av[i] = make_float4(x.x * pa, x.y * pa, x.z * pa, x.w * pa);
+            }
         }
     };
     load_acts(4 * kch);
@@ -297,6 +304,9 @@ int4_batch_kernel(const float *__restrict__ a, const uint2 *__restrict__ bq,
     const bool col_on = g0 + tg < gpr;
     float *gred = red + (size_t)tg * kBPhases * (16 * 128);
     float *orow = out + (size_t)m0 * N + (size_t)(g0 + tg) * kGroup + tc;
+    auto row_unscale = [&](uint32_t mm) {
+        return amax ? ab_pow2(ab_row_exponent(__float_as_uint(fabsf(__ldg(amax + m0 + mm)))) - 8) : 1.f;
+    };
     {
         float v[16];
 #pragma unroll
@@ -317,7 +327,7 @@ int4_batch_kernel(const float *__restrict__ a, const uint2 *__restrict__ bq,
         for (int mm = 0; mm < 16; mm++)
             if ((uint32_t)mm < mrows) {
                 if (splits > 1) gred[red_at(mm, tc)] = v[mm];
-                else if (col_on) orow[(size_t)mm * N] = v[mm];
+                else if (col_on) orow[(size_t)mm * N] = v[mm] * row_unscale(mm);
             }
     }
     if (splits == 1) return;
@@ -337,7 +347,7 @@ int4_batch_kernel(const float *__restrict__ a, const uint2 *__restrict__ bq,
         float v = pv[0];
 #pragma unroll
         for (int q = 1; q < kBMaxCluster; q++) v += pv[q];
-        if (col_on) orow[(size_t)mm * N] = v;
+        if (col_on) orow[(size_t)mm * N] = v * row_unscale(mm);
     }
     cluster.sync();                              // nobody leaves while its sums are being read
 }
@@ -372,7 +382,7 @@ Int4BatchPlan plan_int4_batch(uint32_t M, uint32_t N, uint32_t K)
 
 template <int G>
 static int launch_batch(const Launch &l, const Int4BatchPlan &p, float *out, uint32_t N, uint32_t K,
-                        uint32_t m0, uint32_t mrows)
+                        uint32_t m0, uint32_t mrows, const float *amax)
 {
     static bool attr_set[64] = {};
     int dev = 0;
@@ -400,19 +410,28 @@ static int launch_batch(const Launch &l, const Int4BatchPlan &p, float *out, uin
     cfg.numAttrs = 1;
     int rc = check_cuda(cudaLaunchKernelEx(&cfg, int4_batch_kernel<G>, ptr<const float>(l, 0),
                                            ptr<const uint2>(l, 1), ptr<const __half>(l, 2),
-                                           ptr<const __half>(l, 3), out, N, K, p.kc, m0, mrows),
+                                           ptr<const __half>(l, 3), out, N, K, p.kc, m0, mrows, amax),
                         "int4_batch_kernel");
     count_launch();
     return rc;
 }
 
+size_t int4_batch_workspace(uint32_t M) { return align_up((size_t)M * 4, 256); }
+
+// The rows' largest magnitudes first (into the workspace), then passes of 16 rows.
 int run_int4_batch(const Launch &l, const Int4BatchPlan &p, float *out, uint32_t M, uint32_t N, uint32_t K)
 {
+    if (!l.ws || l.ws_bytes < int4_batch_workspace(M))
+        return fail(AB_ERR_INVALID, "the int4 batch kernel needs %zu bytes of workspace, given %zu",
+                    int4_batch_workspace(M), l.ws_bytes);
+    float *amax = static_cast<float *>(l.ws);
+    int rc = run_row_absmax(l.stream, ptr<const float>(l, 0), amax, M, K, false);
+    if (rc) return rc;
     for (uint32_t m0 = 0; m0 < M; m0 += 16) {
         const uint32_t mrows = M - m0 < 16 ? M - m0 : 16;
-        int rc = p.G == 4 ? launch_batch<4>(l, p, out, N, K, m0, mrows)
-                 : p.G == 2 ? launch_batch<2>(l, p, out, N, K, m0, mrows)
-                            : launch_batch<1>(l, p, out, N, K, m0, mrows);
+        rc = p.G == 4 ? launch_batch<4>(l, p, out, N, K, m0, mrows, amax)
+             : p.G == 2 ? launch_batch<2>(l, p, out, N, K, m0, mrows, amax)
+                        : launch_batch<1>(l, p, out, N, K, m0, mrows, amax);
         if (rc) return rc;
     }
     return AB_OK;

@@ -89,6 +89,7 @@ int4_row_kernel(const float *__restrict__ a, const uint4 *__restrict__ bq, const
     __shared__ unsigned short s_cs[W][kRowMaxKc];          // f16(a s) per group and row of the K range
     __shared__ float s_zw[W][kRowThreads / 32];            // per-warp parts of the correction
     __shared__ float s_zc[W];                              // sum_k (a s)_f16 (16 + z): subtracted at the end
+    __shared__ uint32_t s_amax[kRowThreads / 32];          // the warps' largest |a| of the K range (bits)
     __shared__ __align__(16) float s_red[kRowsPerInstr][kCols];
     __shared__ __align__(16) float s_sum[kCols];           // this CTA's partial row, read by the cluster
     const int tid = threadIdx.x, rl = tid / kLanes, c = tid % kLanes;
@@ -129,6 +130,21 @@ int4_row_kernel(const float *__restrict__ a, const uint4 *__restrict__ bq, const
         const uint32_t r = rl + u * kRowsPerInstr;
         cw[u] = (col_on && r < nrows) ? ldg_row(base + (size_t)r * row_u4) : make_uint4(0, 0, 0, 0);
     }
+    // The activations of this K range times an exact power of two that puts the largest of them in
+    // [2^8, 2^9): a * s then stays a normal f16 whatever the activations' magnitude.  Undone when the
+    // CTA's sums leave (every CTA of a cluster has its own factor).
+    {
+        uint32_t mx = 0;
+#pragma unroll
+        for (int i = 0; i < kMetaIt; i++) mx = max(mx, __float_as_uint(fabsf(av[i])));
+        mx = __reduce_max_sync(0xffffffffu, mx);
+        if ((tid & 31) == 0) s_amax[tid >> 5] = mx;
+    }
+    __syncthreads();
+    const int ea = ab_row_exponent(max(max(s_amax[0], s_amax[1]), max(s_amax[2], s_amax[3])));
+    const float pa = ab_pow2(8 - ea), unscale = ab_pow2(ea - 8);
+#pragma unroll
+    for (int i = 0; i < kMetaIt; i++) av[i] *= pa;
     // f16(a s) once per (row, group), not once per thread that uses it; the correction
     // sum_k (a s)_f16 (16 + z) (or -a z where the scale is 0) is summed here too, in a fixed order
     {
@@ -207,7 +223,7 @@ int4_row_kernel(const float *__restrict__ a, const uint4 *__restrict__ bq, const
         float v = 0.f;
 #pragma unroll
         for (int i = 0; i < kRowsPerInstr; i++) v += s_red[i][at];
-        v -= s_zc[col >> 7];
+        v = (v - s_zc[col >> 7]) * unscale;
         if (splits == 1) {
             if (g0 * kGroup + col < N) out[g0 * kGroup + col] = v;
         } else {

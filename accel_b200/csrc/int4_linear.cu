@@ -246,6 +246,27 @@ static size_t tc_tiles_workspace(uint32_t M, uint32_t N, uint32_t K)
     return align_up(int4_stream_packed_bytes(N, K), 256) + int4_gemm_workspace(M, K);
 }
 
+// The two-kernel tensor-core form (int4_mma.cu) rounds a * s to f16 like the others; it is the
+// fallback for products too wide for one wave of clusters, so it gets the rows' power-of-two factors
+// from outside: a copy of the activations scaled per row, and the output rows scaled back.
+__global__ void __launch_bounds__(256)
+int4_scale_rows_kernel(const float *__restrict__ a, const float *__restrict__ amax, float *__restrict__ scaled, uint32_t K)
+{
+    const float pa = ab_pow2(8 - ab_row_exponent(__float_as_uint(fabsf(amax[blockIdx.x]))));
+    const size_t base = (size_t)blockIdx.x * K;
+    for (uint32_t k = threadIdx.x; k < K; k += 256) scaled[base + k] = a[base + k] * pa;
+}
+
+__global__ void __launch_bounds__(256)
+int4_unscale_rows_kernel(float *__restrict__ out, const float *__restrict__ amax, uint32_t N)
+{
+    const float un = ab_pow2(ab_row_exponent(__float_as_uint(fabsf(amax[blockIdx.x]))) - 8);
+    const size_t base = (size_t)blockIdx.x * N;
+    for (uint32_t n = threadIdx.x; n < N; n += 256) out[base + n] *= un;
+}
+
+static size_t mma_prescale_workspace(uint32_t M, uint32_t K) { return align_up((size_t)M * 4, 256) + align_up((size_t)M * K * 4, 256); }
+
 static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint32_t K)
 {
     if (N == 0 || K == 0 || M == 0) return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u", name, M, N, K);
@@ -267,7 +288,7 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
     Int4RowPlan rp = plan_int4_row(N, K);
     const bool use_row = !use_tc && !use_tiles && !use_mma && !use_batch && rp.ok && M == 1 && forced != 3;
     if (l.query_ws) {
-        l.ws_need = use_tiles ? 0 : use_tc ? tc_tiles_workspace(M, N, K) : (use_batch ? 0 : (use_mma ? mp.ws : (use_row ? 0 : p.ws)));
+        l.ws_need = use_tiles ? int4_tiles_workspace(M) : use_tc ? tc_tiles_workspace(M, N, K) : (use_batch ? int4_batch_workspace(M) : (use_mma ? align_up(mp.ws, 256) + mma_prescale_workspace(M, K) : (use_row ? 0 : p.ws)));
         return AB_OK;
     }
 
@@ -317,16 +338,27 @@ static int launch_int4(Launch &l, const char *name, uint32_t M, uint32_t N, uint
         return check_cuda(cudaGetLastError(), name);
     }
     if (use_mma) {
-        if (mp.ws > l.ws_bytes || (mp.ws && !l.ws))
-            return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, mp.ws,
-                        l.ws_bytes);
-        float *mdst = mp.splits > 1 ? reinterpret_cast<float *>(l.ws) : out;
-        int rc = run_int4_mma(l, mp, mdst, M, N, K);
+        const size_t need = align_up(mp.ws, 256) + mma_prescale_workspace(M, K);
+        if (need > l.ws_bytes || !l.ws)
+            return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, need, l.ws_bytes);
+        unsigned char *w = static_cast<unsigned char *>(l.ws);
+        float *partial = reinterpret_cast<float *>(w);
+        float *amax = reinterpret_cast<float *>(w + align_up(mp.ws, 256));
+        float *scaled = reinterpret_cast<float *>(w + align_up(mp.ws, 256) + align_up((size_t)M * 4, 256));
+        int rc = run_row_absmax(l.stream, ptr<const float>(l, 0), amax, M, K, false);
+        if (rc) return rc;
+        int4_scale_rows_kernel<<<M, 256, 0, l.stream>>>(ptr<const float>(l, 0), amax, scaled, K); count_launch();
+        void *b2[5] = {scaled, l.b[1], l.b[2], l.b[3], l.b[4]};
+        Launch l2 = l;
+        l2.b = b2;
+        float *mdst = mp.splits > 1 ? partial : out;
+        rc = run_int4_mma(l2, mp, mdst, M, N, K);
         if (rc) return rc;
         if (mp.splits > 1) {
             size_t mn = (size_t)M * N;
             int4_reduce_kernel<<<(unsigned)((mn / 4 + 128) / 128), 128, 0, l.stream>>>(mdst, out, mp.splits, mn); count_launch();
         }
+        int4_unscale_rows_kernel<<<M, 256, 0, l.stream>>>(out, amax, N); count_launch();
         note_selection("%s: tensor-core kernel (m16n8k16, f16 operands, f32 accumulate), %u column "
                        "groups x %u K splits of %u rows, %u pass(es) of 16 activation rows", name,
                        mp.groups, mp.splits, mp.kc, (M + 15) / 16);

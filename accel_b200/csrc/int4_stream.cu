@@ -818,6 +818,22 @@ static int sx_launch(cudaStream_t stream, const float *a, const float *amax, con
     return rc;
 }
 
+int run_row_absmax(cudaStream_t stream, const float *a, float *amax, uint32_t M, uint32_t K, bool dependent)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(M);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
+    int rc = check_cuda(cudaLaunchKernelEx(&cfg, int4_row_absmax_kernel, a, amax, K), "int4_row_absmax_kernel");
+    count_launch();
+    return rc;
+}
+
 // The product in passes of at most 16 activation rows.  amax: the rows' largest magnitudes if the
 // caller has them; else `scratch` (int4_stream_workspace(M) bytes) receives them from a small
 // kernel, or, for one or two rows, every CTA finds its own.  mode: kSxPlain (out0 = [M][N]),
@@ -835,22 +851,12 @@ static int run_int4_stream_mode(cudaStream_t stream, const float *a, const float
         p.tiles = (N / 128 + 1) / 2;
         while (p.splits > 1 && p.tiles > sx_resident_clusters<2>(p.splits)) p.splits--;
     }
-    if (!amax && M >= kSxAmaxFromRows) {
+    static const bool amax_in_kernel = getenv("AB_TMP_AMAX_IN_KERNEL") != nullptr;   // TEMPORARY experiment
+    if (!amax && M >= kSxAmaxFromRows && !amax_in_kernel) {
         if (!scratch) return fail(AB_ERR_INVALID, "the prepacked int4 product of %u rows needs %zu bytes of scratch", M,
                                   int4_stream_workspace(M));
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(M);
-        cfg.blockDim = dim3(256);
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = dependent ? 1 : 0;
-        int rc = check_cuda(cudaLaunchKernelEx(&cfg, int4_row_absmax_kernel, a, static_cast<float *>(scratch), K),
-                            "int4_row_absmax_kernel");
+        int rc = run_row_absmax(stream, a, static_cast<float *>(scratch), M, K, dependent);
         if (rc) return rc;
-        count_launch();
         amax = static_cast<const float *>(scratch);
     }
     for (uint32_t m0 = 0; m0 < M; m0 += kSxNB) {

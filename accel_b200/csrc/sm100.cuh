@@ -106,11 +106,7 @@ __device__ __forceinline__ void sx_tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
 
 // The exponent that scales a row: floor(log2(largest magnitude)), clamped; 0 for an all-zero row.
 // Bit patterns of non-negative floats order like the floats; Inf and NaN clamp to the top.
-__device__ __forceinline__ int sx_row_exponent(uint32_t amax_bits)
-{
-    int ea = amax_bits ? (int)((amax_bits >> 23) & 0xffu) - 127 : 0;
-    return ea < -80 ? -80 : (ea > 80 ? 80 : ea);
-}
+__device__ __forceinline__ int sx_row_exponent(uint32_t amax_bits) { return ab_row_exponent(amax_bits); }
 
 // Where the columns go.  Plain: out[m][ld0 .. ].  Split: the columns from group g1 on go to out1 and
 // those from group g2 on to out2, each a contiguous matrix of its own (the fused q | k | v product).

@@ -274,7 +274,10 @@ class DecodeEngine:
                  collective: str = "nccl", use_packed: Optional[bool] = None):
         """collective: how the row-parallel products are summed over the ranks: "nccl" (the
         process group's all-reduce) or "peer" (this library's one-shot kernel over NVLink peer
-        memory, peer.PeerAllReduce; GPUs only)."""
+        memory, peer.PeerAllReduce; GPUs only), or "skip": one rank of a sharded model run on its
+        own with the sums over ranks left out (its results are NOT the model's: this is for
+        timing and profiling one rank's kernels on one GPU, where a profiler may not wrap a
+        multi-rank launch)."""
         cfg, sh = model.cfg, model.shard
         self.model, self.cfg, self.shard, self.ops, self.group = model, cfg, sh, ops, group
         self.collective = collective
@@ -517,7 +520,7 @@ class DecodeEngine:
             main.wait_stream(st)
 
     def _all_reduce(self, t):
-        if self.shard.tp > 1:
+        if self.shard.tp > 1 and self.collective != "skip":
             import torch.distributed as dist
             dist.all_reduce(t, group=self.group)
 

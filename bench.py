@@ -509,6 +509,13 @@ def run_b200(args):
     cache_dtype = torch.float16 if args.kv == "f16" else torch.float32
     cfg = dec.ModelConfig(layers=args.layers, cache_dtype=cache_dtype)
     shard = dec.Shard.plan(cfg, world, rank)
+    if args.shard_of > 1:
+        # one rank's share of an N-way tensor-parallel step on ONE GPU, the sums over ranks left out:
+        # the launch list and the per-kernel times of a rank, which a profiler cannot take from a
+        # multi-rank run.  Not a benchmark figure.
+        if world != 1:
+            raise SystemExit("--shard-of runs in one process")
+        shard = dec.Shard.plan(cfg, args.shard_of, 0)
     t_setup = time.perf_counter()
     model = dec.DecodeModel(cfg, shard, dev, seed=1234)
     B, ctx = args.batch, args.context
@@ -528,7 +535,10 @@ def run_b200(args):
         if int(flag.item()) == 0:
             collective, engine = f"nccl (peer memory unavailable{': ' + why if why else ' on another rank'})", None
     if engine is None:
-        engine = dec.DecodeEngine(model, B, max_context=ctx + total_steps + 16, group=group, collective="nccl")
+        engine = dec.DecodeEngine(model, B, max_context=ctx + total_steps + 16, group=group,
+                                  collective="skip" if args.shard_of > 1 else "nccl")
+        if args.shard_of > 1:
+            collective = f"skipped: rank 0's kernels of a tp{args.shard_of} step, results not the model's"
     engine.overlap = not args.no_overlap
     log = (lambda m: print(f"[rank {rank}] {m}", file=sys.stderr, flush=True)) if args.verbose else (lambda m: None)
     log("engine built")
@@ -669,7 +679,7 @@ def run_b200(args):
     # for the inputs, a dispatch node per kernel, the ids copied into a host-visible block), compiled
     # once and driven with set_payload / ab_exec_submit / ab_fence_wait, replayed as a CUDA graph
     e2e_seam = None
-    if world == 1 and not args.no_seam:
+    if world == 1 and not args.no_seam and args.shard_of == 1:
         try:
             seam = dec.SeamStep(engine, use_graphs=True)
             for _ in range(min(args.warmup, 3)):
@@ -726,7 +736,7 @@ def run_b200(args):
     # kernel the step uses (the load-time prepack of the same matrices); the reference-layout
     # kernel on quant.Int4Quantize's planes is reported beside it.
     gemv = None
-    if world == 1 and cfg.layers >= 4:
+    if world == 1 and cfg.layers >= 4 and args.shard_of == 1:
         a1 = torch.randn(cfg.d_model, device=dev)
         out1 = torch.empty(cfg.ffn, device=dev)
         mats = [m for L in model.layers for m in (L.wg, L.wu)]
@@ -770,7 +780,7 @@ def run_b200(args):
 
     # ---- CPU baseline beside it (rank 0, N = 1 only): the oracle's layer sample
     cpu, layer_par = None, None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.shard_of == 1:
         # parity at the benchmarked shape first (the GPU leg wants the sample's pristine cache):
         # one full-size layer + lm_head + argmax, this library on the GPU against the oracle
         from oracle.step import LayerSample, layer_parity
@@ -850,6 +860,9 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=256, help="positions per sequence and prefill pass")
     ap.add_argument("--no-tp-parity", action="store_true",
                     help="skip the N-rank against one-rank comparison of the first step (N > 1)")
+    ap.add_argument("--shard-of", type=int, default=1, metavar="N",
+                    help="diagnostic: run rank 0's shard of an N-way tensor-parallel step alone on one GPU, "
+                         "collectives skipped (for launch lists; not a benchmark figure)")
     ap.add_argument("--no-seam", action="store_true", help="skip the end-to-end loop through ab_compile / ab_exec_submit")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="keep every operator on one stream")

@@ -135,6 +135,33 @@ def test_config3_shape_against_the_oracle():
         assert np.all(got[s, h] <= vv.max(0) + 1e-5) and np.all(got[s, h] >= vv.min(0) - 1e-5)
 
 
+@pytest.mark.parametrize("qH,kvH", [(4, 4), (8, 2)])
+def test_a_nan_score_poisons_its_head_and_no_other(qH, kvH):
+    """kmath.Max propagates a NaN (kmath/kmath.go:96-104), so in the reference a NaN score makes the
+    running maximum, and with it every weight of that (sequence, query head), NaN.  These kernels
+    keep the maximum with fmaxf (which drops a NaN) but the NaN score still enters the sum of
+    weights and the output, so the outcome is the same: the oracle (which follows kmath.Max) and the
+    device give NaN on exactly the same heads and agree elsewhere."""
+    batch, D, block = 3, 32, 8
+    lengths = np.array([300, 40, 9], np.uint32)
+    k, v, pages, mp = paged_fixture(7, batch, kvH, D, block, lengths)
+    q = normal(8, (batch, 1, qH, D))
+    # one K element of sequence 1, position 17, KV head 0: NaN for the query heads that read that head
+    row = pages[1, 17 // block] * block + 17 % block
+    k[row, 0, 3] = np.nan
+    sc = attn_scale(D)
+    got = T.attention(dev(q), dev(k), dev(v), T.AttentionOptions(
+        lengths=dev(lengths), pages=dev(pages), block=block, scale=sc)).cpu().numpy()
+    want = orc.attention_decode_batched(q, k, v, pages, lengths, batch, qH, kvH, D, block, mp,
+                                        sc).reshape(batch, qH, D)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    group = qH // kvH
+    assert np.all(np.isnan(got[1, :group])) and not np.any(np.isnan(got[1, group:]))
+    assert not np.any(np.isnan(got[0])) and not np.any(np.isnan(got[2]))
+    ok = ~np.isnan(want)
+    assert_close(got[ok], want[ok], ATTN_TOL, "the heads beside the poisoned one")
+
+
 def test_zero_length_is_nan_as_in_the_reference():
     # internal/kernels/batched.go:104,347-349: l = 0, out = 0/0
     batch, qH, kvH, D, block = 2, 4, 2, 16, 4

@@ -57,7 +57,8 @@ def test_workspace_query_and_argument_checks_need_no_gpu():
     M, K, N = 16, 4096, 32000
     need = runtime.workspace_bytes("QuantMatMulInt4", [M * K, K * N // 8, K * N // 128, K * N // 128, M * N],
                                    runtime.gemm_dims(M, N, K))
-    assert need > 0 and need % (M * N * 4) == 0
+    # (the partial tiles, then the rows' largest magnitudes and the activations scaled by them)
+    assert need >= 2 * M * N * 4 + M * 4 + M * K * 4
     with pytest.raises(_lib.AccelError, match="takes 5 bindings"):
         runtime.workspace_bytes("QuantMatVecInt4", [1, 2], runtime.gemm_dims(0, 4096, 4096))
     with pytest.raises(_lib.AccelError, match="uniform block"):

@@ -94,6 +94,10 @@ def test_int4_grouped_is_the_composition(K, kernel):
     got = T.grouped_matmul_int4(dev(x), q, E, dev(counts)).cpu().numpy()
     assert kernel in runtime.last_selection()
     assert_close(got, want, GEMM_TOL, "int4 grouped")
+    # tiny activations keep the accuracy of ordinary ones (rows are scaled by exact powers of two)
+    tiny = (x * np.float32(1e-4)).astype(np.float32)
+    got = T.grouped_matmul_int4(dev(tiny), q, E, dev(counts)).cpu().numpy()
+    assert_close(got, orc.grouped_matmul(tiny, back, off, rows, E, K, N), GEMM_TOL, "int4 grouped, activations x 1e-4")
 
 
 @pytest.mark.parametrize("E,K,N,counts", [(4, 256, 384, [70, 0, 129, 1]), (8, 4096, 1024, None), (3, 100, 128, [128, 128, 5]),

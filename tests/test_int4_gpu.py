@@ -139,6 +139,30 @@ def test_per_element_bound_on_the_reference_layout(M, K, N):
     assert np.all(np.abs(got - want) <= bound), float(np.max(np.abs(got - want) / mag))
 
 
+@pytest.mark.parametrize("factor", [1e-4, 1e4, 1e-20, 1e20])
+@pytest.mark.parametrize("M,K,N,kernel", [(1, 4096, 1024, "streaming row kernel"), (16, 4096, 1024, "cluster"),
+                                          (4, 4096, 32000, "column groups x"), (80, 1024, 512, "tile kernel")])
+def test_activation_magnitude_does_not_matter_on_the_reference_layout(M, K, N, kernel, factor):
+    """The kernels over quant.Int4Quantize's planes round a * s to f16; each scales its activation
+    rows by an exact power of two first (undone in f32), so tiny and huge activations keep the
+    accuracy of ordinary ones, as the reference's f32 arithmetic does: the row kernel, the 16-row
+    cluster kernel, the two-kernel form for wide matrices and the tile kernel."""
+    w, p, s, z = quantized(4, K, N)
+    a = normal(5, (M, K)) * np.float32(factor)
+    if M > 1:
+        a[1] *= np.float32(1e-3)                          # rows of very different magnitude in one call
+    x = torch.from_numpy(a).to(DEV)
+    if M == 1:
+        got = T.int4_matvec(x[0], to_int4(p, s, z, K * N)).cpu().numpy()[None, :]
+        want = orc.quant_matvec_int4(a[0], p, s, z, N, K)[None, :]
+    else:
+        got = T.int4_matmul(x, to_int4(p, s, z, K * N)).cpu().numpy()
+        want = orc.quant_matmul_int4(a, p, s, z, M, N, K)
+    assert kernel in runtime.last_selection(), runtime.last_selection()
+    for m in range(M):
+        assert_close(got[m], want[m], GEMM_TOL, f"row {m} at activations x {factor:g}")
+
+
 def test_device_quantizer_is_bit_identical(rng):
     n = 128 * 4000 + 77
     w = (rng.standard_normal(n) * 0.02).astype(np.float32)
