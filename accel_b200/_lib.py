@@ -123,6 +123,16 @@ SYMBOLS = [
     ("ab_peer_allreduce_error", C.c_int, [_P, C.POINTER(C.c_uint32)]),
     ("ab_peer_allreduce_set_spin_limit", C.c_int, [_P, C.c_uint32]),
     ("ab_peer_allreduce_clear_error", C.c_int, [_P]),
+    ("ab_group_open", C.c_int, [_P, C.c_int, C.c_uint32, C.POINTER(_P)]),
+    ("ab_group_close", C.c_int, [_P]),
+    ("ab_group_size", C.c_int, [_P]),
+    ("ab_group_ordinal", C.c_int, [_P, C.c_int]),
+    ("ab_group_buffer", _P, [_P, C.c_int]),
+    ("ab_group_state", _P, [_P, C.c_int]),
+    ("ab_group_stream", _P, [_P, C.c_int]),
+    ("ab_group_peer_table", _P, [_P]),
+    ("ab_group_all_reduce_f32", C.c_int, [_P, _P, _P, C.c_uint32]),
+    ("ab_group_synchronize", C.c_int, [_P]),
     ("ab_int4_quantize", C.c_int, [_P, C.c_size_t, _P, _P, _P]),
     ("ab_int4_nibble", C.c_uint32, [_P, C.c_size_t]),
     ("ab_int4_dequantize", C.c_int, [_P, _P, _P, C.c_size_t, _P]),

@@ -394,6 +394,27 @@ AB_API int ab_peer_allreduce_error(const void *state, uint32_t *failed_call);
 AB_API int ab_peer_allreduce_set_spin_limit(void *state, uint32_t polls);
 AB_API int ab_peer_allreduce_clear_error(void *state);
 
+/* ---- N devices of one process as a group (specs/060-cuda-bringup.md:261-267, 537-548 leave
+ * multi-device to a later layer; no accel analogue).  ab_group_open enables peer access between
+ * every pair of the named devices (distinct ordinals, at most 8), and gives every rank a zeroed peer
+ * buffer of ab_peer_allreduce_buffer_bytes(capacity_floats), a zeroed state block and a non-blocking
+ * stream; ab_group_peer_table is the HOST array of the buffers in rank order that the
+ * ab_peer_allreduce_* calls take.  A host drives rank r by making ab_group_ordinal(g, r) current and
+ * enqueueing on ab_group_stream(g, r); ab_group_all_reduce_f32 enqueues one all-reduce for every rank
+ * in turn (in[r], out[r]: device memory of rank r); ab_group_synchronize waits for every rank's stream
+ * and reports AB_ERR_TIMEOUT if a bounded wait ran out. */
+typedef struct ab_group ab_group;
+AB_API int ab_group_open(const int *ordinals, int n, uint32_t capacity_floats, ab_group **out);
+AB_API int ab_group_close(ab_group *g);
+AB_API int ab_group_size(const ab_group *g);
+AB_API int ab_group_ordinal(const ab_group *g, int rank);
+AB_API void *ab_group_buffer(const ab_group *g, int rank);
+AB_API void *ab_group_state(const ab_group *g, int rank);
+AB_API void *ab_group_stream(const ab_group *g, int rank);
+AB_API void *const *ab_group_peer_table(const ab_group *g);
+AB_API int ab_group_all_reduce_f32(ab_group *g, const float *const *in, float *const *out, uint32_t n);
+AB_API int ab_group_synchronize(ab_group *g);
+
 #ifdef __cplusplus
 }
 #endif
