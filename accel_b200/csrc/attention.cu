@@ -442,24 +442,50 @@ attn_partition_gqa_kernel(const AttnParams p)
     }
 }
 
-// grid = (q_heads, rows); one thread per output element.
-__global__ void attn_combine_kernel(const AttnParams p)
+// grid = (q_heads, rows), 128 threads; thread d owns output element d.  The partitions' maxima are
+// read by all threads side by side (thread t takes partitions t, t + 128, ...) and reduced once; the
+// weighted sum then walks the partitions with its loads batched eight at a time: with 64-position
+// partitions a 2048-token context has 33 of them, and a loop that waits for each load in turn costs
+// more than the partitions themselves.
+__global__ void __launch_bounds__(128) attn_combine_kernel(const AttnParams p)
 {
+    __shared__ float s_mx[4];
     pdl_enter();
     const uint32_t h = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
     const RowView rv = row_view(p, row);
-    if (rv.zero || d >= p.head_dim) return;
+    if (rv.zero) return;
     uint32_t nparts = (rv.len + p.psize - 1) / p.psize;
     if (nparts == 0) nparts = 1;
     const size_t qrow = (size_t)row * p.q_heads + h;
+    const float2 *ml = p.part_ml + qrow * p.parts;
     float mx = kNegBig;
-    for (uint32_t s = 0; s < nparts; s++) mx = fmaxf(mx, p.part_ml[qrow * p.parts + s].x);
+    for (uint32_t s = d; s < nparts; s += 128) mx = fmaxf(mx, ml[s].x);
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
+    if ((d & 31) == 0) s_mx[d >> 5] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(s_mx[0], s_mx[1]), fmaxf(s_mx[2], s_mx[3]));
+    if (d >= p.head_dim) return;
+    const float *po = p.part_o + qrow * p.parts * p.head_dim + d;
     float lt = 0.f, acc = 0.f;
-    for (uint32_t s = 0; s < nparts; s++) {
-        const float2 ml = p.part_ml[qrow * p.parts + s];
-        const float f = exp2f(ml.x - mx);
-        lt = fmaf(ml.y, f, lt);
-        acc = fmaf(p.part_o[(qrow * p.parts + s) * p.head_dim + d], f, acc);
+    uint32_t s = 0;
+    for (; s + 8 <= nparts; s += 8) {
+        float2 m8[8];
+        float o8[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) { m8[i] = ml[s + i]; o8[i] = po[(size_t)(s + i) * p.head_dim]; }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float f = exp2f(m8[i].x - mx);
+            lt = fmaf(m8[i].y, f, lt);
+            acc = fmaf(o8[i], f, acc);
+        }
+    }
+    for (; s < nparts; s++) {
+        const float2 m1 = ml[s];
+        const float f = exp2f(m1.x - mx);
+        lt = fmaf(m1.y, f, lt);
+        acc = fmaf(po[(size_t)s * p.head_dim], f, acc);
     }
     p.out[qrow * p.head_dim + d] = acc / lt;
 }
@@ -475,7 +501,7 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
                     "128", name, p.head_dim);
     if (p.block == 0)
         return fail(AB_ERR_INVALID, "%s: a page table addresses blocks, and Block is 0", name);
-    // Positions per partition: 256 where that already gives every SM its eight CTAs; a small grid (a
+    // Positions per partition: 256 where that fills at least three quarters of the SMs' CTA slots; a small grid (a
     // tensor-parallel shard's few KV heads, a short batch) takes 128 or 64 so that the K/V stream is
     // spread over all SMs (the partial results grow by the same factor and stay small).
     {
@@ -485,7 +511,7 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
         const uint64_t slots = 8ull * (uint64_t)sm_count();
         p.psize = 64;
         for (uint32_t ps = kPartition; ps >= 128; ps /= 2)
-            if ((uint64_t)((p.capacity + ps - 1) / ps) * per_part >= slots) { p.psize = ps; break; }
+            if ((uint64_t)((p.capacity + ps - 1) / ps) * per_part * 4 >= slots * 3) { p.psize = ps; break; }
     }
     p.parts = (p.capacity + p.psize - 1) / p.psize;
     if (p.parts == 0) p.parts = 1;

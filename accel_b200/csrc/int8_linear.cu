@@ -64,8 +64,8 @@ __device__ __forceinline__ void i8_unpack4(uint32_t w, float (&f)[4])
 
 // grid = (ceil(N / 256), splits), cluster = (1, splits, 1).  MR activation rows (m0 .. m0 + MR - 1).
 // Thread (ty, tx): tx = threadIdx % 16 owns columns 16 tx .. 16 tx + 15 (one 16-byte load per row, a
-// half warp reads 256 contiguous bytes), ty = threadIdx / 16 the rows k = ty, ty + 16, ...; sixteen
-// rows (eight for MR = 2, four for MR = 4) are in flight per thread with their scales and activations.
+// half warp reads 256 contiguous bytes), ty = threadIdx / 16 the rows k = ty, ty + 16, ...; eight rows
+// (four for MR = 4) are in flight per thread, about 10 MB over the device.
 template <int MR>
 __global__ void __launch_bounds__(kI8Threads)
 int8_rows_kernel(const float *__restrict__ a, const int8_t *__restrict__ bq, const __half *__restrict__ bs,
@@ -73,7 +73,7 @@ int8_rows_kernel(const float *__restrict__ a, const int8_t *__restrict__ bq, con
 {
     __shared__ float part[MR][kI8Cols];          // the CTA's sums over its 16 row phases
     cg::cluster_group cluster = cg::this_cluster();
-    constexpr int kFlight = MR == 1 ? 16 : (MR == 2 ? 8 : 4);      // rows in flight per thread
+    constexpr int kFlight = MR <= 2 ? 8 : 4;
     const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const uint32_t col = blockIdx.x * kI8Cols + tx * 16;
     const uint32_t kbeg = blockIdx.y * kc, kend = min(K, kbeg + kc);
@@ -88,7 +88,6 @@ int8_rows_kernel(const float *__restrict__ a, const int8_t *__restrict__ bq, con
         for (uint32_t k = kbeg + ty; k < kend; k += kFlight * kI8Phases) {
             uint4 q[kFlight];
             unsigned short sbits[kFlight];       // raw: converting here would wait for each load in turn
-            float av[kFlight][MR];               // the rows' activations, loaded with the weights, not after them
 #pragma unroll
             for (int u = 0; u < kFlight; u++) {
                 const uint32_t kk = k + u * kI8Phases;
@@ -98,8 +97,6 @@ int8_rows_kernel(const float *__restrict__ a, const int8_t *__restrict__ bq, con
                     const uint64_t flat = (uint64_t)kk * N + col;
                     q[u] = __ldg(reinterpret_cast<const uint4 *>(bq + flat));
                     sbits[u] = __ldg(reinterpret_cast<const unsigned short *>(bs) + (flat >> 5));
-#pragma unroll
-                    for (int m = 0; m < MR; m++) av[u][m] = __ldg(ar + (size_t)m * K + kk);
                 }
             }
             float s[kFlight];
@@ -120,8 +117,9 @@ int8_rows_kernel(const float *__restrict__ a, const int8_t *__restrict__ bq, con
                     }
 #pragma unroll
                     for (int m = 0; m < MR; m++) {
+                        const float av = __ldg(ar + (size_t)m * K + kk);
 #pragma unroll
-                        for (int j = 0; j < 16; j++) acc[m][j] = fmaf(av[u][m], w[j], acc[m][j]);
+                        for (int j = 0; j < 16; j++) acc[m][j] = fmaf(av, w[j], acc[m][j]);
                     }
                 }
             }

@@ -650,12 +650,14 @@ class DecodeEngine:
         if self.shard.tp == 1:
             return self.logits_local
         import torch.distributed as dist
-        widths = {len(Shard.plan(self.cfg, self.shard.tp, r).vocab) for r in range(self.shard.tp)}
-        if len(widths) != 1:
-            raise ValueError("full_logits: the ranks' vocabulary shards differ in width")
-        parts = [torch.empty_like(self.logits_local) for _ in range(self.shard.tp)]
-        dist.all_gather(parts, self.logits_local.contiguous(), group=self.group)
-        return torch.cat(parts, dim=1)
+        # the shards are whole 128-column groups and may differ by one group: gather at the widest
+        widths = [len(Shard.plan(self.cfg, self.shard.tp, r).vocab) for r in range(self.shard.tp)]
+        wmax = max(widths)
+        mine = torch.zeros((self.batch, wmax), dtype=torch.float32, device=self.dev)
+        mine[:, :self.logits_local.shape[1]] = self.logits_local
+        parts = [torch.empty_like(mine) for _ in range(self.shard.tp)]
+        dist.all_gather(parts, mine, group=self.group)
+        return torch.cat([parts[r][:, :widths[r]] for r in range(self.shard.tp)], dim=1)
 
     def prepare(self):
         if self.cfg.cache_dtype == torch.float16 and not hasattr(self, "_k16"):
