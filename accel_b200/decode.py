@@ -408,7 +408,7 @@ class DecodeEngine:
         attn, act = z(M, self.hq * D), z(M, len(self.shard.ffn))
         scale = float(np.float32(1.0) / np.float32(np.sqrt(D)))
         launch = self.ops.launch
-        pages_of = [self.pages[sq].contiguous() for sq in range(B)]
+        pages_of = [self.pages[sq].clone() for sq in range(B)]     # own allocations: a row of the table may start anywhere
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         for p0 in range(base0, base0 + T, S):

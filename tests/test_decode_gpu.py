@@ -217,7 +217,7 @@ def test_prefill_leaves_the_cache_a_token_by_token_decode_leaves(cache_dtype):
     engines = []
     for _ in range(2):
         model = dec.DecodeModel(cfg, dec.Shard.plan(cfg, 1, 0), DEV, seed=3, std=0.08)
-        engines.append(dec.DecodeEngine(model, batch, max_context=64))
+        engines.append(dec.DecodeEngine(model, batch, max_context=72))     # 5 pages per row: rows of the table are not 16-byte aligned
     stepwise, bulk = engines
     for s in range(batch):
         stepwise.reserve(s, T + 2)
