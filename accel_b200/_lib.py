@@ -120,6 +120,8 @@ SYMBOLS = [
                                                 C.c_size_t]),
     ("ab_peer_allreduce_inplace_add_rmsnorm_f32", C.c_int, [_P, C.POINTER(_P), _P, C.c_int, C.c_int, C.c_size_t, _P, _P,
                                                             _P, _P, C.c_uint32, C.c_uint32, C.c_uint32, C.c_size_t]),
+    ("ab_peer_allreduce_inplace_add_rmsnorm_amax_f32", C.c_int, [_P, C.POINTER(_P), _P, C.c_int, C.c_int, C.c_size_t, _P, _P,
+                                                                 _P, _P, C.c_uint32, C.c_uint32, C.c_uint32, C.c_size_t, _P]),
     ("ab_peer_allreduce_error", C.c_int, [_P, C.POINTER(C.c_uint32)]),
     ("ab_peer_allreduce_set_spin_limit", C.c_int, [_P, C.c_uint32]),
     ("ab_peer_allreduce_clear_error", C.c_int, [_P]),

@@ -104,6 +104,9 @@ static const KernelEntry kKernels[] = {
     {"QuantMatMulInt4Packed", 3, 16, launch_quant_matmul_int4_packed},
     {"QuantMatMulInt4PackedSplit3", 5, 32, launch_quant_matmul_int4_packed_split3},
     {"QuantMatMulInt4PackedSwiGLU", 3, 16, launch_quant_matmul_int4_packed_swiglu},
+    {"QuantMatMulInt4PackedA", 4, 16, launch_quant_matmul_int4_packed_a},
+    {"QuantMatMulInt4PackedSplit3A", 6, 32, launch_quant_matmul_int4_packed_split3_a},
+    {"QuantMatMulInt4PackedSwiGLUA", 4, 16, launch_quant_matmul_int4_packed_swiglu_a},
     {"AttentionDecode", 5, 16, launch_attention_decode},
     {"AttentionDecodeF16", 5, 16, launch_attention_decode_f16},
     {"AttentionDecodePaged", 6, 32, launch_attention_decode_paged},
@@ -152,6 +155,7 @@ static const KernelEntry kKernels[] = {
     {"Int4Quantize", 4, 0, launch_int4_quantize},
     {"DecodeStepInputs", 7, 32, launch_decode_step_inputs},
     {"AddRMSNorm", 5, 16, launch_add_rmsnorm},
+    {"AddRMSNormAmax", 6, 16, launch_add_rmsnorm_amax},
     {"RopeScatterQKV", 8, 32, launch_rope_scatter_qkv},
     {"RopeScatterQKVF16", 8, 32, launch_rope_scatter_qkv_f16},
 };

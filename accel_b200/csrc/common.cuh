@@ -136,6 +136,10 @@ int launch_quant_matvec_int4_packed(Launch &);
 int launch_quant_matmul_int4_packed(Launch &);
 int launch_quant_matmul_int4_packed_split3(Launch &);
 int launch_quant_matmul_int4_packed_swiglu(Launch &);
+int launch_quant_matmul_int4_packed_a(Launch &);
+int launch_quant_matmul_int4_packed_split3_a(Launch &);
+int launch_quant_matmul_int4_packed_swiglu_a(Launch &);
+int launch_add_rmsnorm_amax(Launch &);
 
 // launchers, one per reference kernel name (defined beside their kernels)
 int launch_quant_matvec_int4(Launch &);

@@ -17,9 +17,11 @@ static inline unsigned blocks_for(size_t n, int per) { return (unsigned)((n + pe
 template <int PER>
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ delta,
                                                           const float *__restrict__ w, float *__restrict__ sum_out,
-                                                          float *__restrict__ norm_out, uint32_t width, float eps)
+                                                          float *__restrict__ norm_out, uint32_t width, float eps,
+                                                          float *__restrict__ amax_out)
 {
     __shared__ float red[8];
+    __shared__ uint32_t red_mx[8];
     pdl_enter();
     const size_t base = (size_t)blockIdx.x * width;
     float v[PER];
@@ -43,14 +45,38 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const float *__restric
     for (int i = 0; i < 8; i++) total += red[i];
     const float scale = (float)(1.0 / sqrt((double)(total / (float)width + eps)));
 #pragma unroll
+    uint32_t mx = 0;
+#pragma unroll
     for (int j = 0; j < PER; j++) {
         const uint32_t i = threadIdx.x + 256 * j;
-        if (i < width) norm_out[base + i] = v[j] * scale * w[i];
+        if (i < width) {
+            const float o = v[j] * scale * w[i];
+            norm_out[base + i] = o;
+            mx = max(mx, __float_as_uint(fabsf(o)));
+        }
+    }
+    if (amax_out) {
+        // the row's largest magnitude, for the int4 product that reads the row next (it scales its f16
+        // operand by a power of two taken from it): the product then needs no kernel of its own for it
+        mx = __reduce_max_sync(0xffffffffu, mx);
+        if ((threadIdx.x & 31) == 0) red_mx[threadIdx.x >> 5] = mx;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+#pragma unroll
+            for (int i = 1; i < 8; i++) mx = max(mx, red_mx[i]);
+            amax_out[blockIdx.x] = __uint_as_float(mx);
+        }
     }
 }
 
-int launch_add_rmsnorm(Launch &l)
-{   // x, delta, w, sum_out, norm_out; RowDims{Rows,Width,Eps}
+static int launch_add_rmsnorm_any(Launch &l, bool with_amax);
+int launch_add_rmsnorm(Launch &l) { return launch_add_rmsnorm_any(l, false); }
+// x, delta, w, sum_out, norm_out, amax_out f32[rows]; RowDims: AddRMSNorm that also leaves every row's largest
+// |norm| for the prepacked int4 product that follows (QuantMatMulInt4Packed...A)
+int launch_add_rmsnorm_amax(Launch &l) { return launch_add_rmsnorm_any(l, true); }
+
+static int launch_add_rmsnorm_any(Launch &l, bool with_amax)
+{   // x, delta, w, sum_out, norm_out[, amax_out]; RowDims{Rows,Width,Eps}
     if (l.query_ws) { l.ws_need = 0; return AB_OK; }
     uint32_t rows = u32_at(l.u, 0), width = u32_at(l.u, 4);
     float eps = f32_at(l.u, 8);
@@ -63,10 +89,15 @@ int launch_add_rmsnorm(Launch &l)
     if (rows == 0) return AB_OK;
     auto a = ptr<const float>(l, 0), d = ptr<const float>(l, 1), w = ptr<const float>(l, 2);
     auto s = ptr<float>(l, 3), o = ptr<float>(l, 4);
+    float *mx = nullptr;
+    if (with_amax) {
+        if (l.len[5] < rows) return fail(AB_ERR_INVALID, "AddRMSNormAmax: Rows=%u; amax[%u]", rows, l.len[5]);
+        mx = ptr<float>(l, 5);
+    }
     cudaError_t e;
-    if (width <= 256 * 4) e = launch_dependent(add_rmsnorm_kernel<4>, dim3(rows), dim3(256), 0, l.stream, a, d, w, s, o, width, eps);
-    else if (width <= 256 * 16) e = launch_dependent(add_rmsnorm_kernel<16>, dim3(rows), dim3(256), 0, l.stream, a, d, w, s, o, width, eps);
-    else e = launch_dependent(add_rmsnorm_kernel<32>, dim3(rows), dim3(256), 0, l.stream, a, d, w, s, o, width, eps);
+    if (width <= 256 * 4) e = launch_dependent(add_rmsnorm_kernel<4>, dim3(rows), dim3(256), 0, l.stream, a, d, w, s, o, width, eps, mx);
+    else if (width <= 256 * 16) e = launch_dependent(add_rmsnorm_kernel<16>, dim3(rows), dim3(256), 0, l.stream, a, d, w, s, o, width, eps, mx);
+    else e = launch_dependent(add_rmsnorm_kernel<32>, dim3(rows), dim3(256), 0, l.stream, a, d, w, s, o, width, eps, mx);
     count_launch();
     return check_cuda(e, "AddRMSNorm");
 }

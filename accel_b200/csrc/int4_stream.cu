@@ -920,74 +920,88 @@ static size_t packed_workspace(uint32_t M, uint32_t K)
     return packed_tiles(M) ? int4_gemm_workspace(M, K) : int4_stream_workspace(M);
 }
 
-static int launch_packed(Launch &l, const char *name, uint32_t M, uint32_t N, uint32_t K)
+// The "...A" names take the activation rows' largest magnitudes as a second binding (amax f32[M], what
+// AddRMSNormAmax leaves): the decode kernel then needs no kernel of its own for them.  ax = 1 where the
+// binding is present; the batch kernel (from kPackedTileFromRows rows) finds its own factors and ignores it.
+static int launch_packed(Launch &l, const char *name, uint32_t M, uint32_t N, uint32_t K, int ax = 0)
 {
     if (!int4_stream_ok(M, N, K))
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u; the prepacked form needs N a multiple of 128 and K a "
                     "multiple of 4", name, M, N, K);
-    const size_t ws = packed_workspace(M, K);
+    const size_t ws = (ax && !packed_tiles(M)) ? 0 : packed_workspace(M, K);
     if (l.query_ws) { l.ws_need = ws; return AB_OK; }
     const size_t need = int4_stream_packed_bytes(N, K);
-    if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1] * 4 < need || l.len[2] < (uint64_t)M * N)
+    if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1 + ax] * 4 < need || l.len[2 + ax] < (uint64_t)M * N ||
+        (ax && l.len[1] < M))
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u needs a[%llu] packed[%zu bytes] out[%llu]; the lengths "
                     "block says %u, %u words, %u", name, M, N, K, (unsigned long long)M * K, need,
-                    (unsigned long long)M * N, l.len[0], l.len[1], l.len[2]);
+                    (unsigned long long)M * N, l.len[0], l.len[1 + ax], l.len[2 + ax]);
     if (ws > l.ws_bytes || (ws && !l.ws))
         return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, ws, l.ws_bytes);
     if (packed_tiles(M))
-        return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1), kSxPlain,
-                                  ptr<float>(l, 2), nullptr, nullptr, 0, 0, M, N, K, N, l.ws);
-    return run_int4_stream(l.stream, ptr<const float>(l, 0), nullptr, ptr<const unsigned char>(l, 1), ptr<float>(l, 2),
-                           M, N, K, N, l.ws, sx_pdl());
+        return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1 + ax), kSxPlain,
+                                  ptr<float>(l, 2 + ax), nullptr, nullptr, 0, 0, M, N, K, N, l.ws);
+    return run_int4_stream(l.stream, ptr<const float>(l, 0), ax ? ptr<const float>(l, 1) : nullptr,
+                           ptr<const unsigned char>(l, 1 + ax), ptr<float>(l, 2 + ax), M, N, K, N, l.ws, sx_pdl());
 }
 
 // a, packed, out0, out1, out2; uniform {M, N, K, N1, N2, 0, 0, 0}: columns [0, N1) of the product go to
 // out0 [M][N1], [N1, N1 + N2) to out1 [M][N2], the rest to out2 (the fused q | k | v product)
-int launch_quant_matmul_int4_packed_split3(Launch &l)
+static int launch_split3(Launch &l, const char *name, int ax);
+int launch_quant_matmul_int4_packed_split3(Launch &l) { return launch_split3(l, "QuantMatMulInt4PackedSplit3", 0); }
+int launch_quant_matmul_int4_packed_split3_a(Launch &l) { return launch_split3(l, "QuantMatMulInt4PackedSplit3A", 1); }
+
+static int launch_split3(Launch &l, const char *name, int ax)
 {
-    const char *name = "QuantMatMulInt4PackedSplit3";
     const uint32_t M = u32_at(l.u, 0), N = u32_at(l.u, 4), K = u32_at(l.u, 8), N1 = u32_at(l.u, 12), N2 = u32_at(l.u, 16);
     if (!int4_stream_ok(M, N, K) || N1 % 128 || N2 % 128 || N1 == 0 || N2 == 0 || (uint64_t)N1 + N2 >= N)
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u N1=%u N2=%u; N, N1 and N2 are multiples of 128 with "
                     "N1 + N2 < N, K a multiple of 4", name, M, N, K, N1, N2);
-    const size_t ws = packed_workspace(M, K);
+    const size_t ws = (ax && !packed_tiles(M)) ? 0 : packed_workspace(M, K);
     if (l.query_ws) { l.ws_need = ws; return AB_OK; }
     const uint32_t N3 = N - N1 - N2;
-    if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1] * 4 < int4_stream_packed_bytes(N, K) ||
-        l.len[2] < (uint64_t)M * N1 || l.len[3] < (uint64_t)M * N2 || l.len[4] < (uint64_t)M * N3)
+    if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1 + ax] * 4 < int4_stream_packed_bytes(N, K) ||
+        l.len[2 + ax] < (uint64_t)M * N1 || l.len[3 + ax] < (uint64_t)M * N2 || l.len[4 + ax] < (uint64_t)M * N3 ||
+        (ax && l.len[1] < M))
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u N1=%u N2=%u; a[%u] packed[%u words] out0[%u] out1[%u] out2[%u]",
-                    name, M, N, K, N1, N2, l.len[0], l.len[1], l.len[2], l.len[3], l.len[4]);
+                    name, M, N, K, N1, N2, l.len[0], l.len[1 + ax], l.len[2 + ax], l.len[3 + ax], l.len[4 + ax]);
     if (ws > l.ws_bytes || (ws && !l.ws))
         return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, ws, l.ws_bytes);
     if (packed_tiles(M))
-        return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1), kSxSplit3,
-                                  ptr<float>(l, 2), ptr<float>(l, 3), ptr<float>(l, 4), N1, N1 + N2, M, N, K, N1, l.ws);
-    return run_int4_stream_mode(l.stream, ptr<const float>(l, 0), nullptr, ptr<const unsigned char>(l, 1), kSxSplit3,
-                                ptr<float>(l, 2), ptr<float>(l, 3), ptr<float>(l, 4), N1, N1 + N2, M, N, K, N1, l.ws,
-                                sx_pdl());
+        return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1 + ax), kSxSplit3,
+                                  ptr<float>(l, 2 + ax), ptr<float>(l, 3 + ax), ptr<float>(l, 4 + ax), N1, N1 + N2, M, N, K,
+                                  N1, l.ws);
+    return run_int4_stream_mode(l.stream, ptr<const float>(l, 0), ax ? ptr<const float>(l, 1) : nullptr,
+                                ptr<const unsigned char>(l, 1 + ax), kSxSplit3, ptr<float>(l, 2 + ax), ptr<float>(l, 3 + ax),
+                                ptr<float>(l, 4 + ax), N1, N1 + N2, M, N, K, N1, l.ws, sx_pdl());
 }
 
 // a, packed, out; GEMMDims{M, N, K}: the 128-column groups of the packed matrix alternate gate, up;
 // out [M][N / 2] = SwiGLU(gate, up)
-int launch_quant_matmul_int4_packed_swiglu(Launch &l)
+static int launch_swiglu(Launch &l, const char *name, int ax);
+int launch_quant_matmul_int4_packed_swiglu(Launch &l) { return launch_swiglu(l, "QuantMatMulInt4PackedSwiGLU", 0); }
+int launch_quant_matmul_int4_packed_swiglu_a(Launch &l) { return launch_swiglu(l, "QuantMatMulInt4PackedSwiGLUA", 1); }
+
+static int launch_swiglu(Launch &l, const char *name, int ax)
 {
-    const char *name = "QuantMatMulInt4PackedSwiGLU";
     const uint32_t M = u32_at(l.u, 0), N = u32_at(l.u, 4), K = u32_at(l.u, 8);
     if (!int4_stream_ok(M, N, K) || N % 256)
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u; N is a multiple of 256 (gate and up groups in pairs), K a "
                     "multiple of 4", name, M, N, K);
-    const size_t ws = packed_workspace(M, K);
+    const size_t ws = (ax && !packed_tiles(M)) ? 0 : packed_workspace(M, K);
     if (l.query_ws) { l.ws_need = ws; return AB_OK; }
-    if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1] * 4 < int4_stream_packed_bytes(N, K) || l.len[2] < (uint64_t)M * (N / 2))
+    if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1 + ax] * 4 < int4_stream_packed_bytes(N, K) ||
+        l.len[2 + ax] < (uint64_t)M * (N / 2) || (ax && l.len[1] < M))
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u; a[%u] packed[%u words] out[%u]", name, M, N, K, l.len[0],
-                    l.len[1], l.len[2]);
+                    l.len[1 + ax], l.len[2 + ax]);
     if (ws > l.ws_bytes || (ws && !l.ws))
         return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, ws, l.ws_bytes);
     if (packed_tiles(M))
-        return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1), kSxSwiGLU,
-                                  ptr<float>(l, 2), nullptr, nullptr, 0, 0, M, N, K, N / 2, l.ws);
-    return run_int4_stream_mode(l.stream, ptr<const float>(l, 0), nullptr, ptr<const unsigned char>(l, 1), kSxSwiGLU,
-                                ptr<float>(l, 2), nullptr, nullptr, 0, 0, M, N, K, N / 2, l.ws, sx_pdl());
+        return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1 + ax), kSxSwiGLU,
+                                  ptr<float>(l, 2 + ax), nullptr, nullptr, 0, 0, M, N, K, N / 2, l.ws);
+    return run_int4_stream_mode(l.stream, ptr<const float>(l, 0), ax ? ptr<const float>(l, 1) : nullptr,
+                                ptr<const unsigned char>(l, 1 + ax), kSxSwiGLU, ptr<float>(l, 2 + ax), nullptr, nullptr, 0, 0,
+                                M, N, K, N / 2, l.ws, sx_pdl());
 }
 
 int launch_quant_matvec_int4_packed(Launch &l)
@@ -998,6 +1012,11 @@ int launch_quant_matvec_int4_packed(Launch &l)
 int launch_quant_matmul_int4_packed(Launch &l)
 {
     return launch_packed(l, "QuantMatMulInt4Packed", u32_at(l.u, 0), u32_at(l.u, 4), u32_at(l.u, 8));
+}
+
+int launch_quant_matmul_int4_packed_a(Launch &l)
+{
+    return launch_packed(l, "QuantMatMulInt4PackedA", u32_at(l.u, 0), u32_at(l.u, 4), u32_at(l.u, 8), 1);
 }
 
 }  // namespace ab

@@ -301,10 +301,11 @@ template <int PER>
 __global__ void __launch_bounds__(kArThreads)
 peer_allreduce_inplace_add_rmsnorm_kernel(ArPeers peers, ArState *state, int rank, int world, size_t offset,
                                           const float *residual, const float *gain, float *sum_out,
-                                          float *norm_out, uint32_t width, float eps)
+                                          float *norm_out, uint32_t width, float eps, float *amax_out)
 {
     __shared__ int s_fail;
     __shared__ float red[8];
+    __shared__ uint32_t red_mx[8];
     const uint32_t e = *reinterpret_cast<volatile uint32_t *>(&state->epoch) + 1;
     const size_t base = (size_t)blockIdx.x * width;
     if (!signal_and_wait(peers, state, rank, world, e, &s_fail)) {
@@ -356,10 +357,25 @@ peer_allreduce_inplace_add_rmsnorm_kernel(ArPeers peers, ArState *state, int ran
 #pragma unroll
         for (int i = 0; i < 8; i++) total += red[i];
         const float scale = (float)(1.0 / sqrt((double)(total / (float)width + eps)));
+        uint32_t mx = 0;
 #pragma unroll
         for (int j = 0; j < PER; j++) {
             const uint32_t i = threadIdx.x + kArThreads * j;
-            if (i < width) norm_out[base + i] = v[j] * scale * gain[i];
+            if (i < width) {
+                const float o = v[j] * scale * gain[i];
+                norm_out[base + i] = o;
+                mx = max(mx, __float_as_uint(fabsf(o)));
+            }
+        }
+        if (amax_out) {            // the row's largest |norm|, for the int4 product that reads the row next
+            mx = __reduce_max_sync(0xffffffffu, mx);
+            if ((threadIdx.x & 31) == 0) red_mx[threadIdx.x >> 5] = mx;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+#pragma unroll
+                for (int i = 1; i < kArThreads / 32; i++) mx = max(mx, red_mx[i]);
+                amax_out[blockIdx.x] = __uint_as_float(mx);
+            }
         }
     }
     finish_call(state, e);
@@ -528,6 +544,18 @@ extern "C" AB_API int ab_peer_allreduce_inplace_add_rmsnorm_f32(void *stream, vo
                                                                 uint32_t width, uint32_t eps_bits,
                                                                 size_t buffer_bytes)
 {
+    return ab_peer_allreduce_inplace_add_rmsnorm_amax_f32(stream, peer_buffers, state, rank, world, region_offset_bytes,
+                                                          residual, gain, sum_out, norm_out, rows, width, eps_bits,
+                                                          buffer_bytes, nullptr);
+}
+
+extern "C" AB_API int ab_peer_allreduce_inplace_add_rmsnorm_amax_f32(void *stream, void *const *peer_buffers, void *state,
+                                                                     int rank, int world, size_t region_offset_bytes,
+                                                                     const float *residual, const float *gain,
+                                                                     float *sum_out, float *norm_out, uint32_t rows,
+                                                                     uint32_t width, uint32_t eps_bits,
+                                                                     size_t buffer_bytes, float *amax_out)
+{
     using namespace ab;
     const char *what = "ab_peer_allreduce_inplace_add_rmsnorm_f32";
     ArPeers peers{};
@@ -548,10 +576,10 @@ extern "C" AB_API int ab_peer_allreduce_inplace_add_rmsnorm_f32(void *stream, vo
     const size_t off = region_offset_bytes / 4;
     if (width <= (uint32_t)kArThreads * 4)
         peer_allreduce_inplace_add_rmsnorm_kernel<4><<<rows, kArThreads, 0, st>>>(peers, sp, rank, world, off, residual,
-                                                                                  gain, sum_out, norm_out, width, eps);
+                                                                                  gain, sum_out, norm_out, width, eps, amax_out);
     else
         peer_allreduce_inplace_add_rmsnorm_kernel<16><<<rows, kArThreads, 0, st>>>(peers, sp, rank, world, off, residual,
-                                                                                   gain, sum_out, norm_out, width, eps);
+                                                                                   gain, sum_out, norm_out, width, eps, amax_out);
     count_launch();
     return check_cuda(cudaGetLastError(), what);
 }

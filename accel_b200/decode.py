@@ -331,6 +331,7 @@ class DecodeEngine:
         self.top_pairs = z(B, sh.tp, 2)          # every rank's (value, index) per row, after the exchange
         self._my_pairs = z(B, sh.tp, 2)          # this rank's slot filled, the others zero
         self.next_tokens = z(B, dt=I32)
+        self.h_amax = z(B)                       # every row's largest |h|, left by the norm kernels for the products
         self._proj = [self.proj, self.proj]      # where wo and down write their partial results
         if sh.tp > 1 and collective == "peer":
             # the row-parallel products write straight into this rank's peer buffer: two regions
@@ -540,13 +541,20 @@ class DecodeEngine:
         scatter = "ScatterRowsF16" if f16 else "ScatterRows"
         norm_u = _u("<IIfI", B, d, cfg.eps, 0)
 
+        # with the prepacked products the norm kernels also leave every row's largest |h|, and the
+        # products that read h take it as a binding instead of running a kernel of their own for it
+        h_has_amax = False
+
         def add_norm(gain, which):
             """x <- x + (sum over the ranks of the partial product `which`); h <- RMSNorm(x) * gain"""
-            nonlocal x, x2
+            nonlocal x, x2, h_has_amax
             proj = self._proj[which]
+            h_has_amax = False
             if self._peer is not None and self.fuse:
                 # the all-reduce's summing stage adds the residual and normalises: one launch
-                self._peer.all_reduce_region_add_rms_norm(which, x, gain, x2, self.h, cfg.eps)
+                self._peer.all_reduce_region_add_rms_norm(which, x, gain, x2, self.h, cfg.eps,
+                                                          amax_out=self.h_amax if self.use_packed else None)
+                h_has_amax = self.use_packed
                 self._count += 1
                 x, x2 = x2, x
                 return
@@ -556,7 +564,11 @@ class DecodeEngine:
                 proj = self.proj
             else:
                 self._all_reduce(proj)
-            if self.fuse:
+            if self.fuse and self.use_packed:
+                L("AddRMSNormAmax", [x, proj, gain, x2, self.h, self.h_amax], norm_u)
+                h_has_amax = True
+                x, x2 = x2, x
+            elif self.fuse:
                 L("AddRMSNorm", [x, proj, gain, x2, self.h], norm_u)
                 x, x2 = x2, x
             else:
@@ -567,6 +579,7 @@ class DecodeEngine:
         for li, lay in enumerate(self.model.layers):
             if li == 0:
                 L("RMSNorm", [x, lay.g1, self.h], norm_u)
+                h_has_amax = False
             else:
                 add_norm(lay.g1, 1)              # the previous layer's second residual add
 
@@ -599,8 +612,12 @@ class DecodeEngine:
             if self.use_packed and self.fuse:
                 # one product over q | k | v, each written to its own buffer
                 w = lay.wqkv
-                L("QuantMatMulInt4PackedSplit3", [self.h, w.packed, self.q, self.k, self.v],
-                  _u("<IIIIIIII", B, w.N, w.K, self.hq * D, self.hk * D, 0, 0, 0))
+                if h_has_amax:
+                    L("QuantMatMulInt4PackedSplit3A", [self.h, self.h_amax, w.packed, self.q, self.k, self.v],
+                      _u("<IIIIIIII", B, w.N, w.K, self.hq * D, self.hk * D, 0, 0, 0))
+                else:
+                    L("QuantMatMulInt4PackedSplit3", [self.h, w.packed, self.q, self.k, self.v],
+                      _u("<IIIIIIII", B, w.N, w.K, self.hq * D, self.hk * D, 0, 0, 0))
             else:
                 # q, k and v depend only on h: three branches that may run side by side
                 self._parallel([q_branch, k_branch, v_branch])
@@ -616,14 +633,21 @@ class DecodeEngine:
             if self.use_packed and self.fuse:
                 # gate and up as one product whose epilogue applies SwiGLU
                 w = lay.wgu
-                L("QuantMatMulInt4PackedSwiGLU", [self.h, w.packed, self.act], _u("<IIII", B, w.N, w.K, 0))
+                if h_has_amax:
+                    L("QuantMatMulInt4PackedSwiGLUA", [self.h, self.h_amax, w.packed, self.act], _u("<IIII", B, w.N, w.K, 0))
+                else:
+                    L("QuantMatMulInt4PackedSwiGLU", [self.h, w.packed, self.act], _u("<IIII", B, w.N, w.K, 0))
             else:
                 self._parallel([lambda: self._linear(self.h, lay.wg, self.gate),
                                 lambda: self._linear(self.h, lay.wu, self.up)])
                 L("SwiGLU", [self.gate, self.up, self.act])
             self._linear(self.act, lay.wd_p if self.use_packed else lay.wd, self._proj[1])
         add_norm(self.model.g_final, 1)
-        self._linear(self.h, self.model.lm_head_p if self.use_packed else self.model.lm_head, self.logits_local)
+        if h_has_amax:
+            w = self.model.lm_head_p
+            L("QuantMatMulInt4PackedA", [self.h, self.h_amax, w.packed, self.logits_local], _u("<IIII", B, w.N, w.K, 0))
+        else:
+            self._linear(self.h, self.model.lm_head_p if self.use_packed else self.model.lm_head, self.logits_local)
         if self.shard.tp > 1:
             # each rank owns a column range of the vocabulary: it reduces its columns to one (largest
             # logit, index) pair per row, the ranks exchange the pairs (a sum over slots the others

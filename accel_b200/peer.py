@@ -92,8 +92,10 @@ class PeerAllReduce:
             C.c_void_p(out.data_ptr()), out.numel(), self.nbytes))
         return out
 
-    def all_reduce_region_add_rms_norm(self, i: int, residual, gain, sum_out, norm_out, eps: float, stream=None):
-        """sum_out = residual + (sum over the ranks of region i), norm_out = RMSNorm(sum_out) * gain."""
+    def all_reduce_region_add_rms_norm(self, i: int, residual, gain, sum_out, norm_out, eps: float, stream=None,
+                                       amax_out=None):
+        """sum_out = residual + (sum over the ranks of region i), norm_out = RMSNorm(sum_out) * gain;
+        amax_out [rows] f32 (optional) receives every row's largest |norm_out|."""
         import struct
         at, n = self._region_at[i]
         rows, width = residual.shape
@@ -102,9 +104,10 @@ class PeerAllReduce:
         s = stream if stream is not None else torch.cuda.current_stream(residual.device)
         p = lambda x: C.c_void_p(x.data_ptr())
         eps_bits = struct.unpack("<I", struct.pack("<f", eps))[0]
-        _lib.check(_lib.lib().ab_peer_allreduce_inplace_add_rmsnorm_f32(
+        _lib.check(_lib.lib().ab_peer_allreduce_inplace_add_rmsnorm_amax_f32(
             C.c_void_p(s.cuda_stream), self._ptrs, p(self._state), self.rank, self.world, at, p(residual), p(gain),
-            p(sum_out), p(norm_out), rows, width, eps_bits, self.nbytes))
+            p(sum_out), p(norm_out), rows, width, eps_bits, self.nbytes,
+            p(amax_out) if amax_out is not None else None))
 
     def all_reduce_add_rms_norm(self, t, residual, gain, sum_out, norm_out, eps: float, stream=None):
         """sum_out = residual + all-reduce(t), norm_out = RMSNorm(sum_out) * gain, in one launch;

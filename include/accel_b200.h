@@ -260,6 +260,10 @@ AB_API uint64_t ab_launch_count(void);
  *                    {M,N,K,N1,N2}@0..16 (32 B).  One product whose column ranges land in three matrices (q | k | v).
  *  QuantMatMulInt4PackedSwiGLU   a, packed, out f32[M*N/2]                  GEMMDims.  The 128-column groups of the packed
  *                    matrix alternate gate, up; out = SwiGLU(gate, up) (elementwise.go:85) from the epilogue.
+ *  QuantMatMulInt4PackedA, QuantMatMulInt4PackedSplit3A, QuantMatMulInt4PackedSwiGLUA   the three forms above with
+ *                    one more binding after a: amax f32[M], every activation row's largest magnitude (what
+ *                    AddRMSNormAmax leaves).  The decode kernel scales its f16 operand by a power of two taken from
+ *                    it; without the binding a small kernel finds the maxima first.  Bit-identical results.
  *  GroupedMatMulInt4Packed   x f32[T*K], packed (Experts prepacked matrices end to end), offsets u32[E+1], out f32[T*N]
  *                    GroupedTiledDims.  GroupedMatMulInt4 over prepacked experts, on the tcgen05 tile kernel.
  *  ArgmaxShard       logits f32[rows*Width], pairs f32[rows*Parts*2]        {Width,Rows,Parts,Rank,First}@0..16 (32 B)
@@ -276,6 +280,8 @@ AB_API uint64_t ab_launch_count(void);
  *  AddRMSNorm        x, delta, w, sum f32[rows*width], norm f32[rows*width]  RowDims (16 B).  No reference kernel: ElemAdd
  *                    (elementwise.go:22) followed by RMSNorm (norm.go:46) in one launch, sum = x + delta, norm =
  *                    RMSNorm(sum) * w; bit-identical to the two dispatches.  Width <= 8192.
+ *  AddRMSNormAmax    x, delta, w, sum, norm, amax f32[rows]                  RowDims.  AddRMSNorm that also writes every
+ *                    row's largest |norm| for the ...A product that reads norm next.
  *  RopeScatterQKV, RopeScatterQKVF16   pos_q u32[B*QHeads], pos_k u32[B*KVHeads], slots u32[B], q f32 (in place),
  *                    k f32 (in place), v f32, k_cache, v_cache (f32 / f16 [Capacity, KVHeads, HeadDim])
  *                    {Batch,QHeads,KVHeads,HeadDim,RotaryDim,Capacity,Base f32}@0..24 (32 B).  No reference kernel:
@@ -386,6 +392,13 @@ AB_API int ab_peer_allreduce_inplace_add_rmsnorm_f32(void *stream, void *const *
                                                      const float *residual, const float *gain,
                                                      float *sum_out, float *norm_out, uint32_t rows,
                                                      uint32_t width, uint32_t eps_bits, size_t buffer_bytes);
+/* The same call that also leaves every row's largest |norm_out| in amax_out[rows] (NULL: none), for
+ * the prepacked int4 product that reads norm_out next (QuantMatMulInt4Packed...A). */
+AB_API int ab_peer_allreduce_inplace_add_rmsnorm_amax_f32(void *stream, void *const *peer_buffers, void *state,
+                                                     int rank, int world, size_t region_offset_bytes,
+                                                     const float *residual, const float *gain,
+                                                     float *sum_out, float *norm_out, uint32_t rows,
+                                                     uint32_t width, uint32_t eps_bits, size_t buffer_bytes, float *amax_out);
 /* AB_OK, or AB_ERR_TIMEOUT with *failed_call = the 1-based call that gave up (synchronous). */
 AB_API int ab_peer_allreduce_error(const void *state, uint32_t *failed_call);
 /* How many polls of a peer's flag a CTA spends before it gives up (0 restores the default, about a

@@ -175,3 +175,44 @@ def test_the_swiglu_epilogue_equals_the_product_followed_by_swiglu(M, K, F):
     mm = (lambda q: orc.quant_matmul_int4(a_np, *q, M, F, K)) if M > 1 else \
         (lambda q: orc.quant_matvec_int4(a_np[0], *q, F, K)[None, :])
     assert_close(out.cpu().numpy(), orc.swiglu(mm(qg), mm(qu)), 2e-3, "SwiGLU epilogue against the oracle")
+
+
+@pytest.mark.parametrize("M", [1, 16, 40])
+def test_the_forms_that_take_the_rows_maxima_equal_the_plain_forms(M):
+    """AddRMSNormAmax leaves every row's largest |norm| and the ...A products take it as a binding
+    instead of running a kernel of their own for it: same factors, same kernels, so the results are
+    bit-identical to AddRMSNorm followed by the plain packed products."""
+    import struct
+    K, F = 1024, 512
+    rng = np.random.default_rng(33)
+    x, delta = normal(40, (M, K)), normal(41, (M, K))
+    gain = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    dx, dd, dg = (torch.from_numpy(t).to(DEV) for t in (x, delta, gain))
+    s0, h0 = torch.empty(M, K, device=DEV), torch.empty(M, K, device=DEV)
+    s1, h1 = torch.empty(M, K, device=DEV), torch.empty(M, K, device=DEV)
+    amax = torch.full((M,), float("nan"), device=DEV)
+    runtime.launch("AddRMSNorm", [dx, dd, dg, s0, h0], runtime.row_dims(M, K, 1e-5))
+    runtime.launch("AddRMSNormAmax", [dx, dd, dg, s1, h1, amax], runtime.row_dims(M, K, 1e-5))
+    torch.cuda.synchronize()
+    assert torch.equal(s0, s1) and torch.equal(h0, h1)
+    assert torch.equal(amax, h0.abs().max(dim=1).values)
+    # plain, three-output and SwiGLU products, with and without the maxima
+    N = 2 * F
+    p, s, z = orc.int4_quantize(normal(42, (K, N), 0.02))
+    packed = packed_of(p, s, z, K, N)
+    a0, a1 = torch.empty(M, N, device=DEV), torch.full((M, N), float("nan"), device=DEV)
+    runtime.launch("QuantMatMulInt4Packed", [h0, packed, a0], runtime.gemm_dims(M, N, K))
+    runtime.launch("QuantMatMulInt4PackedA", [h0, amax, packed, a1], runtime.gemm_dims(M, N, K))
+    assert torch.equal(a0, a1)
+    u3 = struct.pack("<IIIIIIII", M, N, K, 512, 256, 0, 0, 0)
+    o0 = [torch.empty(M, n, device=DEV) for n in (512, 256, 256)]
+    o1 = [torch.full((M, n), float("nan"), device=DEV) for n in (512, 256, 256)]
+    runtime.launch("QuantMatMulInt4PackedSplit3", [h0, packed, *o0], u3)
+    runtime.launch("QuantMatMulInt4PackedSplit3A", [h0, amax, packed, *o1], u3)
+    assert all(torch.equal(a, b) for a, b in zip(o0, o1))
+    g0, g1 = torch.empty(M, F, device=DEV), torch.full((M, F), float("nan"), device=DEV)
+    runtime.launch("QuantMatMulInt4PackedSwiGLU", [h0, packed, g0], runtime.gemm_dims(M, N, K))
+    runtime.launch("QuantMatMulInt4PackedSwiGLUA", [h0, amax, packed, g1], runtime.gemm_dims(M, N, K))
+    torch.cuda.synchronize()
+    quant.int4_stream_check()
+    assert torch.equal(g0, g1)
