@@ -15,20 +15,21 @@
 // magnitude and from the group's largest scale, so that B sits in the upper part of the f16 range
 // whatever the magnitude of the activations or weights; it is undone in the f32 epilogue.
 //
-// Two MMAs per 16 weight rows, both D[128 x NB] += A[128 x 16] B[16 x NB] with A in tensor memory:
+// One MMA per 16 weight rows, D[128 x NB] += A[128 x 16] B[16 x NB] with A in tensor memory:
 //   codes  A's 128 rows are the group's 128 columns (one per TMEM lane).  A thread owns a column:
 //          the prepacked stream gives it 32 consecutive k of that column as one 16-byte shared
 //          memory load; four masks per word turn eight codes into four f16x2 registers whose
 //          halves are the f16 SUBNORMALS code * 2^-24 (or * 2^-20: the odd mask keeps the nibble
 //          four bits up, and B carries 1/16 there), exactly; tcgen05.st puts 32 k of the column
 //          into 16 TMEM columns of its lane.  0.7 instructions per weight, no conversion.
-//   zeros  A's row 0 is z[k] (already f16): the same B, one more accumulator, whose lane 0 is
-//          sum_k B[m][k] z[k], so the two sums cancel as they do in exact arithmetic.
+//   zeros  sum_k B[m][k] z[k] on the CUDA cores (fma.rn.f32.f16: exact products of the same rounded
+//          B and the stream's f16 zeros, f32 sums), so the two sums cancel as they do in exact
+//          arithmetic.  (A second MMA for this term was tried: tcgen05.mma has a floor of about 46
+//          cycles per instruction whatever N, so it doubled the loop's time.)
 //   B      K-major in shared memory (8 x 8 core matrices, no swizzle), written per 64-row chunk by
 //          the expander threads from a (global, f32) and the chunk's scales (in the stream).
-// A row whose scale is 0 is the constant z (internal/kernels/int4.go:85-87): its B is 0, both
-// MMAs skip it, and the threads that build B add a z in f32 (a branch taken only where a scale
-// is 0).
+// A row whose scale is 0 is the constant z (internal/kernels/int4.go:85-87): its B is 0, the MMA
+// skips it, and the threads that build B add a z in f32 (a branch taken only where a scale is 0).
 //
 // Stream layout (ab_int4_prepack): a header of one float per group, 2^E_s with E_s =
 // floor(log2(the group's largest scale)), then per group and per chunk of 64 weight rows 4352
@@ -38,12 +39,12 @@
 // group is ONE contiguous run.
 //
 // Roles in a CTA of 320 threads: warps 0-7 expand codes and build B; warp 8 allocates TMEM and one
-// of its lanes issues the MMAs; one lane of warp 9 issues the bulk copies eight chunks ahead.
+// of its lanes issues the MMAs; one lane of warp 9 issues the bulk copies six chunks ahead.
 // Stages are handed over by mbarriers (copy -> full -> expanders -> ready -> MMA -> commit -> free);
 // there is no CTA-wide barrier in the loop.  K splits of a column group form a thread-block
 // cluster: every CTA stores its partial rows into the shared memory of the CTA that owns the row
 // and arrives on that CTA's mbarrier; the owner adds the splits in split order (deterministic, no
-// workspace, no cluster-wide barrier at the end).  Every wait is bounded: one that runs out sets g_sm100_error, the CTA skips its
+// workspace); one cluster-wide barrier at the end keeps the copies' sources alive.  Every wait is bounded: one that runs out sets g_sm100_error, the CTA skips its
 // remaining work, frees its TMEM and returns.
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
@@ -529,8 +530,11 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
     if (splits > 1) {
         // the bulk copies that carry this CTA's partial rows read its shared memory until they are
         // done, which is when every CTA of the cluster has received its rows: nobody leaves before
+        // (relaxed: nothing has to become visible through this barrier; a thread arrives only after
+        // it has seen its own CTA's rows complete, in program order, and the release form costs
+        // about 2000 cycles more)
         __syncwarp();
-        asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+        asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     }
     if (tid == 0) SX_STAMP(6);
