@@ -38,8 +38,9 @@
 // where k % 8 is 2, 3, 6 or 7), 64 zeros (f16, times 16 in those rows).  A CTA's K range of one
 // group is ONE contiguous run.
 //
-// Roles in a CTA of 320 threads: warps 0-7 expand codes and build B; warp 8 allocates TMEM and one
-// of its lanes issues the MMAs; one lane of warp 9 issues the bulk copies six chunks ahead.
+// Roles in a CTA of 352 threads: warps 0-7 expand codes and build B; warp 8 allocates TMEM; one
+// lane each of warps 8 and 10 issues MMAs (two lanes, because one thread gets an MMA out only every
+// 46 cycles); the lanes of warp 9 issue the bulk copies six chunks ahead.
 // Stages are handed over by mbarriers (copy -> full -> expanders -> ready -> MMA -> commit -> free);
 // there is no CTA-wide barrier in the loop.  K splits of a column group form a thread-block
 // cluster: every CTA stores its partial rows into the shared memory of the CTA that owns the row
@@ -58,8 +59,9 @@ namespace cg = cooperative_groups;
 
 namespace ab {
 
-static constexpr int kSxThreads = 320;
+static constexpr int kSxThreads = 352;
 static constexpr int kSxExpanders = 256;
+static constexpr int kSxIssuers = 2;               // lanes that issue MMAs (warps 8 and 10)
 static constexpr int kSxNC = 6;                   // ring stages in flight from global memory
 static constexpr int kSxNA = 3;                   // A (TMEM) and B (shared) stages
 __host__ __device__ constexpr uint32_t sx_tmem_cols(int G) { return G == 1 ? 128u : 256u; }   // per group: D (32) + 3 x 32
@@ -72,7 +74,12 @@ __device__ long long g_sx_trace[64];
 #define SX_FLUSH(base) do { if (blockIdx.x == 0 && blockIdx.y == 0) for (int q_ = 0; q_ < 8; q_++) g_sx_trace[(base) + q_] += sx_acc[q_]; } while (0)
 #define SX_NOW() clock64()
 #define SX_DECL() long long sx_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+__device__ long long g_sx_cta[2048][4];          // per CTA: SM, start, loop end, end (cycles of its SM)
+#define SX_CTA(i) do { const unsigned b_ = blockIdx.y * gridDim.x + blockIdx.x; if (b_ < 2048) { \
+        if ((i) == 1) { unsigned sm_; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_)); g_sx_cta[b_][0] = sm_; } \
+        g_sx_cta[b_][i] = clock64(); } } while (0)
 #else
+#define SX_CTA(i) do { } while (0)
 #define SX_STAMP(i) do { } while (0)
 #define SX_ACC(i, t) do { (void)(t); } while (0)
 #define SX_FLUSH(base) do { } while (0)
@@ -131,7 +138,7 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
     volatile int *s_abort = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid == 0) SX_STAMP(0);
+    if (tid == 0) { SX_STAMP(0); SX_CTA(1); }
     const uint32_t groups = N / 128, g0 = blockIdx.x * G, splits = gridDim.y, split = blockIdx.y;
     const uint32_t gcount = min((uint32_t)G, groups - g0);          // the last tile may hold fewer groups
     const uint32_t c_beg = (uint32_t)((uint64_t)nchunks_total * split / splits);
@@ -142,14 +149,21 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
     const size_t group_stride = (size_t)nchunks_total * kSxChunkBytes;
 
     if (warp == 9) {
-        // the copy warp initialises the barriers and starts the first stages at once, one lane per
-        // stage (issuing a copy takes a few hundred cycles): the weights depend on nothing that
-        // runs before this kernel
-        if (lane == 0) {
-            for (int i = 0; i < kSxNC; i++) { sx_bar_init(&w_full[i], 1); sx_bar_init(&w_empty[i], kSxExpanders / 32); }
-            for (int i = 0; i < kSxNA; i++) { sx_bar_init(&ab_ready[i], kSxExpanders / 32); sx_bar_init(&ab_free[i], 1); }
-            sx_bar_init(done, 1);
-            sx_bar_init(red_bar, 1);                 // completes when every K split's rows have arrived
+        // the copy warp initialises the barriers and starts the first stages at once (the weights
+        // depend on nothing that runs before this kernel).  The barriers lie one after another
+        // (w_full, w_empty, ab_ready, ab_free, done, red_bar): one lane initialises each, and one
+        // lane issues each of the first copies; a single lane doing them in a row spends a few
+        // hundred cycles apiece
+        constexpr int kBars = 2 * kSxNC + 2 * kSxNA + 2;
+        if (lane < kBars) {
+            // w_empty, ab_ready: one arrival per expander warp; ab_free, done: one commit per MMA lane
+            const uint32_t count = lane < kSxNC ? 1u : lane < 2 * kSxNC + kSxNA ? (uint32_t)(kSxExpanders / 32)
+                                   : lane < kBars - 1 ? (uint32_t)kSxIssuers : 1u;
+            sx_bar_init(&w_full[lane], count);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+        if (lane == 31) {
             *s_abort = 0;
             if (splits > 1) {
                 // this CTA owns rows split, split + splits, ... of the tile: their partial sums arrive
@@ -157,15 +171,15 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
                 const uint32_t owned = M > split ? (M - split + splits - 1) / splits : 0u;
                 sx_bar_expect_tx(red_bar, owned * splits * (uint32_t)G * 128u * 4u);
             }
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             SX_STAMP(40);
         }
-        __syncwarp();
-        if ((uint32_t)lane < (uint32_t)kSxNC && (uint32_t)lane < nch) {
-            sx_bar_expect_tx(&w_full[lane], gcount * kSxChunkBytes);
-            for (uint32_t gi = 0; gi < gcount; gi++)
-                sx_bulk_load(ring + lane * kStage + gi * kSxChunkBytes,
-                             stream + gi * group_stride + (size_t)lane * kSxChunkBytes, kSxChunkBytes, &w_full[lane]);
+        {   // lane = stage * G + group: the lane of a stage's first group announces the stage's bytes
+            const uint32_t st0 = (uint32_t)lane / G, gi = (uint32_t)lane % G;
+            if (st0 < (uint32_t)kSxNC && st0 < nch && gi < gcount) {
+                if (gi == 0) sx_bar_expect_tx(&w_full[st0], gcount * kSxChunkBytes);
+                sx_bulk_load(ring + st0 * kStage + gi * kSxChunkBytes,
+                             stream + gi * group_stride + (size_t)st0 * kSxChunkBytes, kSxChunkBytes, &w_full[st0]);
+            }
         }
         if (lane == 0) SX_STAMP(41);
     }
@@ -205,10 +219,18 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
             }
             SX_FLUSH(32);
         }
-    } else if (warp == 8) {
-        // ---- the MMA lane: per group and 16 weight rows, codes (A in tensor memory) times B
+    } else if (warp == 8 || warp == 10) {
+        // ---- the MMA lanes: per group and 16 weight rows, codes (A in tensor memory) times B.  One
+        //      thread gets an MMA of this shape out every 46 cycles whatever the tensor pipe has to
+        //      do (measured: 8 cycles' worth at N = 16), and several threads overlap, so two lanes
+        //      share the work, each with an accumulator of its own (MMAs of different threads are
+        //      not ordered among themselves): with two groups a lane takes one group, with one
+        //      group a lane takes two of the four k slices and the epilogue adds the two sums
         if (lane == 0) {
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((128u >> 4) << 24);
+            const uint32_t q = warp == 8 ? 0u : 1u;
+            const uint32_t gi = G == 2 ? q : 0u, j0 = G == 2 ? 0u : 2u * q, nj = G == 2 ? 4u : 2u;
+            const uint32_t dcol = tmem + (G == 2 ? gi * 32u : q * 16u);
             SX_DECL();
             for (uint32_t c = 0; c < nch; c++) {
                 const uint32_t ab = c % kSxNA;
@@ -216,18 +238,19 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
                 if (!sx_bar_wait(&ab_ready[ab], (c / kSxNA) & 1)) { *s_abort = 1; break; }
                 SX_ACC(0, tt);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (uint32_t gi = 0; gi < gcount; gi++) {
+                if (gi < gcount) {
                     const uint32_t bbase = sx_smem(bring + (ab * G + gi) * kSxBStage);
-#pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        sx_mma_ts(tmem + gi * 32, tmem + kA0 + (gi * kSxNA + ab) * 32 + 8 * j,
-                                  sx_desc(bbase + j * 2 * kSxLbo, kSxLbo, 128), idesc, (c > 0 || j > 0) ? 1u : 0u);
+#pragma unroll 4
+                    for (uint32_t jj = 0; jj < nj; jj++) {
+                        const uint32_t j = j0 + jj;
+                        sx_mma_ts(dcol, tmem + kA0 + (gi * kSxNA + ab) * 32 + 8 * j,
+                                  sx_desc(bbase + j * 2 * kSxLbo, kSxLbo, 128), idesc, (c > 0 || jj > 0) ? 1u : 0u);
+                    }
                 }
-                sx_commit(&ab_free[ab]);             // arrives once these MMAs have read A and B
+                sx_commit(&ab_free[ab]);             // arrives once this lane's MMAs have read A and B
             }
             sx_commit(done);
-            SX_STAMP(21);
-            SX_FLUSH(24);
+            if (q == 0) { SX_STAMP(21); SX_FLUSH(24); }
         }
     } else {
         // ---- expanders: warp w puts k-half w/4 of columns 32 (w%4) + lane of every group into TMEM;
@@ -402,7 +425,7 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
                 SX_ACC(5, tt);
             }
         }
-        if (tid == 0) { SX_STAMP(4); SX_FLUSH(8); }
+        if (tid == 0) { SX_STAMP(4); SX_FLUSH(8); SX_CTA(2); }
         if (tid == 224) SX_FLUSH(16);
         // the zero-point term of each activation row (sixteen lanes hold parts of it); the constant
         // rows' part was summed in units that lack the group's power of two
@@ -450,6 +473,12 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
                     if ((uint32_t)gi < gcount) {
                         uint32_t r[16];
                         sx_tmem_ld16(tmem + tlane + gi * 32, r);
+                        if (G == 1) {                // the second MMA lane's sum, 16 columns on
+                            uint32_t r2[16];
+                            sx_tmem_ld16(tmem + tlane + 16, r2);
+#pragma unroll
+                            for (int i = 0; i < 16; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+                        }
                         if (tid == 0 && gi == 0) SX_STAMP(10);
 #pragma unroll
                         for (int i = 0; i < 16; i++)
@@ -479,8 +508,8 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
                         for (int gi = 0; gi < G; gi++) tile[(i * G + gi) * 128 + tcol] = vals[gi][i];
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     asm volatile("bar.sync 2, 128;" ::: "memory");
-                    if ((uint32_t)tid < M) {
-                        const uint32_t i = (uint32_t)tid, owner = i % splits, slot = (i / splits) * splits + rank;
+                    if (lane < NB / 4 && (uint32_t)(lane * 4 + warp) < M) {     // four rows per warp: issuing is slow
+                        const uint32_t i = (uint32_t)(lane * 4 + warp), owner = i % splits, slot = (i / splits) * splits + rank;
                         uint32_t raddr, rbar;
                         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
                                      : "=r"(raddr) : "r"(sx_smem(&recv[slot * G * 128])), "r"(owner));
@@ -537,7 +566,7 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
         asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     }
-    if (tid == 0) SX_STAMP(6);
+    if (tid == 0) { SX_STAMP(6); SX_CTA(3); }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 8)
