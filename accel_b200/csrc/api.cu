@@ -107,12 +107,15 @@ static const KernelEntry kKernels[] = {
     {"QuantMatMulInt4PackedA", 4, 16, launch_quant_matmul_int4_packed_a},
     {"QuantMatMulInt4PackedSplit3A", 6, 32, launch_quant_matmul_int4_packed_split3_a},
     {"QuantMatMulInt4PackedSwiGLUA", 4, 16, launch_quant_matmul_int4_packed_swiglu_a},
+    {"QuantMatMulInt4PackedSwiGLUAMax", 5, 16, launch_quant_matmul_int4_packed_swiglu_a_max},
     {"AttentionDecode", 5, 16, launch_attention_decode},
     {"AttentionDecodeF16", 5, 16, launch_attention_decode_f16},
     {"AttentionDecodePaged", 6, 32, launch_attention_decode_paged},
     {"AttentionDecodePagedF16", 6, 32, launch_attention_decode_paged_f16},
     {"AttentionDecodeBatched", 6, 32, launch_attention_decode_batched},
     {"AttentionDecodeBatchedF16", 6, 32, launch_attention_decode_batched_f16},
+    {"AttentionDecodeBatchedMax", 7, 32, launch_attention_decode_batched_max},
+    {"AttentionDecodeBatchedF16Max", 7, 32, launch_attention_decode_batched_f16_max},
     {"AttentionRagged", 7, 32, launch_attention_ragged},
     {"AttentionRaggedF16", 7, 32, launch_attention_ragged_f16},
     {"AttentionPrefill", 5, 32, launch_attention_prefill},
@@ -300,7 +303,7 @@ static size_t elem_bytes_of(const char *k, int i)
     if (is("QuantMatVecF32") || is("QuantMatMulTiledF32")) return i == 1 ? 1 : (i == 2 ? 2 : 4);
     if (is("AttentionPrefillF16") || is("AttentionPrefillPagedF16")) return (i == 1 || i == 2) ? 2 : 4;
     if (is("AttentionDecodeF16") || is("AttentionDecodePagedF16") || is("AttentionDecodeBatchedF16") ||
-        is("AttentionRaggedF16"))
+        is("AttentionDecodeBatchedF16Max") || is("AttentionRaggedF16"))
         return (i == 1 || i == 2) ? 2 : 4;
     if (is("ScatterRowsF16")) return (i == 0 || i == 2) ? 2 : 4;
     if (is("GatherRowsF16")) return i == 0 ? 2 : 4;

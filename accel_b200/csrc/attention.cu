@@ -39,6 +39,8 @@ struct AttnParams {
     const void *k, *v;
     const uint32_t *pages, *lengths, *offsets;
     float *out;
+    float *out_max;     // NULL, or [rows][qH][4]: the largest |out| of the elements each warp of the kernel
+                        // that wrote the head wrote (NaN counts as the largest; entries nobody wrote for are 0)
     float *part_o;      // [rows][qH][parts][D]
     float2 *part_ml;    // [rows][qH][parts]
     uint32_t rows;      // sequences (batched), tokens (ragged), 1 otherwise
@@ -49,6 +51,17 @@ struct AttnParams {
     int mode;
     uint32_t base;      // prefill: query row s sees positions <= base + s
 };
+
+// One warp wrote a whole head (r4: this lane's four elements, on: the lane holds any): entry 0 of
+// the head's four maxima is the largest magnitude, the others 0.  Magnitudes compare by their bit
+// patterns, so that a NaN is the largest.  All 32 lanes call.
+__device__ __forceinline__ void head_max_store(float *slot, const float4 &r4, bool on, int lane)
+{
+    uint32_t b = max(max(__float_as_uint(fabsf(r4.x)), __float_as_uint(fabsf(r4.y))),
+                     max(__float_as_uint(fabsf(r4.z)), __float_as_uint(fabsf(r4.w))));
+    b = __reduce_max_sync(0xffffffffu, on ? b : 0u);
+    if (lane < 4) slot[lane] = lane == 0 ? __uint_as_float(b) : 0.f;
+}
 
 // What one query row may see.
 struct RowView { const uint32_t *pages; uint32_t len; bool zero; };
@@ -123,6 +136,7 @@ attn_partition_kernel(const AttnParams p)
         if (part == 0) {
             for (uint32_t i = threadIdx.x; i < G * D; i += kAttnThreads)
                 p.out[((size_t)row * p.q_heads + hq0) * D + i] = 0.f;
+            if (p.out_max && threadIdx.x < G * 4) p.out_max[((size_t)row * p.q_heads + hq0) * 4 + threadIdx.x] = 0.f;
         }
         return;
     }
@@ -228,10 +242,9 @@ attn_partition_kernel(const AttnParams p)
             }
             const size_t qrow = (size_t)row * p.q_heads + hq0 + g;
             if (p.parts == 1) {
-                if (lane_on) {
-                    float4 r4 = make_float4(acc.x / lt, acc.y / lt, acc.z / lt, acc.w / lt);
-                    *reinterpret_cast<float4 *>(p.out + qrow * D + lane * 4) = r4;
-                }
+                const float4 r4 = make_float4(acc.x / lt, acc.y / lt, acc.z / lt, acc.w / lt);
+                if (lane_on) *reinterpret_cast<float4 *>(p.out + qrow * D + lane * 4) = r4;
+                if (p.out_max) head_max_store(p.out_max + qrow * 4, r4, lane_on, lane);
             } else {
                 if (lane_on)
                     *reinterpret_cast<float4 *>(p.part_o + (qrow * p.parts + part) * D + lane * 4) = acc;
@@ -296,6 +309,7 @@ attn_partition_gqa_kernel(const AttnParams p)
         if (part == 0) {
             for (uint32_t i = threadIdx.x; i < G * D; i += kAttnThreads)
                 p.out[((size_t)row * p.q_heads + hq0) * D + i] = 0.f;
+            if (p.out_max && threadIdx.x < G * 4) p.out_max[((size_t)row * p.q_heads + hq0) * 4 + threadIdx.x] = 0.f;
         }
         return;
     }
@@ -429,10 +443,9 @@ attn_partition_gqa_kernel(const AttnParams p)
             }
             const size_t qrow = (size_t)row * p.q_heads + hq0 + g;
             if (p.parts == 1) {
-                if (out_on) {
-                    float4 r4 = make_float4(acc.x / lt, acc.y / lt, acc.z / lt, acc.w / lt);
-                    *reinterpret_cast<float4 *>(p.out + qrow * D + lane * 4) = r4;
-                }
+                const float4 r4 = make_float4(acc.x / lt, acc.y / lt, acc.z / lt, acc.w / lt);
+                if (out_on) *reinterpret_cast<float4 *>(p.out + qrow * D + lane * 4) = r4;
+                if (p.out_max) head_max_store(p.out_max + qrow * 4, r4, out_on, lane);
             } else {
                 if (out_on)
                     *reinterpret_cast<float4 *>(p.part_o + (qrow * p.parts + part) * D + lane * 4) = acc;
@@ -465,8 +478,8 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const AttnParams p)
     if ((d & 31) == 0) s_mx[d >> 5] = mx;
     __syncthreads();
     mx = fmaxf(fmaxf(s_mx[0], s_mx[1]), fmaxf(s_mx[2], s_mx[3]));
-    if (d >= p.head_dim) return;
-    const float *po = p.part_o + qrow * p.parts * p.head_dim + d;
+    const bool on = d < p.head_dim;              // the other threads follow along on element 0 and store nothing
+    const float *po = p.part_o + qrow * p.parts * p.head_dim + (on ? d : 0u);
     float lt = 0.f, acc = 0.f;
     uint32_t s = 0;
     for (; s + 8 <= nparts; s += 8) {
@@ -487,7 +500,12 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const AttnParams p)
         lt = fmaf(m1.y, f, lt);
         acc = fmaf(po[(size_t)s * p.head_dim], f, acc);
     }
-    p.out[qrow * p.head_dim + d] = acc / lt;
+    const float val = acc / lt;
+    if (on) p.out[qrow * p.head_dim + d] = val;
+    if (p.out_max) {                             // one entry per warp: its 32 elements of the head
+        const uint32_t b = __reduce_max_sync(0xffffffffu, on ? __float_as_uint(fabsf(val)) : 0u);
+        if ((d & 31) == 0) p.out_max[qrow * 4 + (d >> 5)] = __uint_as_float(b);
+    }
 }
 
 template <typename T>
@@ -608,8 +626,8 @@ static int paged(Launch &l, bool f16, const char *name)
     return f16 ? run_attention<__half>(l, p, name) : run_attention<float>(l, p, name);
 }
 
-static int batched(Launch &l, bool f16, bool ragged, const char *name)
-{   // q, k, v, pages, lengths, [offsets,] out; BatchedDims / RaggedDims
+static int batched(Launch &l, bool f16, bool ragged, const char *name, bool with_max = false)
+{   // q, k, v, pages, lengths, [offsets,] out [, outmax]; BatchedDims / RaggedDims
     AttnParams p{};
     p.mode = ragged ? kRagged : kBatched;
     p.batch = u32_at(l.u, 0); p.q_heads = u32_at(l.u, 4); p.kv_heads = u32_at(l.u, 8);
@@ -620,15 +638,17 @@ static int batched(Launch &l, bool f16, bool ragged, const char *name)
     p.rows = ragged ? (per ? (uint32_t)(l.len[0] / per) : 0) : p.batch;   // tokens = len(q)/(qH*D)
     p.capacity = p.max_pages * p.block;
     if (l.len[3] < (uint64_t)p.batch * p.max_pages || l.len[4] < p.batch ||
-        (ragged && l.len[5] < p.batch + 1) || l.len[out_i] < (uint64_t)p.rows * per)
+        (ragged && l.len[5] < p.batch + 1) || l.len[out_i] < (uint64_t)p.rows * per ||
+        (with_max && l.len[out_i + 1] < (uint64_t)p.rows * p.q_heads * 4))
         return fail(AB_ERR_INVALID, "%s: Batch=%u MaxPages=%u rows=%u and the lengths block says "
-                    "pages[%u] lengths[%u] out[%u]", name, p.batch, p.max_pages, p.rows, l.len[3],
-                    l.len[4], l.len[out_i]);
+                    "pages[%u] lengths[%u] out[%u]%s", name, p.batch, p.max_pages, p.rows, l.len[3],
+                    l.len[4], l.len[out_i], with_max ? " (outmax holds rows * QHeads * 4)" : "");
     if (!l.query_ws) {
         p.q = ptr<const float>(l, 0); p.k = l.b[1]; p.v = l.b[2];
         p.pages = ptr<const uint32_t>(l, 3); p.lengths = ptr<const uint32_t>(l, 4);
         p.offsets = ragged ? ptr<const uint32_t>(l, 5) : nullptr;
         p.out = ptr<float>(l, out_i);
+        p.out_max = with_max ? ptr<float>(l, out_i + 1) : nullptr;
     }
     return f16 ? run_attention<__half>(l, p, name) : run_attention<float>(l, p, name);
 }
@@ -678,6 +698,10 @@ int launch_attention_decode_paged(Launch &l) { return paged(l, false, "Attention
 int launch_attention_decode_paged_f16(Launch &l) { return paged(l, true, "AttentionDecodePagedF16"); }
 int launch_attention_decode_batched(Launch &l) { return batched(l, false, false, "AttentionDecodeBatched"); }
 int launch_attention_decode_batched_f16(Launch &l) { return batched(l, true, false, "AttentionDecodeBatchedF16"); }
+// the same with a seventh binding, outmax f32[Batch][QHeads][4]: a row's largest |out| is the largest of
+// its QHeads * 4 entries (for the int4 product that reads out next: its "A" form, AmaxParts = QHeads * 4)
+int launch_attention_decode_batched_max(Launch &l) { return batched(l, false, false, "AttentionDecodeBatchedMax", true); }
+int launch_attention_decode_batched_f16_max(Launch &l) { return batched(l, true, false, "AttentionDecodeBatchedF16Max", true); }
 int launch_attention_ragged(Launch &l) { return batched(l, false, true, "AttentionRagged"); }
 int launch_attention_ragged_f16(Launch &l) { return batched(l, true, true, "AttentionRaggedF16"); }
 

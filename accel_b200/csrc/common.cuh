@@ -122,7 +122,8 @@ int run_int4_prepack(cudaStream_t stream, const uint32_t *codes, const uint16_t 
                      unsigned char *packed, uint32_t N, uint32_t K);
 size_t int4_stream_workspace(uint32_t M);
 int run_int4_stream(cudaStream_t stream, const float *a, const float *amax, const unsigned char *packed, float *out,
-                    uint32_t M, uint32_t N, uint32_t K, uint32_t ldo, void *scratch, bool dependent);
+                    uint32_t M, uint32_t N, uint32_t K, uint32_t ldo, void *scratch, bool dependent,
+                    uint32_t amax_parts = 1);       // amax: [M][amax_parts], a row's maximum is the largest entry
 int int4_stream_error_flag();
 // the batch int4 kernel over the same prepacked weights: 128-row tiles on tcgen05 (int4_gemm.cu);
 // mode 0 plain, 1 three column ranges, 2 SwiGLU over (gate, up) pairs of groups
@@ -139,6 +140,7 @@ int launch_quant_matmul_int4_packed_swiglu(Launch &);
 int launch_quant_matmul_int4_packed_a(Launch &);
 int launch_quant_matmul_int4_packed_split3_a(Launch &);
 int launch_quant_matmul_int4_packed_swiglu_a(Launch &);
+int launch_quant_matmul_int4_packed_swiglu_a_max(Launch &);
 int launch_add_rmsnorm_amax(Launch &);
 
 // launchers, one per reference kernel name (defined beside their kernels)
@@ -152,6 +154,8 @@ int launch_attention_decode_paged(Launch &);
 int launch_attention_decode_paged_f16(Launch &);
 int launch_attention_decode_batched(Launch &);
 int launch_attention_decode_batched_f16(Launch &);
+int launch_attention_decode_batched_max(Launch &);
+int launch_attention_decode_batched_f16_max(Launch &);
 int launch_attention_ragged(Launch &);
 int launch_attention_ragged_f16(Launch &);
 int launch_attention_prefill(Launch &);

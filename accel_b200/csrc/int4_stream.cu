@@ -304,7 +304,20 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
             asm volatile("bar.sync 1, 256;" ::: "memory");
         }
         const bool brow = bm < M;
-        const uint32_t mb = brow ? (amax ? __float_as_uint(fabsf(__ldg(amax + bm))) : amax_s[bm]) : 0u;
+        uint32_t mb = 0u;
+        if (amax == nullptr) {
+            mb = brow ? amax_s[bm] : 0u;
+        } else if (ep.amax_parts <= 1) {
+            mb = brow ? __float_as_uint(fabsf(__ldg(amax + bm))) : 0u;
+        } else {
+            // the row's maximum is the largest of its entries: the sixteen threads of a row (lanes
+            // 16 apart never mix) share the loads
+            if (brow)
+                for (uint32_t q = bq; q < ep.amax_parts; q += 16)
+                    mb = max(mb, __float_as_uint(fabsf(__ldg(amax + (size_t)bm * ep.amax_parts + q))));
+#pragma unroll
+            for (int sh = 8; sh > 0; sh >>= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, sh));
+        }
         const int ea = sx_row_exponent(mb);
         const float pa = __uint_as_float((uint32_t)(127 + 12 - ea) << 23);            // 2^(12 - E_a)
         const float *ax = a + (size_t)(brow ? bm : 0) * K + kbeg + 4 * bq;            // next activations to load
@@ -459,8 +472,12 @@ int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
                 // one finished row of the tile: both groups' sums of column tcol
                 auto emit = [&](uint32_t m, const float (&v)[G]) {
                     if (G == 2 && ep.swiglu) {
-                        ep.out0[(size_t)m * ep.ld0 + (size_t)blockIdx.x * 128 + tcol] =
-                            __fdiv_rn(v[0], 1.f + expf(-v[0])) * v[G - 1];
+                        const float o = __fdiv_rn(v[0], 1.f + expf(-v[0])) * v[G - 1];
+                        ep.out0[(size_t)m * ep.ld0 + (size_t)blockIdx.x * 128 + tcol] = o;
+                        if (ep.max_out) {            // this warp's 32 columns of row m (NaN counts as the largest)
+                            const uint32_t mx = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(o)));
+                            if (lane == 0) ep.max_out[(size_t)m * ep.max_ld + blockIdx.x * 4 + warp] = __uint_as_float(mx);
+                        }
                     } else {
 #pragma unroll
                         for (int gi = 0; gi < G; gi++)
@@ -877,7 +894,8 @@ enum { kSxPlain = 0, kSxSplit3 = 1, kSxSwiGLU = 2 };
 
 static int run_int4_stream_mode(cudaStream_t stream, const float *a, const float *amax, const unsigned char *packed,
                                 int mode, float *out0, float *out1, float *out2, uint32_t n1, uint32_t n2, uint32_t M,
-                                uint32_t N, uint32_t K, uint32_t ld0, void *scratch, bool dependent)
+                                uint32_t N, uint32_t K, uint32_t ld0, void *scratch, bool dependent,
+                                uint32_t amax_parts = 1, float *max_out = nullptr)
 {
     SxPlan p = sx_plan(N, K);
     if (mode == kSxSwiGLU && p.G != 2) {             // (gate, up) pairs are tiles of two groups
@@ -894,8 +912,13 @@ static int run_int4_stream_mode(cudaStream_t stream, const float *a, const float
     }
     for (uint32_t m0 = 0; m0 < M; m0 += kSxNB) {
         const uint32_t rows = M - m0 < (uint32_t)kSxNB ? M - m0 : (uint32_t)kSxNB;
-        const float *ap = a + (size_t)m0 * K, *mp = amax ? amax + m0 : nullptr;
+        const float *ap = a + (size_t)m0 * K, *mp = amax ? amax + (size_t)m0 * amax_parts : nullptr;
         SxEpilogue ep{};
+        ep.amax_parts = amax_parts;
+        if (max_out) {
+            ep.max_ld = N / 64;                      // four warps per tile of 256 columns
+            ep.max_out = max_out + (size_t)m0 * ep.max_ld;
+        }
         ep.g1 = ep.g2 = 0xffffffffu;
         ep.ld0 = ld0;
         ep.out0 = out0 + (size_t)m0 * ld0;
@@ -919,10 +942,10 @@ static int run_int4_stream_mode(cudaStream_t stream, const float *a, const float
 }
 
 int run_int4_stream(cudaStream_t stream, const float *a, const float *amax, const unsigned char *packed, float *out,
-                    uint32_t M, uint32_t N, uint32_t K, uint32_t ldo, void *scratch, bool dependent)
+                    uint32_t M, uint32_t N, uint32_t K, uint32_t ldo, void *scratch, bool dependent, uint32_t amax_parts)
 {
     return run_int4_stream_mode(stream, a, amax, packed, kSxPlain, out, nullptr, nullptr, 0, 0, M, N, K, ldo, scratch,
-                                dependent);
+                                dependent, amax_parts ? amax_parts : 1u);
 }
 
 int int4_stream_error_flag()
@@ -958,6 +981,10 @@ static size_t packed_workspace(uint32_t M, uint32_t K)
 // binding is present; the batch kernel (from kPackedTileFromRows rows) finds its own factors and ignores it.
 static int launch_packed(Launch &l, const char *name, uint32_t M, uint32_t N, uint32_t K, int ax = 0)
 {
+    // the "A" form's fourth uniform word: entries per row of the amax binding (0 or 1: one per row);
+    // with P entries a row's maximum is the largest of them (what the attention kernels and the
+    // SwiGLU product leave: one per head and warp, one per tile and warp)
+    const uint32_t parts = ax && l.ubytes >= 16 && u32_at(l.u, 12) ? u32_at(l.u, 12) : 1u;
     if (!int4_stream_ok(M, N, K))
         return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u; the prepacked form needs N a multiple of 128 and K a "
                     "multiple of 4", name, M, N, K);
@@ -965,17 +992,17 @@ static int launch_packed(Launch &l, const char *name, uint32_t M, uint32_t N, ui
     if (l.query_ws) { l.ws_need = ws; return AB_OK; }
     const size_t need = int4_stream_packed_bytes(N, K);
     if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1 + ax] * 4 < need || l.len[2 + ax] < (uint64_t)M * N ||
-        (ax && l.len[1] < M))
-        return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u needs a[%llu] packed[%zu bytes] out[%llu]; the lengths "
-                    "block says %u, %u words, %u", name, M, N, K, (unsigned long long)M * K, need,
-                    (unsigned long long)M * N, l.len[0], l.len[1 + ax], l.len[2 + ax]);
+        (ax && l.len[1] < (uint64_t)M * parts))
+        return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u needs a[%llu] packed[%zu bytes] out[%llu] (and amax[%llu]); the "
+                    "lengths block says %u, %u words, %u", name, M, N, K, (unsigned long long)M * K, need,
+                    (unsigned long long)M * N, (unsigned long long)M * parts, l.len[0], l.len[1 + ax], l.len[2 + ax]);
     if (ws > l.ws_bytes || (ws && !l.ws))
         return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, ws, l.ws_bytes);
     if (packed_tiles(M))
         return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1 + ax), kSxPlain,
                                   ptr<float>(l, 2 + ax), nullptr, nullptr, 0, 0, M, N, K, N, l.ws);
     return run_int4_stream(l.stream, ptr<const float>(l, 0), ax ? ptr<const float>(l, 1) : nullptr,
-                           ptr<const unsigned char>(l, 1 + ax), ptr<float>(l, 2 + ax), M, N, K, N, l.ws, sx_pdl());
+                           ptr<const unsigned char>(l, 1 + ax), ptr<float>(l, 2 + ax), M, N, K, N, l.ws, sx_pdl(), parts);
 }
 
 // a, packed, out0, out1, out2; uniform {M, N, K, N1, N2, 0, 0, 0}: columns [0, N1) of the product go to
@@ -1011,11 +1038,15 @@ static int launch_split3(Launch &l, const char *name, int ax)
 
 // a, packed, out; GEMMDims{M, N, K}: the 128-column groups of the packed matrix alternate gate, up;
 // out [M][N / 2] = SwiGLU(gate, up)
-static int launch_swiglu(Launch &l, const char *name, int ax);
+// "...SwiGLUAMax" has a fifth binding, outmax f32[M][N / 64]: entry 4 t + w of a row is the largest
+// |out| among the 32 columns warp w of tile t wrote (a tile is 128 output columns), for the product
+// that reads out next (its "A" form with AmaxParts = N / 64).  Decode kernel only (fewer than 49 rows).
+static int launch_swiglu(Launch &l, const char *name, int ax, int mx = 0);
 int launch_quant_matmul_int4_packed_swiglu(Launch &l) { return launch_swiglu(l, "QuantMatMulInt4PackedSwiGLU", 0); }
 int launch_quant_matmul_int4_packed_swiglu_a(Launch &l) { return launch_swiglu(l, "QuantMatMulInt4PackedSwiGLUA", 1); }
+int launch_quant_matmul_int4_packed_swiglu_a_max(Launch &l) { return launch_swiglu(l, "QuantMatMulInt4PackedSwiGLUAMax", 1, 1); }
 
-static int launch_swiglu(Launch &l, const char *name, int ax)
+static int launch_swiglu(Launch &l, const char *name, int ax, int mx)
 {
     const uint32_t M = u32_at(l.u, 0), N = u32_at(l.u, 4), K = u32_at(l.u, 8);
     if (!int4_stream_ok(M, N, K) || N % 256)
@@ -1024,17 +1055,20 @@ static int launch_swiglu(Launch &l, const char *name, int ax)
     const size_t ws = (ax && !packed_tiles(M)) ? 0 : packed_workspace(M, K);
     if (l.query_ws) { l.ws_need = ws; return AB_OK; }
     if (l.len[0] < (uint64_t)M * K || (uint64_t)l.len[1 + ax] * 4 < int4_stream_packed_bytes(N, K) ||
-        l.len[2 + ax] < (uint64_t)M * (N / 2) || (ax && l.len[1] < M))
-        return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u; a[%u] packed[%u words] out[%u]", name, M, N, K, l.len[0],
-                    l.len[1 + ax], l.len[2 + ax]);
+        l.len[2 + ax] < (uint64_t)M * (N / 2) || (ax && l.len[1] < M) || (mx && l.len[3 + ax] < (uint64_t)M * (N / 64)))
+        return fail(AB_ERR_INVALID, "%s: M=%u N=%u K=%u; a[%u] packed[%u words] out[%u]%s", name, M, N, K, l.len[0],
+                    l.len[1 + ax], l.len[2 + ax], mx ? " outmax[M * N / 64]" : "");
     if (ws > l.ws_bytes || (ws && !l.ws))
         return fail(AB_ERR_INVALID, "%s: needs %zu bytes of workspace, given %zu", name, ws, l.ws_bytes);
+    if (mx && packed_tiles(M))
+        return fail(AB_ERR_INVALID, "%s: M=%u; the form that leaves row maxima runs on the decode kernel, fewer than "
+                    "%u rows (use QuantMatMulInt4PackedSwiGLUA)", name, M, kPackedTileFromRows);
     if (packed_tiles(M))
         return run_int4_gemm_mode(l.stream, ptr<const float>(l, 0), ptr<const unsigned char>(l, 1 + ax), kSxSwiGLU,
                                   ptr<float>(l, 2 + ax), nullptr, nullptr, 0, 0, M, N, K, N / 2, l.ws);
     return run_int4_stream_mode(l.stream, ptr<const float>(l, 0), ax ? ptr<const float>(l, 1) : nullptr,
                                 ptr<const unsigned char>(l, 1 + ax), kSxSwiGLU, ptr<float>(l, 2 + ax), nullptr, nullptr, 0, 0,
-                                M, N, K, N / 2, l.ws, sx_pdl());
+                                M, N, K, N / 2, l.ws, sx_pdl(), 1, mx ? ptr<float>(l, 3 + ax) : nullptr);
 }
 
 int launch_quant_matvec_int4_packed(Launch &l)

@@ -117,6 +117,12 @@ struct SxEpilogue {
     uint32_t g1, g2;              // 0xffffffff: no such destination
     uint32_t ld0, ld1, ld2;
     uint32_t swiglu;
+    // row maxima in parts: the producer of a matrix leaves, per row, the largest magnitude of each
+    // part it wrote (a head, a warp's columns), and the product that reads the matrix takes a row's
+    // maximum as the largest of its entries
+    uint32_t amax_parts;          // entries per row of the amax binding (1: one maximum per row)
+    float *max_out;               // SwiGLU form: [M][max_ld], entry 4 * tile + warp = the largest |out| of the
+    uint32_t max_ld;              // 32 columns that warp wrote; NULL: not wanted
 };
 
 __device__ __forceinline__ void sx_store(const SxEpilogue &e, uint32_t m, uint32_t g, uint32_t t, float v)

@@ -332,6 +332,10 @@ class DecodeEngine:
         self._my_pairs = z(B, sh.tp, 2)          # this rank's slot filled, the others zero
         self.next_tokens = z(B, dt=I32)
         self.h_amax = z(B)                       # every row's largest |h|, left by the norm kernels for the products
+        # the same for the inputs of wo and down, in parts: one entry per head and warp of the attention
+        # kernel, one per 32 columns of the SwiGLU product; the product that follows takes the largest
+        self.attn_max = z(B, self.hq * 4)
+        self.act_max = z(B, max(len(sh.ffn) // 32, 1))
         self._proj = [self.proj, self.proj]      # where wo and down write their partial results
         if sh.tp > 1 and collective == "peer":
             # the row-parallel products write straight into this rank's peer buffer: two regions
@@ -544,6 +548,8 @@ class DecodeEngine:
         # with the prepacked products the norm kernels also leave every row's largest |h|, and the
         # products that read h take it as a binding instead of running a kernel of their own for it
         h_has_amax = False
+        # the decode kernel (fewer than 49 rows) is the one that takes maxima in parts and leaves them
+        maxima = self.use_packed and self.fuse and B <= 48
 
         def add_norm(gain, which):
             """x <- x + (sum over the ranks of the partial product `which`); h <- RMSNorm(x) * gain"""
@@ -625,15 +631,27 @@ class DecodeEngine:
                 L("RopeScatterQKVF16" if f16 else "RopeScatterQKV",
                   [self.pos_q, self.pos_k, self.slots, self.q, self.k, self.v, self.k_cache[li], self.v_cache[li]],
                   _u("<IIIIIIfI", B, self.hq, self.hk, D, D, self.capacity, cfg.rope_base, 0))
-            L("AttentionDecodeBatchedF16" if f16 else "AttentionDecodeBatched",
-              [self.q, self.k_cache[li], self.v_cache[li], self.pages, self.lengths, self.attn],
-              _u("<IIIIIIfI", B, self.hq, self.hk, D, cfg.block, self.max_pages, scale, 0))
-            self._linear(self.attn, lay.wo_p if self.use_packed else lay.wo, self._proj[0])
+            attn_u = _u("<IIIIIIfI", B, self.hq, self.hk, D, cfg.block, self.max_pages, scale, 0)
+            attn_b = [self.q, self.k_cache[li], self.v_cache[li], self.pages, self.lengths, self.attn]
+            if maxima:
+                # the kernel that writes a product's input also leaves its rows' largest magnitudes
+                L("AttentionDecodeBatchedF16Max" if f16 else "AttentionDecodeBatchedMax", attn_b + [self.attn_max], attn_u)
+                w = lay.wo_p
+                L("QuantMatMulInt4PackedA", [self.attn, self.attn_max, w.packed, self._proj[0]],
+                  _u("<IIII", B, w.N, w.K, self.attn_max.shape[1]))
+            else:
+                L("AttentionDecodeBatchedF16" if f16 else "AttentionDecodeBatched", attn_b, attn_u)
+                self._linear(self.attn, lay.wo_p if self.use_packed else lay.wo, self._proj[0])
             add_norm(lay.g2, 0)
+            act_has_max = False
             if self.use_packed and self.fuse:
                 # gate and up as one product whose epilogue applies SwiGLU
                 w = lay.wgu
-                if h_has_amax:
+                if h_has_amax and maxima:
+                    L("QuantMatMulInt4PackedSwiGLUAMax", [self.h, self.h_amax, w.packed, self.act, self.act_max],
+                      _u("<IIII", B, w.N, w.K, 0))
+                    act_has_max = True
+                elif h_has_amax:
                     L("QuantMatMulInt4PackedSwiGLUA", [self.h, self.h_amax, w.packed, self.act], _u("<IIII", B, w.N, w.K, 0))
                 else:
                     L("QuantMatMulInt4PackedSwiGLU", [self.h, w.packed, self.act], _u("<IIII", B, w.N, w.K, 0))
@@ -641,7 +659,12 @@ class DecodeEngine:
                 self._parallel([lambda: self._linear(self.h, lay.wg, self.gate),
                                 lambda: self._linear(self.h, lay.wu, self.up)])
                 L("SwiGLU", [self.gate, self.up, self.act])
-            self._linear(self.act, lay.wd_p if self.use_packed else lay.wd, self._proj[1])
+            if act_has_max:
+                w = lay.wd_p
+                L("QuantMatMulInt4PackedA", [self.act, self.act_max, w.packed, self._proj[1]],
+                  _u("<IIII", B, w.N, w.K, lay.wgu.N // 64))
+            else:
+                self._linear(self.act, lay.wd_p if self.use_packed else lay.wd, self._proj[1])
         add_norm(self.model.g_final, 1)
         if h_has_amax:
             w = self.model.lm_head_p

@@ -264,6 +264,14 @@ AB_API uint64_t ab_launch_count(void);
  *                    one more binding after a: amax f32[M], every activation row's largest magnitude (what
  *                    AddRMSNormAmax leaves).  The decode kernel scales its f16 operand by a power of two taken from
  *                    it; without the binding a small kernel finds the maxima first.  Bit-identical results.
+ *                    QuantMatMulInt4PackedA reads the fourth word of its GEMMDims as AmaxParts: with P > 1 amax is
+ *                    f32[M*P] and a row's maximum is the largest of its P entries (what the two kernels below leave).
+ *  QuantMatMulInt4PackedSwiGLUAMax   a, amax f32[M], packed, out f32[M*N/2], outmax f32[M*N/64]   GEMMDims.  ...SwiGLUA
+ *                    that also leaves the largest |out| of every 32 output columns (NaN counts as the largest), for
+ *                    the product that reads out next: its A form with AmaxParts = N/64.  Up to 48 rows.
+ *  AttentionDecodeBatchedMax, AttentionDecodeBatchedF16Max   AttentionDecodeBatched(F16) with a seventh binding,
+ *                    outmax f32[B*qH*4]: four maxima per head whose largest is the head's largest |out|; the
+ *                    product that reads out next takes them as AmaxParts = qH*4.  out is bit-identical.
  *  GroupedMatMulInt4Packed   x f32[T*K], packed (Experts prepacked matrices end to end), offsets u32[E+1], out f32[T*N]
  *                    GroupedTiledDims.  GroupedMatMulInt4 over prepacked experts, on the tcgen05 tile kernel.
  *  ArgmaxShard       logits f32[rows*Width], pairs f32[rows*Parts*2]        {Width,Rows,Parts,Rank,First}@0..16 (32 B)

@@ -246,3 +246,36 @@ def test_refusals():
         T.attention(torch.zeros(2, 3, qH, D, device=DEV), k, k, T.AttentionOptions(
             lengths=torch.ones(2, dtype=torch.int32, device=DEV),
             pages=torch.zeros(2, 4, dtype=torch.int32, device=DEV), block=4))
+
+
+@pytest.mark.parametrize("f16", [False, True])
+@pytest.mark.parametrize("qH,kvH,D,block,lengths", [
+    (32, 32, 128, 16, [1, 300, 2048, 700]),        # several partitions: the combine kernel writes out
+    (32, 8, 128, 16, [5, 900, 64, 1500]),          # grouped heads
+    (8, 4, 64, 8, [3, 17, 40, 9]),                 # one partition: the partition kernels write out
+    (6, 2, 40, 4, [1, 30, 0, 12]),                 # a head dimension that leaves lanes idle; a zero length (NaN)
+])
+def test_batched_with_the_rows_maxima(qH, kvH, D, block, lengths, f16):
+    """AttentionDecodeBatched(F16)Max: out is bit-identical to the plain kernel's, and outmax
+    [Batch][QHeads][4] holds, per head, maxima whose largest is the largest |out| of the head (NaN
+    counts as the largest), for the int4 product that reads out next."""
+    from accel_b200 import runtime as rt
+    import struct
+    lengths = np.array(lengths, np.uint32)
+    batch = len(lengths)
+    k, v, pages, mp = paged_fixture(7, batch, kvH, D, block, np.maximum(lengths, 1), f16=f16)
+    q = normal(8, (batch, 1, qH, D))
+    u = struct.pack("<IIIIIIfI", batch, qH, kvH, D, block, mp, attn_scale(D), 0)
+    b = [dev(q), dev(k), dev(v), dev(pages.reshape(-1)), dev(lengths)]
+    o0 = torch.full((batch, qH, D), float("nan"), device=DEV)
+    o1 = torch.full((batch, qH, D), float("nan"), device=DEV)
+    mx = torch.full((batch, qH, 4), float("nan"), device=DEV)
+    name = "AttentionDecodeBatchedF16" if f16 else "AttentionDecodeBatched"
+    rt.launch(name, b + [o0], u)
+    rt.launch(name + "Max", b + [o1, mx], u)
+    torch.cuda.synchronize()
+    assert torch.equal(o0.view(torch.int32), o1.view(torch.int32))
+    # compare magnitudes by their bit patterns: a NaN is the largest
+    want = o1.abs().view(torch.int32).amax(dim=2)
+    got = mx.abs().view(torch.int32).amax(dim=2)
+    assert torch.equal(got, want)

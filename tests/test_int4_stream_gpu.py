@@ -2,6 +2,8 @@
 against the oracle, through the C ABI: ab_int4_prepack, then QuantMatVecInt4Packed /
 QuantMatMulInt4Packed by name.  Tolerance 1e-3 relative (max-norm) as for every int4 product, plus
 the reference's per-element bound (internal/kernels/int4_test.go:99-182)."""
+import struct
+
 import numpy as np
 import pytest
 import torch
@@ -216,3 +218,59 @@ def test_the_forms_that_take_the_rows_maxima_equal_the_plain_forms(M):
     torch.cuda.synchronize()
     quant.int4_stream_check()
     assert torch.equal(g0, g1)
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 33])
+def test_row_maxima_in_parts(M):
+    """The producer of a product's input may leave a row's largest magnitudes in parts (the attention
+    kernels: one per head and warp; the SwiGLU product: one per 32 columns) and the product that
+    follows takes the largest of a row's entries: bit-identical to the plain forms, whatever the
+    split.  QuantMatMulInt4PackedSwiGLUAMax is the producer: its out equals ...SwiGLUA's and outmax
+    holds the largest |out| of every 32 columns."""
+    K, F = 1024, 512
+    N = 2 * F
+    p, s, z = orc.int4_quantize(normal(52, (K, N), 0.02))
+    packed = packed_of(p, s, z, K, N)
+    a = torch.from_numpy(normal(53, (M, K))).to(DEV)
+    a[0, 7] = 300.0                                         # the maximum sits in one part only
+    plain = torch.empty(M, N, device=DEV)
+    runtime.launch("QuantMatMulInt4Packed", [a, packed, plain], runtime.gemm_dims(M, N, K))
+    for parts in (1, 4, 32, 37):
+        # a split of the columns into `parts` runs of unequal length; empty parts hold 0
+        edges = np.unique(np.concatenate([[0, K], np.random.default_rng(parts).integers(0, K, parts - 1)]))
+        amax = torch.zeros(M, parts, device=DEV)
+        for i in range(len(edges) - 1):
+            amax[:, i] = a[:, edges[i]:edges[i + 1]].abs().amax(dim=1)
+        out = torch.full((M, N), float("nan"), device=DEV)
+        runtime.launch("QuantMatMulInt4PackedA", [a, amax, packed, out], struct.pack("<IIII", M, N, K, parts))
+        torch.cuda.synchronize()
+        assert torch.equal(out, plain), parts
+    one = a.abs().amax(dim=1).contiguous()
+    g0, g1 = torch.empty(M, F, device=DEV), torch.full((M, F), float("nan"), device=DEV)
+    gmax = torch.full((M, N // 64), float("nan"), device=DEV)
+    runtime.launch("QuantMatMulInt4PackedSwiGLUA", [a, one, packed, g0], runtime.gemm_dims(M, N, K))
+    runtime.launch("QuantMatMulInt4PackedSwiGLUAMax", [a, one, packed, g1, gmax], runtime.gemm_dims(M, N, K))
+    torch.cuda.synchronize()
+    quant.int4_stream_check()
+    assert torch.equal(g0, g1)
+    assert torch.equal(gmax, g1.view(M, F // 32, 32).abs().amax(dim=2))
+    # and the product that reads it next
+    K2 = F
+    p2, s2, z2 = orc.int4_quantize(normal(54, (K2, 256), 0.02))
+    packed2 = packed_of(p2, s2, z2, K2, 256)
+    d0, d1 = torch.empty(M, 256, device=DEV), torch.full((M, 256), float("nan"), device=DEV)
+    runtime.launch("QuantMatMulInt4Packed", [g1, packed2, d0], runtime.gemm_dims(M, 256, K2))
+    runtime.launch("QuantMatMulInt4PackedA", [g1, gmax, packed2, d1], struct.pack("<IIII", M, 256, K2, N // 64))
+    torch.cuda.synchronize()
+    assert torch.equal(d0, d1)
+
+
+def test_the_form_that_leaves_maxima_refuses_the_batch_kernel():
+    M, K, N = 64, 256, 512
+    p, s, z = orc.int4_quantize(normal(55, (K, N), 0.02))
+    packed = packed_of(p, s, z, K, N)
+    a = torch.zeros(M, K, device=DEV)
+    with pytest.raises(Exception, match="decode kernel"):
+        runtime.launch("QuantMatMulInt4PackedSwiGLUAMax", [a, torch.zeros(M, device=DEV), packed,
+                                                           torch.zeros(M, N // 2, device=DEV),
+                                                           torch.zeros(M, N // 64, device=DEV)], runtime.gemm_dims(M, N, K))
