@@ -455,6 +455,309 @@ attn_partition_gqa_kernel(const AttnParams p)
     }
 }
 
+// ---- grouped-query heads on the tensor cores (head dimension 128) -----------------------------------
+// The half-warp kernel above is bound by instruction issue: every (position, head) costs its FMAs
+// and shuffles on the CUDA cores.  Here a warp takes 16 positions at a time and both products run as
+// mma.sync m16n8k8 (tf32 operands, f32 accumulators) with the HEADS as the 8-wide dimension, so
+// nothing is padded but heads G..7:
+//   S^T [16 positions x 8 heads] = K tile [16 x 128] . Q^T [128 x 8]            16 MMAs
+//   O^T [128 d x 8 heads]       += V tile^T [128 x 16] . P^T [16 x 8]           16 MMAs
+// A sum does not care in which order its terms come, so the k index of each product is permuted
+// until the fragment a thread needs is what 128-bit loads of whole sectors bring it: of a K row a
+// thread (g = lane / 4, t = lane % 4) holds 8 d's of every 32 (rows g and g + 8 of the tile), of a V
+// row 16 d's of 128 (positions t, t + 4, t + 8, t + 12), and Q's fragments and the output's rows follow
+// the same maps.  K and Q are rounded to tf32 (cvt.rna), P too; V is used as it is (the MMA drops its
+// low 13 bits: a bias of at most 2^-11 of the output).  An f16 cache converts exactly.  The running
+// softmax is the recurrence of the other kernels per 16 positions; P goes from the accumulator
+// layout of S^T to the B layout of the second product by 8 shuffles.
+__device__ __forceinline__ uint32_t tf32_rna(float x)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 ld_nc16(const void *p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t half_lo_f32(uint32_t w) { return __float_as_uint(__half2float(__ushort_as_half((unsigned short)(w & 0xffffu)))); }
+__device__ __forceinline__ uint32_t half_hi_f32(uint32_t w) { return __float_as_uint(__half2float(__ushort_as_half((unsigned short)(w >> 16)))); }
+
+// Which d a thread's m-th element of a K row's 32-d block c is (m = 0..7), and which d its m-th
+// element of a V row is (m = 0..15): the order its 128-bit loads bring them in.
+template <typename T> __device__ __forceinline__ uint32_t tc_kd(int c, int m, int t)
+{
+    return sizeof(T) == 4 ? (uint32_t)(32 * c + 4 * t + (m < 4 ? m : 12 + m)) : (uint32_t)(32 * c + 8 * t + m);
+}
+template <typename T> __device__ __forceinline__ uint32_t tc_vd(int m, int g)
+{
+    return sizeof(T) == 4 ? (uint32_t)(32 * (m >> 2) + 4 * g + (m & 3)) : (uint32_t)(64 * (m >> 3) + 8 * g + (m & 7));
+}
+
+// grid = (parts, kv_heads, rows); head_dim = 128; G = 2, 4 or 8 query heads per KV head
+// (two warps per CTA, so that a warp walks eight tiles of a 256-position partition and the start of a
+// CTA weighs less, measured no better than four)
+static constexpr int kTcWarps = 4;
+static constexpr int kTcThreads = kTcWarps * 32;
+
+template <typename T, int G>
+__global__ void __launch_bounds__(kTcThreads, 256 / kTcThreads)
+attn_partition_gqa_mma_kernel(const AttnParams p)
+{
+    pdl_wait();
+    constexpr uint32_t D = 128;
+    constexpr int W = sizeof(T) == 4 ? 8 : 4;        // 32-bit words a thread holds of a K row's 32-d block
+    constexpr int VW = sizeof(T) == 4 ? 16 : 8;      // ... and of a V row
+    const uint32_t part = blockIdx.x, row = blockIdx.z, kvh = blockIdx.y;
+    const uint32_t hq0 = kvh * G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+
+    const RowView rv = row_view(p, row);
+    const uint32_t begin = part * p.psize;
+    if (rv.zero) {
+        if (part == 0) {
+            for (uint32_t i = threadIdx.x; i < G * D; i += kTcThreads)
+                p.out[((size_t)row * p.q_heads + hq0) * D + i] = 0.f;
+            if (p.out_max && threadIdx.x < G * 4) p.out_max[((size_t)row * p.q_heads + hq0) * 4 + threadIdx.x] = 0.f;
+        }
+        return;
+    }
+    if (begin >= rv.len && !(part == 0)) return;     // partition 0 always reports (len 0 -> NaN)
+    const uint32_t end = min(rv.len, begin + p.psize);
+
+    const T *kc = reinterpret_cast<const T *>(p.k);
+    const T *vc = reinterpret_cast<const T *>(p.v);
+    const size_t row_stride = (size_t)p.kv_heads * D;
+    const size_t head_off = (size_t)kvh * D;
+
+    // Q^T as B fragments: column g is head g (zero past the group), rows in the K fragments' order
+    uint32_t qb[16][2];
+#pragma unroll
+    for (int c = 0; c < 4; c++)
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const float q = g < G ? p.q[((size_t)row * p.q_heads + hq0 + g) * D + tc_kd<T>(c, 2 * i + e, t)] * p.scale_log2 : 0.f;
+                qb[4 * c + i][e] = tf32_rna(q);
+            }
+
+    float m[2] = {kNegBig, kNegBig}, l[2] = {0.f, 0.f};     // heads 2t, 2t + 1; l: this thread's positions only
+    float o[8][4];                                            // O^T: 8 tiles of 16 d's x heads 2t, 2t + 1
+#pragma unroll
+    for (int mt = 0; mt < 8; mt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[mt][e] = 0.f;
+
+    // lane i < 16 finds where position p0 + i of a tile lies; the others get it by shuffle.  The look-up
+    // runs one tile ahead, so that a tile's loads do not wait for its page-table entries.
+    auto lookup = [&](uint32_t p0) -> uint32_t {
+        uint32_t phys = 0;
+        if (lane < 16 && p0 + lane < end) {
+            const uint32_t j = p0 + lane;
+            phys = rv.pages == nullptr ? j : __ldg(rv.pages + j / p.block) * p.block + j % p.block;
+        }
+        return phys;
+    };
+    auto load_tile = [&](uint32_t p0, uint32_t phys, uint32_t (&kraw)[2][4][W], uint32_t (&vraw)[4][VW]) {
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const uint32_t ph = __shfl_sync(0xffffffffu, phys, g + 8 * r);
+            const bool ok = p0 + g + 8 * r < end;
+            const T *src = kc + (size_t)ph * row_stride + head_off;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                if (sizeof(T) == 4) {
+                    uint4 a = make_uint4(0, 0, 0, 0), b = a;
+                    if (ok) { a = ld_nc16(src + 32 * c + 4 * t); b = ld_nc16(src + 32 * c + 16 + 4 * t); }
+                    kraw[r][c][0] = a.x; kraw[r][c][1] = a.y; kraw[r][c][2] = a.z; kraw[r][c][3] = a.w;
+                    kraw[r][c][W - 4] = b.x; kraw[r][c][W - 3] = b.y; kraw[r][c][W - 2] = b.z; kraw[r][c][W - 1] = b.w;
+                } else {
+                    uint4 a = make_uint4(0, 0, 0, 0);
+                    if (ok) a = ld_nc16(src + 32 * c + 8 * t);
+                    kraw[r][c][0] = a.x; kraw[r][c][1] = a.y; kraw[r][c][2] = a.z; kraw[r][c][3] = a.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < 4; n++) {
+            const uint32_t ph = __shfl_sync(0xffffffffu, phys, t + 4 * n);
+            const bool ok = p0 + t + 4 * n < end;
+            const T *src = vc + (size_t)ph * row_stride + head_off;
+#pragma unroll
+            for (int q = 0; q < VW / 4; q++) {
+                uint4 a = make_uint4(0, 0, 0, 0);
+                if (ok) a = ld_nc16(sizeof(T) == 4 ? src + 32 * q + 4 * g : src + 64 * q + 8 * g);
+                vraw[n][4 * q] = a.x; vraw[n][4 * q + 1] = a.y; vraw[n][4 * q + 2] = a.z; vraw[n][4 * q + 3] = a.w;
+            }
+        }
+    };
+    // an f16 tile is 8 KB: the registers hold two, and the next tile's loads are in flight while this
+    // one is multiplied; an f32 tile (16 KB) fills them alone
+    constexpr bool kAhead = sizeof(T) == 2;
+    constexpr uint32_t kStep = 16u * kTcWarps;
+    const uint32_t first = begin + 16u * warp;
+    uint32_t phys_next = lookup(first);
+    uint32_t kraw[2][4][W], vraw[4][VW];
+    uint32_t knext[kAhead ? 2 : 1][4][W], vnext[kAhead ? 4 : 1][VW];
+    if (kAhead && first < end) {
+        load_tile(first, phys_next, kraw, vraw);
+        phys_next = lookup(first + kStep);
+    }
+    for (uint32_t p0 = first; p0 < end; p0 += kStep) {
+        if (kAhead) {
+            if (p0 + kStep < end) load_tile(p0 + kStep, phys_next, reinterpret_cast<uint32_t (&)[2][4][W]>(knext),
+                                            reinterpret_cast<uint32_t (&)[4][VW]>(vnext));
+            phys_next = lookup(p0 + 2 * kStep);
+        } else {
+            const uint32_t phys = phys_next;
+            phys_next = lookup(p0 + kStep);
+            load_tile(p0, phys, kraw, vraw);
+        }
+
+        // S^T: sc[0], sc[1] = position g x heads 2t, 2t + 1; sc[2], sc[3] = position g + 8
+        float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};       // two chains of eight MMAs
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t a0, a1, a2, a3;
+                if (sizeof(T) == 4) {
+                    a0 = tf32_rna(__uint_as_float(kraw[0][c][2 * i]));     a2 = tf32_rna(__uint_as_float(kraw[0][c][2 * i + 1]));
+                    a1 = tf32_rna(__uint_as_float(kraw[1][c][2 * i]));     a3 = tf32_rna(__uint_as_float(kraw[1][c][2 * i + 1]));
+                } else {
+                    a0 = half_lo_f32(kraw[0][c][i]); a2 = half_hi_f32(kraw[0][c][i]);
+                    a1 = half_lo_f32(kraw[1][c][i]); a3 = half_hi_f32(kraw[1][c][i]);
+                }
+                mma_tf32((i & 1) ? sc2 : sc, a0, a1, a2, a3, qb[4 * c + i][0], qb[4 * c + i][1]);
+            }
+#pragma unroll
+        for (int e = 0; e < 4; e++) sc[e] += sc2[e];
+
+        // the running softmax of heads 2t, 2t + 1 over these 16 positions
+        const bool ok0 = p0 + g < end, ok1 = p0 + g + 8 < end;
+        float pc[4], alpha[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; hh++) {
+            float mx = m[hh];
+            mx = ok0 ? fmaxf(mx, sc[hh]) : mx;
+            mx = ok1 ? fmaxf(mx, sc[2 + hh]) : mx;
+#pragma unroll
+            for (int sh = 4; sh <= 16; sh <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
+            alpha[hh] = exp2f(m[hh] - mx);
+            m[hh] = mx;
+            pc[hh] = ok0 ? exp2f(sc[hh] - mx) : 0.f;
+            pc[2 + hh] = ok1 ? exp2f(sc[2 + hh] - mx) : 0.f;
+            l[hh] = fmaf(l[hh], alpha[hh], pc[hh] + pc[2 + hh]);
+        }
+        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+            for (int mt = 0; mt < 8; mt++) { o[mt][0] *= alpha[0]; o[mt][1] *= alpha[1]; o[mt][2] *= alpha[0]; o[mt][3] *= alpha[1]; }
+        }
+        // P^T as B fragments: thread (g, t) needs P[position t, t + 4 (+ 8)][head g], which the thread of
+        // position-row t (or t + 4) that owns heads 2 (g / 2), 2 (g / 2) + 1 holds
+        uint32_t pb[2][2];
+        {
+            const int srcA = t * 4 + (g >> 1), srcB = (t + 4) * 4 + (g >> 1);
+            const bool odd = g & 1;
+#pragma unroll
+            for (int ks = 0; ks < 2; ks++) {
+                const float eA = __shfl_sync(0xffffffffu, pc[2 * ks], srcA), oA = __shfl_sync(0xffffffffu, pc[2 * ks + 1], srcA);
+                const float eB = __shfl_sync(0xffffffffu, pc[2 * ks], srcB), oB = __shfl_sync(0xffffffffu, pc[2 * ks + 1], srcB);
+                pb[ks][0] = tf32_rna(odd ? oA : eA);
+                pb[ks][1] = tf32_rna(odd ? oB : eB);
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++)
+#pragma unroll
+            for (int ks = 0; ks < 2; ks++) {
+                uint32_t a0, a1, a2, a3;
+                if (sizeof(T) == 4) {
+                    a0 = vraw[2 * ks][2 * mt];     a1 = vraw[2 * ks][2 * mt + 1];
+                    a2 = vraw[2 * ks + 1][2 * mt]; a3 = vraw[2 * ks + 1][2 * mt + 1];
+                } else {
+                    a0 = half_lo_f32(vraw[2 * ks][mt]);     a1 = half_hi_f32(vraw[2 * ks][mt]);
+                    a2 = half_lo_f32(vraw[2 * ks + 1][mt]); a3 = half_hi_f32(vraw[2 * ks + 1][mt]);
+                }
+                mma_tf32(o[mt], a0, a1, a2, a3, pb[ks][0], pb[ks][1]);
+            }
+        if (kAhead) {
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+#pragma unroll
+                    for (int w = 0; w < W; w++) kraw[r][c][w] = knext[kAhead ? r : 0][c][w];
+#pragma unroll
+            for (int n = 0; n < 4; n++)
+#pragma unroll
+                for (int w = 0; w < VW; w++) vraw[n][w] = vnext[kAhead ? n : 0][w];
+        }
+    }
+
+    // a head's sum is spread over the eight position-rows: add them up
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++)
+#pragma unroll
+        for (int sh = 4; sh <= 16; sh <<= 1) l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], sh);
+
+    // merge the warps
+    __shared__ float sm_m[kTcWarps][G], sm_l[kTcWarps][G];
+    __shared__ float4 sm_o[kTcWarps][G][32];
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+        const int head = 2 * t + hh;
+        if (head < G) {
+            if (g == 0) { sm_m[warp][head] = m[hh]; sm_l[warp][head] = l[hh]; }
+            float *dst = reinterpret_cast<float *>(&sm_o[warp][head][0]);
+#pragma unroll
+            for (int mt = 0; mt < 8; mt++) {
+                dst[tc_vd<T>(2 * mt, g)] = o[mt][hh];
+                dst[tc_vd<T>(2 * mt + 1, g)] = o[mt][2 + hh];
+            }
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int gg = 0; gg < G; gg++) {
+            float mx = sm_m[0][gg];
+#pragma unroll
+            for (int w = 1; w < kTcWarps; w++) mx = fmaxf(mx, sm_m[w][gg]);
+            float lt = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < kTcWarps; w++) {
+                const float f = exp2f(sm_m[w][gg] - mx);
+                lt = fmaf(sm_l[w][gg], f, lt);
+                const float4 ow = sm_o[w][gg][lane];
+                acc.x = fmaf(ow.x, f, acc.x); acc.y = fmaf(ow.y, f, acc.y);
+                acc.z = fmaf(ow.z, f, acc.z); acc.w = fmaf(ow.w, f, acc.w);
+            }
+            const size_t qrow = (size_t)row * p.q_heads + hq0 + gg;
+            if (p.parts == 1) {
+                const float4 r4 = make_float4(acc.x / lt, acc.y / lt, acc.z / lt, acc.w / lt);
+                *reinterpret_cast<float4 *>(p.out + qrow * D + lane * 4) = r4;
+                if (p.out_max) head_max_store(p.out_max + qrow * 4, r4, true, lane);
+            } else {
+                *reinterpret_cast<float4 *>(p.part_o + (qrow * p.parts + part) * D + lane * 4) = acc;
+                if (lane == 0) p.part_ml[qrow * p.parts + part] = make_float2(mx, lt);
+            }
+        }
+    }
+}
+
 // grid = (q_heads, rows), 128 threads; thread d owns output element d.  The partitions' maxima are
 // read by all threads side by side (thread t takes partitions t, t + 128, ...) and reduced once; the
 // weighted sum then walks the partitions with its loads batched eight at a time: with 64-position
@@ -550,6 +853,8 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
     dim3 grid(p.parts, G == 1 ? p.q_heads : p.kv_heads, p.rows);
     // grouped heads: half a warp per position when the head dimension allows 8 elements per lane
     const bool gqa = G > 1 && p.head_dim % 8 == 0;
+    // ... and the tensor cores where the head dimension is 128
+    const bool gqa_mma = G > 1 && p.head_dim == 128;
     // an f16 cache without grouping: 16 lanes x 16 bytes cover a row, where a full warp would issue
     // 8-byte loads
     const bool half_rows = sizeof(T) == 2 && group == 1 && p.head_dim % 8 == 0;
@@ -557,6 +862,11 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
 #define AB_MHA(GG) lerr = launch_dependent(attn_partition_kernel<T, GG>, grid, dim3(kAttnThreads), 0, l.stream, p)
     cudaError_t lerr = cudaSuccess;
     const bool deep = false;      // four positions in flight per half warp measured no faster than two
+#define AB_TC(GG) lerr = launch_dependent(attn_partition_gqa_mma_kernel<T, GG>, grid, dim3(kTcThreads), 0, l.stream, p)
+    if (gqa_mma) {
+        if (G == 2) AB_TC(2); else if (G == 4) AB_TC(4); else AB_TC(8);
+    } else
+#undef AB_TC
     switch (G) {
     case 1:
         if (half_rows) { if (deep) AB_GQA(1, 4); else AB_GQA(1, 2); }
