@@ -504,20 +504,48 @@ template <typename T> __device__ __forceinline__ uint32_t tc_vd(int m, int g)
     return sizeof(T) == 4 ? (uint32_t)(32 * (m >> 2) + 4 * g + (m & 3)) : (uint32_t)(64 * (m >> 3) + 8 * g + (m & 7));
 }
 
-// grid = (parts, kv_heads, rows); head_dim = 128; G = 2, 4 or 8 query heads per KV head
-// (two warps per CTA, so that a warp walks eight tiles of a 256-position partition and the start of a
-// CTA weighs less, measured no better than four)
+// grid = (parts, kv_heads, rows); head_dim = 128; G = 2, 4 or 8 query heads per KV head.
+// (Two warps per CTA, so that a warp walks eight tiles of a partition and the start of a CTA weighs
+// less, measured no better than four.)
+//
+// The tiles come through shared memory by cp.async, whole rows at a time (512 bytes of one position
+// per instruction at f32, as the one-head kernel reads them: with each thread fetching its own
+// fragments, 64 bytes per row and instruction, the kernel stopped at 0.70 of the HBM peak whatever
+// the number of warps), and the fragments are read back with 128-bit shared-memory loads; the rows
+// are padded (K by 64 bytes, V by 32) so that a quarter-warp's loads fall into different banks.
+// A tile belongs to one warp: __syncwarp orders its copies and loads, there is no CTA-wide barrier in
+// the loop.  One stage per warp and three CTAs per SM (twelve warps) measured the same as two stages.
 static constexpr int kTcWarps = 4;
 static constexpr int kTcThreads = kTcWarps * 32;
+template <typename T> __host__ __device__ constexpr int tc_stages() { return 1; }
+template <typename T> __host__ __device__ constexpr uint32_t tc_row_bytes() { return 128u * (uint32_t)sizeof(T); }
+template <typename T> __host__ __device__ constexpr uint32_t tc_kstride() { return tc_row_bytes<T>() + 64u; }
+template <typename T> __host__ __device__ constexpr uint32_t tc_vstride() { return tc_row_bytes<T>() + 32u; }
+template <typename T> __host__ __device__ constexpr uint32_t tc_tile_bytes() { return 16u * (tc_kstride<T>() + tc_vstride<T>()); }
+template <typename T> __host__ __device__ constexpr size_t tc_smem_bytes() { return (size_t)tc_stages<T>() * kTcWarps * tc_tile_bytes<T>(); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool ok)
+{   // ok = false fills the 16 bytes with zeros and reads nothing
+    const uint32_t n = ok ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
 
 template <typename T, int G>
-__global__ void __launch_bounds__(kTcThreads, 256 / kTcThreads)
+__global__ void __launch_bounds__(kTcThreads, 3)
 attn_partition_gqa_mma_kernel(const AttnParams p)
 {
+    extern __shared__ __align__(16) unsigned char tc_ring[];
     pdl_wait();
     constexpr uint32_t D = 128;
-    constexpr int W = sizeof(T) == 4 ? 8 : 4;        // 32-bit words a thread holds of a K row's 32-d block
-    constexpr int VW = sizeof(T) == 4 ? 16 : 8;      // ... and of a V row
+    constexpr bool F32 = sizeof(T) == 4;
+    constexpr int kTcStages = tc_stages<T>();
+    constexpr int kVQ = F32 ? 4 : 2;                 // 16-byte pieces of a V row a thread reads
     const uint32_t part = blockIdx.x, row = blockIdx.z, kvh = blockIdx.y;
     const uint32_t hq0 = kvh * G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -540,6 +568,55 @@ attn_partition_gqa_mma_kernel(const AttnParams p)
     const size_t row_stride = (size_t)p.kv_heads * D;
     const size_t head_off = (size_t)kvh * D;
 
+    // stage st of this warp: 16 K rows, then 16 V rows
+    const uint32_t ring0 = (uint32_t)__cvta_generic_to_shared(tc_ring) + (uint32_t)warp * tc_tile_bytes<T>();
+    auto stage = [&](int st) -> uint32_t { return ring0 + (uint32_t)st * kTcWarps * tc_tile_bytes<T>(); };
+    constexpr uint32_t KS = tc_kstride<T>(), VS = tc_vstride<T>(), VOFF = 16u * KS;
+    // where this thread's fragments lie: K rows g, g + 8 at the d's of block c; V rows t + 4 n at its 16 d's
+    const uint32_t koff = (uint32_t)g * KS + (F32 ? 16u * t : 16u * t), voff = VOFF + (uint32_t)t * VS + 16u * g;
+
+    // lane i < 16 finds where position p0 + i of a tile lies; the others get it by shuffle.  The look-up
+    // runs one tile ahead of the copies.
+    auto lookup = [&](uint32_t p0) -> uint32_t {
+        uint32_t phys = 0;
+        if (lane < 16 && p0 + lane < end) {
+            const uint32_t j = p0 + lane;
+            phys = rv.pages == nullptr ? j : __ldg(rv.pages + j / p.block) * p.block + j % p.block;
+        }
+        return phys;
+    };
+    // whole rows: an instruction copies one position's 512 bytes (f32) or two positions' 256 (f16) of K,
+    // then of V.  Positions past the end are zeros.
+    auto issue_tile = [&](uint32_t p0, uint32_t phys, int st) {
+        const uint32_t base = stage(st);
+        constexpr int kPerInstr = F32 ? 1 : 2;
+#pragma unroll
+        for (int j = 0; j < 16 / kPerInstr; j++) {
+            const int rowi = F32 ? j : 2 * j + (lane >> 4);
+            const int chunk = F32 ? lane : (lane & 15);
+            const uint32_t ph = __shfl_sync(0xffffffffu, phys, rowi);
+            const bool ok = p0 + rowi < end;
+            const size_t src = (size_t)ph * row_stride + head_off + (size_t)chunk * (16 / sizeof(T));
+            cp_async16(base + (uint32_t)rowi * KS + 16u * chunk, kc + src, ok);
+            cp_async16(base + VOFF + (uint32_t)rowi * VS + 16u * chunk, vc + src, ok);
+        }
+    };
+
+    constexpr uint32_t kStep = 16u * kTcWarps;
+    const uint32_t first = begin + 16u * warp;
+    uint32_t phys_next;
+    {
+        uint32_t ph[kTcStages];
+#pragma unroll
+        for (int k = 0; k < kTcStages; k++) ph[k] = lookup(first + k * kStep);
+#pragma unroll
+        for (int k = 0; k < kTcStages - 1; k++) {
+            if (first + k * kStep < end) issue_tile(first + k * kStep, ph[k], k);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        phys_next = ph[kTcStages - 1];
+    }
+
     // Q^T as B fragments: column g is head g (zero past the group), rows in the K fragments' order
     uint32_t qb[16][2];
 #pragma unroll
@@ -559,88 +636,48 @@ attn_partition_gqa_mma_kernel(const AttnParams p)
 #pragma unroll
         for (int e = 0; e < 4; e++) o[mt][e] = 0.f;
 
-    // lane i < 16 finds where position p0 + i of a tile lies; the others get it by shuffle.  The look-up
-    // runs one tile ahead, so that a tile's loads do not wait for its page-table entries.
-    auto lookup = [&](uint32_t p0) -> uint32_t {
-        uint32_t phys = 0;
-        if (lane < 16 && p0 + lane < end) {
-            const uint32_t j = p0 + lane;
-            phys = rv.pages == nullptr ? j : __ldg(rv.pages + j / p.block) * p.block + j % p.block;
-        }
-        return phys;
-    };
-    auto load_tile = [&](uint32_t p0, uint32_t phys, uint32_t (&kraw)[2][4][W], uint32_t (&vraw)[4][VW]) {
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-            const uint32_t ph = __shfl_sync(0xffffffffu, phys, g + 8 * r);
-            const bool ok = p0 + g + 8 * r < end;
-            const T *src = kc + (size_t)ph * row_stride + head_off;
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                if (sizeof(T) == 4) {
-                    uint4 a = make_uint4(0, 0, 0, 0), b = a;
-                    if (ok) { a = ld_nc16(src + 32 * c + 4 * t); b = ld_nc16(src + 32 * c + 16 + 4 * t); }
-                    kraw[r][c][0] = a.x; kraw[r][c][1] = a.y; kraw[r][c][2] = a.z; kraw[r][c][3] = a.w;
-                    kraw[r][c][W - 4] = b.x; kraw[r][c][W - 3] = b.y; kraw[r][c][W - 2] = b.z; kraw[r][c][W - 1] = b.w;
-                } else {
-                    uint4 a = make_uint4(0, 0, 0, 0);
-                    if (ok) a = ld_nc16(src + 32 * c + 8 * t);
-                    kraw[r][c][0] = a.x; kraw[r][c][1] = a.y; kraw[r][c][2] = a.z; kraw[r][c][3] = a.w;
-                }
-            }
-        }
-#pragma unroll
-        for (int n = 0; n < 4; n++) {
-            const uint32_t ph = __shfl_sync(0xffffffffu, phys, t + 4 * n);
-            const bool ok = p0 + t + 4 * n < end;
-            const T *src = vc + (size_t)ph * row_stride + head_off;
-#pragma unroll
-            for (int q = 0; q < VW / 4; q++) {
-                uint4 a = make_uint4(0, 0, 0, 0);
-                if (ok) a = ld_nc16(sizeof(T) == 4 ? src + 32 * q + 4 * g : src + 64 * q + 8 * g);
-                vraw[n][4 * q] = a.x; vraw[n][4 * q + 1] = a.y; vraw[n][4 * q + 2] = a.z; vraw[n][4 * q + 3] = a.w;
-            }
-        }
-    };
-    // an f16 tile is 8 KB: the registers hold two, and the next tile's loads are in flight while this
-    // one is multiplied; an f32 tile (16 KB) fills them alone
-    constexpr bool kAhead = sizeof(T) == 2;
-    constexpr uint32_t kStep = 16u * kTcWarps;
-    const uint32_t first = begin + 16u * warp;
-    uint32_t phys_next = lookup(first);
-    uint32_t kraw[2][4][W], vraw[4][VW];
-    uint32_t knext[kAhead ? 2 : 1][4][W], vnext[kAhead ? 4 : 1][VW];
-    if (kAhead && first < end) {
-        load_tile(first, phys_next, kraw, vraw);
-        phys_next = lookup(first + kStep);
-    }
+    int st = 0;                                               // stage of the tile being multiplied
     for (uint32_t p0 = first; p0 < end; p0 += kStep) {
-        if (kAhead) {
-            if (p0 + kStep < end) load_tile(p0 + kStep, phys_next, reinterpret_cast<uint32_t (&)[2][4][W]>(knext),
-                                            reinterpret_cast<uint32_t (&)[4][VW]>(vnext));
-            phys_next = lookup(p0 + 2 * kStep);
-        } else {
-            const uint32_t phys = phys_next;
-            phys_next = lookup(p0 + kStep);
-            load_tile(p0, phys, kraw, vraw);
+        {   // the tile kTcStages - 1 ahead goes into the stage the previous tile has left
+            const uint32_t pi = p0 + (kTcStages - 1) * kStep;
+            const int sti = st == 0 ? kTcStages - 1 : st - 1;
+            __syncwarp();                             // every lane has read what that stage held
+            if (pi < end) issue_tile(pi, phys_next, sti);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            phys_next = lookup(pi + kStep);
+            asm volatile("cp.async.wait_group %0;" ::"n"(kTcStages - 1) : "memory");
+            __syncwarp();                             // ... and sees what the other lanes copied
         }
+        const uint32_t tile = stage(st);
 
         // S^T: sc[0], sc[1] = position g x heads 2t, 2t + 1; sc[2], sc[3] = position g + 8
         float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};       // two chains of eight MMAs
 #pragma unroll
-        for (int c = 0; c < 4; c++)
+        for (int c = 0; c < 4; c++) {
+            uint32_t k0[8], k1[8];                            // rows g and g + 8: the thread's words of block c
+            if (F32) {
+                const uint4 a = lds16(tile + koff + 128u * c), b = lds16(tile + koff + 128u * c + 64u);
+                const uint4 a1 = lds16(tile + koff + 8u * KS + 128u * c), b1 = lds16(tile + koff + 8u * KS + 128u * c + 64u);
+                k0[0] = a.x; k0[1] = a.y; k0[2] = a.z; k0[3] = a.w; k0[4] = b.x; k0[5] = b.y; k0[6] = b.z; k0[7] = b.w;
+                k1[0] = a1.x; k1[1] = a1.y; k1[2] = a1.z; k1[3] = a1.w; k1[4] = b1.x; k1[5] = b1.y; k1[6] = b1.z; k1[7] = b1.w;
+            } else {
+                const uint4 a = lds16(tile + koff + 64u * c), a1 = lds16(tile + koff + 8u * KS + 64u * c);
+                k0[0] = a.x; k0[1] = a.y; k0[2] = a.z; k0[3] = a.w;
+                k1[0] = a1.x; k1[1] = a1.y; k1[2] = a1.z; k1[3] = a1.w;
+            }
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 uint32_t a0, a1, a2, a3;
-                if (sizeof(T) == 4) {
-                    a0 = tf32_rna(__uint_as_float(kraw[0][c][2 * i]));     a2 = tf32_rna(__uint_as_float(kraw[0][c][2 * i + 1]));
-                    a1 = tf32_rna(__uint_as_float(kraw[1][c][2 * i]));     a3 = tf32_rna(__uint_as_float(kraw[1][c][2 * i + 1]));
+                if (F32) {
+                    a0 = tf32_rna(__uint_as_float(k0[2 * i])); a2 = tf32_rna(__uint_as_float(k0[2 * i + 1]));
+                    a1 = tf32_rna(__uint_as_float(k1[2 * i])); a3 = tf32_rna(__uint_as_float(k1[2 * i + 1]));
                 } else {
-                    a0 = half_lo_f32(kraw[0][c][i]); a2 = half_hi_f32(kraw[0][c][i]);
-                    a1 = half_lo_f32(kraw[1][c][i]); a3 = half_hi_f32(kraw[1][c][i]);
+                    a0 = half_lo_f32(k0[i]); a2 = half_hi_f32(k0[i]);
+                    a1 = half_lo_f32(k1[i]); a3 = half_hi_f32(k1[i]);
                 }
                 mma_tf32((i & 1) ? sc2 : sc, a0, a1, a2, a3, qb[4 * c + i][0], qb[4 * c + i][1]);
             }
+        }
 #pragma unroll
         for (int e = 0; e < 4; e++) sc[e] += sc2[e];
 
@@ -678,33 +715,35 @@ attn_partition_gqa_mma_kernel(const AttnParams p)
                 pb[ks][1] = tf32_rna(odd ? oB : eB);
             }
         }
+        // O^T += V^T P^T: a 16-byte piece of a V row is four d's (f32: tiles 2q, 2q + 1) or eight (f16:
+        // tiles 4q .. 4q + 3) of the thread's sixteen
 #pragma unroll
-        for (int mt = 0; mt < 8; mt++)
+        for (int q = 0; q < kVQ; q++) {
+            uint4 v[4];
 #pragma unroll
-            for (int ks = 0; ks < 2; ks++) {
-                uint32_t a0, a1, a2, a3;
-                if (sizeof(T) == 4) {
-                    a0 = vraw[2 * ks][2 * mt];     a1 = vraw[2 * ks][2 * mt + 1];
-                    a2 = vraw[2 * ks + 1][2 * mt]; a3 = vraw[2 * ks + 1][2 * mt + 1];
-                } else {
-                    a0 = half_lo_f32(vraw[2 * ks][mt]);     a1 = half_hi_f32(vraw[2 * ks][mt]);
-                    a2 = half_lo_f32(vraw[2 * ks + 1][mt]); a3 = half_hi_f32(vraw[2 * ks + 1][mt]);
+            for (int n = 0; n < 4; n++) v[n] = lds16(tile + voff + 4u * n * VS + 128u * q);
+            const uint32_t vw[4][4] = {{v[0].x, v[0].y, v[0].z, v[0].w}, {v[1].x, v[1].y, v[1].z, v[1].w},
+                                       {v[2].x, v[2].y, v[2].z, v[2].w}, {v[3].x, v[3].y, v[3].z, v[3].w}};
+#pragma unroll
+            for (int x = 0; x < (F32 ? 2 : 4); x++) {
+                const int mt = F32 ? 2 * q + x : 4 * q + x;
+#pragma unroll
+                for (int ks = 0; ks < 2; ks++) {
+                    uint32_t a0, a1, a2, a3;
+                    if (F32) {
+                        a0 = vw[2 * ks][2 * x];     a1 = vw[2 * ks][2 * x + 1];
+                        a2 = vw[2 * ks + 1][2 * x]; a3 = vw[2 * ks + 1][2 * x + 1];
+                    } else {
+                        a0 = half_lo_f32(vw[2 * ks][x]);     a1 = half_hi_f32(vw[2 * ks][x]);
+                        a2 = half_lo_f32(vw[2 * ks + 1][x]); a3 = half_hi_f32(vw[2 * ks + 1][x]);
+                    }
+                    mma_tf32(o[mt], a0, a1, a2, a3, pb[ks][0], pb[ks][1]);
                 }
-                mma_tf32(o[mt], a0, a1, a2, a3, pb[ks][0], pb[ks][1]);
             }
-        if (kAhead) {
-#pragma unroll
-            for (int r = 0; r < 2; r++)
-#pragma unroll
-                for (int c = 0; c < 4; c++)
-#pragma unroll
-                    for (int w = 0; w < W; w++) kraw[r][c][w] = knext[kAhead ? r : 0][c][w];
-#pragma unroll
-            for (int n = 0; n < 4; n++)
-#pragma unroll
-                for (int w = 0; w < VW; w++) vraw[n][w] = vnext[kAhead ? n : 0][w];
         }
+        st = st == kTcStages - 1 ? 0 : st + 1;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // a head's sum is spread over the eight position-rows: add them up
 #pragma unroll
@@ -712,9 +751,10 @@ attn_partition_gqa_mma_kernel(const AttnParams p)
 #pragma unroll
         for (int sh = 4; sh <= 16; sh <<= 1) l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], sh);
 
-    // merge the warps
+    // merge the warps (their outputs go where the ring was)
     __shared__ float sm_m[kTcWarps][G], sm_l[kTcWarps][G];
-    __shared__ float4 sm_o[kTcWarps][G][32];
+    __syncthreads();
+    float4 (*sm_o)[G][32] = reinterpret_cast<float4 (*)[G][32]>(tc_ring);
 #pragma unroll
     for (int hh = 0; hh < 2; hh++) {
         const int head = 2 * t + hh;
@@ -811,6 +851,22 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const AttnParams p)
     }
 }
 
+// the tensor-core kernel's ring is more shared memory than a kernel gets unasked: once per device and kernel
+static int tc_prepare(void (*kernel)(const AttnParams), size_t bytes)
+{
+    static struct { void (*k)(const AttnParams); int dev; } done[64];
+    static int ndone = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    for (int i = 0; i < ndone; i++)
+        if (done[i].k == kernel && done[i].dev == dev) return AB_OK;
+    int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes),
+                        "attn_partition_gqa_mma_kernel shared memory");
+    if (rc) return rc;
+    if (ndone < 64) { done[ndone].k = kernel; done[ndone].dev = dev; ndone++; }
+    return AB_OK;
+}
+
 template <typename T>
 static int run_attention(Launch &l, AttnParams &p, const char *name)
 {
@@ -862,7 +918,8 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
 #define AB_MHA(GG) lerr = launch_dependent(attn_partition_kernel<T, GG>, grid, dim3(kAttnThreads), 0, l.stream, p)
     cudaError_t lerr = cudaSuccess;
     const bool deep = false;      // four positions in flight per half warp measured no faster than two
-#define AB_TC(GG) lerr = launch_dependent(attn_partition_gqa_mma_kernel<T, GG>, grid, dim3(kTcThreads), 0, l.stream, p)
+#define AB_TC(GG) lerr = tc_prepare(attn_partition_gqa_mma_kernel<T, GG>, tc_smem_bytes<T>()) ? cudaErrorInvalidValue : \
+        launch_dependent(attn_partition_gqa_mma_kernel<T, GG>, grid, dim3(kTcThreads), tc_smem_bytes<T>(), l.stream, p)
     if (gqa_mma) {
         if (G == 2) AB_TC(2); else if (G == 4) AB_TC(4); else AB_TC(8);
     } else
