@@ -537,7 +537,7 @@ __device__ __forceinline__ uint4 lds16(uint32_t addr)
 }
 
 template <typename T, int G>
-__global__ void __launch_bounds__(kTcThreads, 3)
+__global__ void __launch_bounds__(kTcThreads, sizeof(T) == 4 ? 3 : 4)
 attn_partition_gqa_mma_kernel(const AttnParams p)
 {
     extern __shared__ __align__(16) unsigned char tc_ring[];
