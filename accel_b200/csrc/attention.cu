@@ -20,6 +20,7 @@
 #include <math_constants.h>
 
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -546,8 +547,10 @@ attn_partition_gqa_mma_kernel(const AttnParams p)
     constexpr bool F32 = sizeof(T) == 4;
     constexpr int kTcStages = tc_stages<T>();
     constexpr int kVQ = F32 ? 4 : 2;                 // 16-byte pieces of a V row a thread reads
-    const uint32_t part = blockIdx.x, row = blockIdx.z, kvh = blockIdx.y;
-    const uint32_t hq0 = kvh * G;
+    // G = 1: one query head per CTA, whatever the number of heads that share its KV head
+    const uint32_t part = blockIdx.x, row = blockIdx.z;
+    const uint32_t kvh = G == 1 ? blockIdx.y / (p.q_heads / p.kv_heads) : blockIdx.y;
+    const uint32_t hq0 = G == 1 ? blockIdx.y : kvh * G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
     const RowView rv = row_view(p, row);
@@ -856,6 +859,8 @@ static int tc_prepare(void (*kernel)(const AttnParams), size_t bytes)
 {
     static struct { void (*k)(const AttnParams); int dev; } done[64];
     static int ndone = 0;
+    static std::mutex mu;                            // launches may come from several host threads
+    std::lock_guard<std::mutex> lock(mu);
     int dev = 0;
     cudaGetDevice(&dev);
     for (int i = 0; i < ndone; i++)
@@ -910,7 +915,9 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
     // grouped heads: half a warp per position when the head dimension allows 8 elements per lane
     const bool gqa = G > 1 && p.head_dim % 8 == 0;
     // ... and the tensor cores where the head dimension is 128
-    const bool gqa_mma = G > 1 && p.head_dim == 128;
+    // (an f16 cache without grouping too: whole-row copies serve its 256-byte rows better than the
+    // half-warp loads, 0.70 against 0.58-0.63 of the peak)
+    const bool gqa_mma = p.head_dim == 128 && (G > 1 || sizeof(T) == 2);
     // an f16 cache without grouping: 16 lanes x 16 bytes cover a row, where a full warp would issue
     // 8-byte loads
     const bool half_rows = sizeof(T) == 2 && group == 1 && p.head_dim % 8 == 0;
@@ -921,7 +928,7 @@ static int run_attention(Launch &l, AttnParams &p, const char *name)
 #define AB_TC(GG) lerr = tc_prepare(attn_partition_gqa_mma_kernel<T, GG>, tc_smem_bytes<T>()) ? cudaErrorInvalidValue : \
         launch_dependent(attn_partition_gqa_mma_kernel<T, GG>, grid, dim3(kTcThreads), tc_smem_bytes<T>(), l.stream, p)
     if (gqa_mma) {
-        if (G == 2) AB_TC(2); else if (G == 4) AB_TC(4); else AB_TC(8);
+        if (G == 1) AB_TC(1); else if (G == 2) AB_TC(2); else if (G == 4) AB_TC(4); else AB_TC(8);
     } else
 #undef AB_TC
     switch (G) {

@@ -720,7 +720,8 @@ def run_b200(args):
     attn_bytes = int(2 * engine.hk * cfg.head_dim * esz * lens.sum()
                      + 2 * B * engine.hq * cfg.head_dim * 4 + engine.pages.numel() * 4 + B * 4)
     attn_gbs = attn_bytes / (attn_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "attn_partition_kernel (+ attn_combine_kernel)",
+    roofline = {"bound": "hbm", "kernel": ("attn_partition_gqa_mma_kernel<__half, 1>" if cache_dtype == torch.float16
+                                            else "attn_partition_kernel") + " (+ attn_combine_kernel)",
                 "achieved": attn_gbs, "peak": peak, "unit": "GB/s", "frac": attn_gbs / peak,
                 "peak_source": peak_src, "bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
                 # dram__bytes_read + dram__bytes_write of one launch: NOT measured in this run (it needs
