@@ -91,7 +91,8 @@ def test_a_length_past_the_page_table_is_truncated():
 
 @pytest.mark.parametrize("f16", [False, True])
 @pytest.mark.parametrize("qH,kvH,D,block", [(32, 8, 128, 16), (32, 32, 128, 16), (8, 4, 64, 8),
-                                            (6, 2, 40, 4), (16, 2, 128, 32), (4, 4, 8, 1)])
+                                            (6, 2, 40, 4), (16, 2, 128, 32), (4, 4, 8, 1), (8, 4, 128, 16),
+                                            (6, 2, 128, 8)])
 def test_batched_matches_the_oracle(qH, kvH, D, block, f16):
     batch = 5
     rng = np.random.default_rng(qH * 1000 + D)
@@ -176,9 +177,11 @@ def test_zero_length_is_nan_as_in_the_reference():
 
 
 @pytest.mark.parametrize("f16", [False, True])
-def test_ragged_matches_the_oracle(f16):
+@pytest.mark.parametrize("qH,kvH,D", [(8, 2, 64), (8, 2, 128), (4, 2, 128)])
+def test_ragged_matches_the_oracle(qH, kvH, D, f16):
     # internal/kernels/ragged.go:61-241: a prefill chunk, three decodes, an empty row, padding
-    qH, kvH, D, block, MP = 8, 2, 64, 8, 80
+    # (head dimension 128 with grouped heads runs on the tensor cores)
+    block, MP = 8, 80
     extents = np.array([37, 1, 0, 1, 1], np.uint32)
     lengths = np.array([300, 77, 9, 1, 600], np.uint32)
     batch = extents.size

@@ -23,6 +23,8 @@ def u32(a):
     (8, 2, 64, 16, 130, 37, False),      # a prefill that extends a cache of 37 positions; GQA
     (8, 2, 64, 16, 130, 37, True),
     (32, 8, 128, 16, 40, 500, True),
+    (32, 8, 128, 16, 70, 300, False),    # grouped heads of dimension 128: the tensor-core kernel, f32 cache
+    (4, 2, 128, 8, 33, 90, False),       # two heads per KV head
 ])
 def test_paged_prefill_matches_the_oracle(qH, kvH, D, block, q_seq, base, f16):
     rng = np.random.default_rng(q_seq + base)
