@@ -3,6 +3,7 @@ refuses what it must, and its host-side pieces (quantizer, f16, block pool, shar
 bit-identical to the oracle."""
 import ctypes as C
 import re
+import struct
 from pathlib import Path
 
 import numpy as np
@@ -34,6 +35,31 @@ def test_kernel_registry_names_the_reference_kernels():
               "SegmentOffsets", "ScatterRows", "ScatterRowsF16", "GatherRows", "RMSNorm", "RoPE",
               "SwiGLU", "ElemAdd", "SampleArgmax", "CastF32ToF16"]:
         assert n in names
+
+
+def test_every_registered_kernel_is_documented_in_the_header():
+    """include/accel_b200.h lists every kernel name ab_launch dispatches, with its bindings and uniform."""
+    header = (ROOT / "include" / "accel_b200.h").read_text()
+    words = set(re.findall(r"[A-Za-z0-9_]+", header))
+    missing = [n for n in runtime.kernel_names() if n not in words]
+    assert not missing, missing
+
+
+def test_the_forms_with_row_maxima_are_registered_with_their_binding_counts():
+    # AttentionDecodeBatchedMax: the seventh binding holds four maxima per head
+    lens = [32 * 32 * 128, 1, 1, 32 * 256, 32, 32 * 32 * 128, 32 * 32 * 4]
+    u = runtime.batched_dims(32, 32, 8, 128, 16, 256, 0.088)
+    assert runtime.workspace_bytes("AttentionDecodeBatchedMax", lens, u) == \
+        runtime.workspace_bytes("AttentionDecodeBatched", lens[:6], u)
+    with pytest.raises(_lib.AccelError, match="takes 7 bindings"):
+        runtime.workspace_bytes("AttentionDecodeBatchedMax", lens[:6], u)
+    # the decode kernel takes its rows' maxima as a binding and needs no scratch for them
+    M, K, N = 16, 4096, 11008
+    packed_words = (_lib.lib().ab_int4_prepack_bytes(K, N) + 3) // 4
+    assert runtime.workspace_bytes("QuantMatMulInt4PackedA", [M * K, M * 32, packed_words, M * N],
+                                   struct.pack("<IIII", M, N, K, 32)) == 0
+    assert runtime.workspace_bytes("QuantMatMulInt4Packed", [M * K, packed_words, M * N],
+                                   runtime.gemm_dims(M, N, K)) > 0
 
 
 def test_an_unknown_kernel_is_a_refusal_not_a_fallback():
