@@ -108,7 +108,9 @@ __host__ __device__ constexpr size_t sx_smem_bytes(int G)
 
 // grid = (ceil(N / 128 / G), K splits), cluster = (1, splits, 1); a CTA owns G adjacent column
 // groups.  a: [M][K] f32 (M <= 16 rows of this pass), amax: the largest magnitude of each of the M
-// rows (NULL: every CTA scans its own K range), packed: the stream, ep: where the columns go.
+// rows, or [M][ep.amax_parts] maxima of parts of a row of which the largest counts (NULL: every CTA
+// scans its own K range), packed: the stream, ep: where the columns go (and, for the SwiGLU form,
+// where the largest |out| of every warp's 32 columns goes).
 template <int G>
 __global__ void __launch_bounds__(kSxThreads)
 int4_stream_kernel(const float *__restrict__ a, const float *__restrict__ amax,
